@@ -1,0 +1,182 @@
+/* lmg_b200.h - C ABI of the B200 (sm_100a) gridding library, liblmg_b200.so.
+ *
+ * These entry points are what a binding of libmolgrid's gridding path calls instead of
+ * the reference's own CUDA overloads.  Each declaration names the reference interface it
+ * replaces (paths relative to the libmolgrid tree).  Conventions:
+ *
+ *  - Every array argument is a DEVICE pointer to dense row-major fp32 unless its comment
+ *    says "host".  Grids are [T][D][D][D] per example with Z fastest, as in the reference
+ *    (include/libmolgrid/grid.h:119-128); batches add a leading example dimension.
+ *  - Nothing is allocated on the caller's behalf: kernels take their scratch memory from
+ *    the caller-provided workspace (size from lmg_workspace_bytes).  Outputs are fully
+ *    overwritten.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream, which is
+ *    what the reference always uses).  No call synchronises the host unless it says so.
+ *  - Return value: LMG_OK or an LMG_ERR_* code; lmg_last_error() (thread-local) describes
+ *    the last failure.  The codes map back to the reference's exceptions:
+ *    LMG_ERR_OUT_OF_RANGE <-> std::out_of_range, LMG_ERR_INVALID_ARGUMENT <->
+ *    std::invalid_argument, LMG_ERR_CUDA <-> std::runtime_error (LMG_CUDA_CHECK,
+ *    include/libmolgrid/common.h:41-47).  Nothing throws across this boundary.
+ *  - There is no CPU fallback: without a CUDA device every compute call fails with
+ *    LMG_ERR_CUDA.
+ */
+#ifndef LMG_B200_H_
+#define LMG_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  LMG_OK = 0,
+  LMG_ERR_OUT_OF_RANGE = 1,
+  LMG_ERR_INVALID_ARGUMENT = 2,
+  LMG_ERR_CUDA = 3,
+  LMG_ERR_WORKSPACE = 4
+};
+
+/* GridMaker settings and derived constants.
+ * Replaces the data members of libmolgrid::GridMaker (include/libmolgrid/grid_maker.h:36-48). */
+typedef struct lmg_gridmaker {
+  float resolution;
+  float dimension;
+  float radius_scale;
+  float gaussian_radius_multiple; /* stored non-negative, as the reference does */
+  float final_radius_multiple;
+  float A, B, C, D, E;
+  unsigned dim; /* grid points per side */
+  int binary;
+  int radii_type_indexed;
+} lmg_gridmaker;
+
+/* Fills *g exactly as GridMaker::GridMaker + GridMaker::initialize do
+ * (include/libmolgrid/grid_maker.h:70-74, src/grid_maker.cpp:15-36), on the host. */
+int lmg_gridmaker_init(lmg_gridmaker* g, float resolution, float dimension, int binary,
+                       int radii_type_indexed, float radius_scale, float gaussian_radius_multiple);
+
+/* Rotation about `center` followed by a translation.
+ * Replaces libmolgrid::Transform's state (include/libmolgrid/transform.h:28-31);
+ * q = (real, i, j, k) as libmolgrid::Quaternion stores it (include/libmolgrid/quaternion.h:22-26). */
+typedef struct lmg_transform {
+  float q[4];
+  float center[3];
+  float translate[3];
+} lmg_transform;
+
+/* Fills *t with a random transform drawn exactly as Transform::Transform(float3, float, bool)
+ * does (src/transform.cpp:13-33) from the library's engine; lmg_set_random_seed reseeds it
+ * (python/bindings.in.cpp:400, src/libmolgrid.cpp:11).  Host only. */
+int lmg_transform_random(lmg_transform* t, const float center[3], float random_translate,
+                         int random_rotate);
+void lmg_set_random_seed(unsigned seed);
+
+/* The atoms of a batch of `batch` examples, padded to `max_atoms` per example: the argument
+ * set of the reference's batched raw-tensor overloads (include/libmolgrid/grid_maker.h:265-301)
+ * with the per-example Transform of forward(Example, Transform, Grid)
+ * (src/grid_maker.cpp:109-116) folded in.  batch == 1 gives the single-example overloads. */
+typedef struct lmg_atoms {
+  int batch;
+  int max_atoms;
+  int ntypes;                /* channels of the grid (and length of a type vector) */
+  const int* n_atoms;        /* [batch] valid atoms per example, or NULL: all max_atoms */
+  const float* coords;       /* [batch][max_atoms][3] */
+  const float* type_index;   /* [batch][max_atoms], or NULL when type_vector is given */
+  const float* type_vector;  /* [batch][max_atoms][ntypes], or NULL */
+  const float* radii;        /* [batch][max_atoms], or [batch][ntypes] if radii_type_indexed */
+  const float* centers;      /* [batch][3] grid centres, or NULL: use center_host for all */
+  float center_host[3];      /* host value */
+  const lmg_transform* transforms; /* [batch] applied to coords before gridding, or NULL */
+  const lmg_transform* transform_host; /* host: one transform for every example, or NULL;
+                                          ignored when `transforms` is given */
+} lmg_atoms;
+
+enum {
+  LMG_OP_FORWARD = 0,
+  LMG_OP_BACKWARD = 1,
+  LMG_OP_BACKWARD_GRADIENTS = 2,
+  LMG_OP_BACKWARD_RELEVANCE = 3
+};
+
+/* Scratch bytes that let the given op process the whole batch in one pass.  A smaller
+ * workspace makes the op run the batch in several passes; it fails with LMG_ERR_WORKSPACE
+ * only if not even one example fits.  `vector_types` != 0 for type_vector input. */
+size_t lmg_workspace_bytes(const lmg_gridmaker* g, int op, int batch, int max_atoms, int ntypes,
+                           int vector_types);
+
+/* Density (or binary occupancy) grids out[batch][ntypes][D][D][D].
+ * Replaces GridMaker::forward for index types (src/grid_maker.cu:260-289, CPU :153-212),
+ * vector types (src/grid_maker.cu:402-441, CPU :214-271) and their batched / Transform
+ * overloads (include/libmolgrid/grid_maker.h:194-201,265-301, src/grid_maker.cpp:109-141).
+ * Results follow the reference's CPU path. */
+int lmg_forward(const lmg_gridmaker* g, const lmg_atoms* atoms, float* out, void* workspace,
+                size_t workspace_bytes, void* stream);
+
+/* Atom gradients atom_gradients[batch][max_atoms][3] from grid gradients
+ * diff[batch][ntypes][D][D][D]; with vector types also type_gradients[batch][max_atoms][ntypes]
+ * (must be NULL for index types).
+ * Replaces GridMaker::backward (src/grid_maker.cu:576-642, CPU src/grid_maker.cpp:436-519). */
+int lmg_backward(const lmg_gridmaker* g, const lmg_atoms* atoms, const float* diff,
+                 float* atom_gradients, float* type_gradients, void* workspace,
+                 size_t workspace_bytes, void* stream);
+
+/* Second-order pass for vector types: from diff and the incoming atom_gradients /
+ * type_gradients produce diffdiff[batch][ntypes][D][D][D], atom_diffdiff[batch][max_atoms][3]
+ * and type_diffdiff[batch][max_atoms][ntypes] (identically zero).
+ * Replaces GridMaker::backward_gradients (src/grid_maker.cu:755-803, CPU
+ * src/grid_maker.cpp:529-672). */
+int lmg_backward_gradients(const lmg_gridmaker* g, const lmg_atoms* atoms, const float* diff,
+                           const float* atom_gradients, const float* type_gradients,
+                           float* diffdiff, float* atom_diffdiff, float* type_diffdiff,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
+/* Per-atom relevance relevance[batch][max_atoms] from a density grid and a relevance grid,
+ * index types only.
+ * Replaces GridMaker::backward_relevance (src/grid_maker.cu:974-992, CPU
+ * src/grid_maker.cpp:684-704). */
+int lmg_backward_relevance(const lmg_gridmaker* g, const lmg_atoms* atoms, const float* density,
+                           const float* diff, float* relevance, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
+/* out[n][3] = transform applied to in[n][3]; in-place is allowed; `t` is a host struct.
+ * dotranslate == 0 rotates about the centre only.
+ * Replaces Transform::forward / Transform::backward on Grid2fCUDA
+ * (src/transform.cu:66-93, CPU src/transform.cpp:57-108). */
+int lmg_transform_forward(const lmg_transform* t, int n, const float* in, float* out,
+                          int dotranslate, void* stream);
+int lmg_transform_backward(const lmg_transform* t, int n, const float* in, float* out,
+                           int dotranslate, void* stream);
+
+/* GridInterpolater settings.
+ * Replaces libmolgrid::GridInterpolater's members (include/libmolgrid/grid_interpolater.h:33-38,59-64). */
+typedef struct lmg_interpolater {
+  float in_resolution, in_dimension, out_resolution, out_dimension;
+  unsigned in_dim, out_dim;
+} lmg_interpolater;
+
+int lmg_interpolater_init(lmg_interpolater* gi, float in_resolution, float in_dimension,
+                          float out_resolution, float out_dimension);
+
+/* Trilinear resample out[batch][nchannels][Dout]^3 of in[batch][nchannels][Din]^3 under one
+ * transform per example.  transforms[batch], in_centers[batch][3] and out_centers[batch][3]
+ * are HOST arrays (the reference takes them by value); they are copied into the launch.
+ * Replaces GridInterpolater::forward (src/grid_interpolater.cu:134-166, CPU
+ * src/grid_interpolater.cpp:16-48). */
+int lmg_interpolate(const lmg_interpolater* gi, int batch, int nchannels, const float* in,
+                    const lmg_transform* transforms, const float* in_centers,
+                    const float* out_centers, float* out, void* stream);
+
+/* Reads back (synchronising `stream`) the status word that kernels of the last call that used
+ * `workspace` wrote: 0, or LMG_ERR_OUT_OF_RANGE / LMG_ERR_INVALID_ARGUMENT when an atom's type
+ * index was >= ntypes - the data-dependent checks of src/grid_maker.cpp:172 and :458-460,
+ * which the reference makes on the host while it loops over atoms. */
+int lmg_check_status(void* workspace, void* stream);
+
+const char* lmg_last_error(void);
+int lmg_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LMG_B200_H_ */

@@ -1,0 +1,464 @@
+// Host side of the C ABI declared in include/lmg_b200.h: argument checks, workspace carving,
+// pass splitting and kernel launches.  Nothing here computes results on the CPU.
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <random>
+#include <string>
+
+#include "../../include/lmg_b200.h"
+#include "lmg_launch.h"
+#include "lmg_misc.h"
+
+namespace {
+
+thread_local std::string g_err;
+std::default_random_engine g_engine;  // same engine type as libmolgrid::random_engine
+float g_radius_hint = 3.5f;           // largest radius*radius_scale*final_radius_multiple expected
+int g_precise = -1;                   // -1 auto, 0 fast density, 1 reference-order density
+
+int fail(int code, const std::string& msg) {
+  g_err = msg;
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(LMG_ERR_CUDA, std::string("CUDA Error: ") + what + ": " + cudaGetErrorString(e));
+}
+
+size_t align_up(size_t v, size_t a = 256) { return (v + a - 1) / a * a; }
+
+lmg::GMParams to_params(const lmg_gridmaker* g) {
+  lmg::GMParams p;
+  p.res = g->resolution;
+  p.half = (float)(g->dimension / 2.0);  // src/grid_maker.cpp:101
+  p.rscale = g->radius_scale;
+  p.G = g->gaussian_radius_multiple;
+  p.finalm = g->final_radius_multiple;
+  p.A = g->A; p.B = g->B; p.C = g->C; p.D = g->D; p.E = g->E;
+  p.dim = g->dim;
+  p.binary = g->binary;
+  p.rti = g->radii_type_indexed;
+  return p;
+}
+
+lmg::Xform to_xform(const lmg_transform* t) {
+  lmg::Xform X;
+  for (int i = 0; i < 4; i++) X.q[i] = t->q[i];
+  for (int i = 0; i < 3; i++) { X.c[i] = t->center[i]; X.t[i] = t->translate[i]; }
+  return X;
+}
+
+int regions_touched(int nvox, int s) { return (nvox + s - 2) / s + 1; }
+
+struct Geometry {
+  int nrx, nry, nrz, nreg, cap;
+};
+
+Geometry geometry(const lmg_gridmaker* g) {
+  Geometry G;
+  int d = (int)g->dim;
+  G.nrx = (d + lmg::REG_X - 1) / lmg::REG_X;
+  G.nry = (d + lmg::REG_Y - 1) / lmg::REG_Y;
+  G.nrz = (d + lmg::REG_Z - 1) / lmg::REG_Z;
+  G.nreg = G.nrx * G.nry * G.nrz;
+  int nvox = (int)std::floor(2.0f * g_radius_hint / g->resolution) + 2;
+  if (nvox < 2) nvox = 2;
+  long cap = (long)std::min(regions_touched(nvox, lmg::REG_X), G.nrx) *
+             std::min(regions_touched(nvox, lmg::REG_Y), G.nry) *
+             std::min(regions_touched(nvox, lmg::REG_Z), G.nrz);
+  G.cap = (int)std::min<long>(cap, 1 << 20);
+  return G;
+}
+
+// Scratch layout of one pass over nb examples.
+struct Layout {
+  size_t status, recs, chanp, cnt, bigcount, biglist, list, partial, total;
+  size_t per_example;
+  size_t M, listcap;
+};
+
+constexpr size_t STATUS_BYTES = 256;
+
+Layout layout(const lmg_gridmaker* g, int op, int nb, int N, int T, int vec) {
+  Layout L;
+  std::memset(&L, 0, sizeof L);
+  Geometry G = geometry(g);
+  size_t recs = align_up((size_t)N * sizeof(lmg::Rec));
+  size_t chanp = (vec && g->radii_type_indexed) ? align_up((size_t)T * sizeof(lmg::ChanParam)) : 0;
+  bool lists = op == LMG_OP_FORWARD || op == LMG_OP_BACKWARD_GRADIENTS;
+  L.M = lists ? (size_t)G.nreg * (vec ? 1 : T) : 0;
+  L.listcap = lists ? (size_t)N * G.cap : 0;
+  size_t cnt = align_up(L.M * 4);
+  size_t bigcount = lists ? 256 : 0;
+  size_t biglist = lists ? align_up((size_t)N * 4) : 0;
+  size_t list = align_up(L.listcap * 4);
+  size_t partial = (vec && (op == LMG_OP_BACKWARD || op == LMG_OP_BACKWARD_GRADIENTS))
+                       ? align_up((size_t)N * T * 3 * 4) : 0;
+  L.per_example = recs + chanp + cnt + bigcount + biglist + list + partial;
+  size_t o = STATUS_BYTES;
+  L.status = 0;
+  L.recs = o; o += recs * nb;
+  L.chanp = o; o += chanp * nb;
+  // counters and big-list counters are adjacent so that one memset clears both
+  L.cnt = o; o += cnt * nb;
+  L.bigcount = o; o += bigcount * nb;
+  L.biglist = o; o += biglist * nb;
+  L.list = o; o += list * nb;
+  L.partial = o; o += partial * nb;
+  L.total = o;
+  return L;
+}
+
+int check_common(const lmg_gridmaker* g, const lmg_atoms* a, const void* ws) {
+  if (g == nullptr || a == nullptr) return fail(LMG_ERR_INVALID_ARGUMENT, "null settings or atoms");
+  if (a->batch < 0 || a->max_atoms < 0 || a->ntypes <= 0)
+    return fail(LMG_ERR_INVALID_ARGUMENT, "negative batch/atom count or no types");
+  if (a->batch > 0 && a->max_atoms > 0 && (a->coords == nullptr || a->radii == nullptr))
+    return fail(LMG_ERR_INVALID_ARGUMENT, "coords/radii missing memory");
+  if ((a->type_index == nullptr) == (a->type_vector == nullptr) && a->batch > 0 && a->max_atoms > 0)
+    return fail(LMG_ERR_INVALID_ARGUMENT, "exactly one of type_index and type_vector must be given");
+  if (a->ntypes > 65535) return fail(LMG_ERR_INVALID_ARGUMENT, "more than 65535 types");
+  if (g->dim > 65535) return fail(LMG_ERR_OUT_OF_RANGE, "grid dimension above 65535 points");
+  // src/grid_maker.cpp:160-162, :443-445
+  if (a->type_index != nullptr && g->radii_type_indexed)
+    return fail(LMG_ERR_INVALID_ARGUMENT, "Type indexed radii not supported with index types.");
+  if (ws == nullptr) return fail(LMG_ERR_WORKSPACE, "workspace missing");
+  return LMG_OK;
+}
+
+void fill_emit(lmg::EmitArgs& E, const lmg_gridmaker* g, const lmg_atoms* a) {
+  std::memset(&E, 0, sizeof E);
+  E.gm = to_params(g);
+  E.N = a->max_atoms;
+  E.T = a->ntypes;
+  E.vec = a->type_vector != nullptr;
+  E.n_atoms = a->n_atoms;
+  E.coords = a->coords;
+  E.type_index = a->type_index;
+  E.type_vector = a->type_vector;
+  E.radii = a->radii;
+  E.centers = a->centers;
+  for (int i = 0; i < 3; i++) E.center_host[i] = a->center_host[i];
+  E.transforms = reinterpret_cast<const lmg::Xform*>(a->transforms);
+  if (a->transforms == nullptr && a->transform_host != nullptr) {
+    E.xform_host = to_xform(a->transform_host);
+    E.has_xform_host = 1;
+  }
+  E.check_types = 1;
+}
+
+void carve(lmg::EmitArgs& E, const Layout& L, char* ws, int nb) {
+  (void)nb;
+  E.status = reinterpret_cast<int*>(ws + L.status);
+  E.recs = reinterpret_cast<lmg::Rec*>(ws + L.recs);
+  E.chanp = reinterpret_cast<lmg::ChanParam*>(ws + L.chanp);
+  E.cnt = L.M ? reinterpret_cast<unsigned*>(ws + L.cnt) : nullptr;
+  E.bigcount = reinterpret_cast<unsigned*>(ws + L.bigcount);
+  E.biglist = reinterpret_cast<unsigned*>(ws + L.biglist);
+  E.list = reinterpret_cast<unsigned*>(ws + L.list);
+  E.M = (int)L.M;
+  E.listcap = L.listcap;
+}
+
+// number of examples per pass that fit the workspace; 0 if none
+int examples_per_pass(const Layout& one, size_t ws_bytes, int batch) {
+  if (ws_bytes < STATUS_BYTES + one.per_example) return 0;
+  size_t fit = (ws_bytes - STATUS_BYTES) / one.per_example;
+  return (int)std::min<size_t>(fit, (size_t)batch);
+}
+
+bool use_precise(const lmg_gridmaker* g) {
+  if (g_precise >= 0) return g_precise != 0;
+  // the fast exponential loses relative accuracy in proportion to the exponent's size (2*G^2)
+  return g->gaussian_radius_multiple > 2.0f;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* lmg_last_error(void) { return g_err.c_str(); }
+int lmg_version(void) { return 100; }
+
+void lmg_set_random_seed(unsigned seed) { g_engine.seed(seed); }
+
+// Tuning knobs (not part of the reference interface).
+void lmg_set_max_radius_hint(float angstroms) { g_radius_hint = angstroms > 0 ? angstroms : 3.5f; }
+void lmg_set_precise(int mode) { g_precise = mode; }
+
+int lmg_gridmaker_init(lmg_gridmaker* g, float res, float d, int bin, int rti, float rscale, float grm) {
+  if (g == nullptr) return fail(LMG_ERR_INVALID_ARGUMENT, "null settings");
+  g->resolution = res;
+  g->dimension = d;
+  g->radius_scale = rscale;
+  g->gaussian_radius_multiple = grm;
+  g->binary = bin != 0;
+  g->radii_type_indexed = rti != 0;
+  if (g->gaussian_radius_multiple < 0) {
+    // a negative multiple asks for a truncated Gaussian without the quadratic tail
+    g->gaussian_radius_multiple *= -1;
+    g->final_radius_multiple = g->gaussian_radius_multiple;
+  } else {
+    g->final_radius_multiple = (1 + 2 * grm * grm) / (2 * grm);
+  }
+  g->dim = (unsigned)(std::round(d / res) + 1);
+  // The reference evaluates these with the double-precision exponential of a float argument and
+  // keeps the caller's sign of grm; the products run in double and are rounded once to float.
+  double e = ::exp((double)(-2 * grm * grm));
+  g->A = (float)(e * 4 * grm * grm);
+  g->B = (float)(-e * (4 * grm + 8 * grm * grm * grm));
+  g->C = (float)(e * (4 * grm * grm * grm * grm + 4 * grm * grm + 1));
+  g->D = (float)(8 * grm * grm * ::exp(-2.0 * grm * grm));
+  g->E = (float)(-(4 * grm + 8 * grm * grm * grm) * e);
+  return LMG_OK;
+}
+
+int lmg_interpolater_init(lmg_interpolater* gi, float inres, float indim, float outres, float outdim) {
+  if (gi == nullptr) return fail(LMG_ERR_INVALID_ARGUMENT, "null settings");
+  gi->in_resolution = inres;
+  gi->in_dimension = indim;
+  gi->out_resolution = outres;
+  gi->out_dimension = outdim;
+  gi->in_dim = (unsigned)(std::round(indim / inres) + 1);
+  gi->out_dim = (unsigned)(std::round(outdim / outres) + 1);
+  return LMG_OK;
+}
+
+int lmg_transform_random(lmg_transform* t, const float center[3], float random_translate,
+                         int random_rotate) {
+  if (t == nullptr || center == nullptr) return fail(LMG_ERR_INVALID_ARGUMENT, "null transform");
+  for (int i = 0; i < 3; i++) t->center[i] = center[i];
+  // three translation draws are always consumed, then three more for a rotation
+  std::uniform_real_distribution<double> sym(-1.0, 1);
+  for (int i = 0; i < 3; i++) t->translate[i] = (float)(sym(g_engine) * random_translate);
+  t->q[0] = 1; t->q[1] = 0; t->q[2] = 0; t->q[3] = 0;
+  if (random_rotate) {
+    // uniform random unit quaternion from three uniform variates
+    std::uniform_real_distribution<double> unit(0, 1);
+    double u1 = unit(g_engine), u2 = unit(g_engine), u3 = unit(g_engine);
+    double s1 = std::sqrt(1 - u1), s2 = std::sqrt(u1);
+    t->q[0] = (float)(s1 * std::sin(2 * M_PI * u2));
+    t->q[1] = (float)(s1 * std::cos(2 * M_PI * u2));
+    t->q[2] = (float)(s2 * std::sin(2 * M_PI * u3));
+    t->q[3] = (float)(s2 * std::cos(2 * M_PI * u3));
+  }
+  return LMG_OK;
+}
+
+size_t lmg_workspace_bytes(const lmg_gridmaker* g, int op, int batch, int max_atoms, int ntypes,
+                           int vector_types) {
+  if (g == nullptr || batch < 0 || max_atoms < 0 || ntypes <= 0) return 0;
+  return layout(g, op, batch > 0 ? batch : 1, max_atoms, ntypes, vector_types).total;
+}
+
+int lmg_check_status(void* workspace, void* stream) {
+  if (workspace == nullptr) return fail(LMG_ERR_WORKSPACE, "workspace missing");
+  int st = 0;
+  cudaError_t e = cudaMemcpyAsync(&st, workspace, sizeof st, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return cuda_fail(e, "reading status");
+  if (st == 1) return fail(LMG_ERR_OUT_OF_RANGE, "Type index larger than allowed");
+  if (st == 2) return fail(LMG_ERR_INVALID_ARGUMENT, "Incorrect channel size for diff");
+  return LMG_OK;
+}
+
+int lmg_forward(const lmg_gridmaker* g, const lmg_atoms* a, float* out, void* workspace,
+                size_t workspace_bytes, void* stream) {
+  int rc = check_common(g, a, workspace);
+  if (rc) return rc;
+  if (a->batch == 0) return LMG_OK;
+  if (out == nullptr) return fail(LMG_ERR_INVALID_ARGUMENT, "Output grid not allocated");
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = (char*)workspace;
+  int vec = a->type_vector != nullptr;
+  size_t grid_elems = (size_t)a->ntypes * g->dim * g->dim * g->dim;
+  cudaError_t e = cudaMemsetAsync(ws, 0, STATUS_BYTES, st);
+  if (e != cudaSuccess) return cuda_fail(e, "clearing status");
+  if (a->max_atoms == 0 || g->dim == 0) {
+    e = cudaMemsetAsync(out, 0, grid_elems * a->batch * sizeof(float), st);
+    return e == cudaSuccess ? LMG_OK : cuda_fail(e, "zeroing output");
+  }
+  Layout one = layout(g, LMG_OP_FORWARD, 1, a->max_atoms, a->ntypes, vec);
+  int per_pass = examples_per_pass(one, workspace_bytes, a->batch);
+  if (per_pass == 0)
+    return fail(LMG_ERR_WORKSPACE, "workspace too small for one example: need " +
+                                       std::to_string(STATUS_BYTES + one.per_example) + " bytes");
+  Geometry G = geometry(g);
+  for (int b0 = 0; b0 < a->batch; b0 += per_pass) {
+    int nb = std::min(per_pass, a->batch - b0);
+    Layout L = layout(g, LMG_OP_FORWARD, nb, a->max_atoms, a->ntypes, vec);
+    lmg::EmitArgs E;
+    fill_emit(E, g, a);
+    carve(E, L, ws, nb);
+    E.b0 = b0; E.nb = nb;
+    E.round_types = 0;
+    E.nrx = G.nrx; E.nry = G.nry; E.nrz = G.nrz; E.cap = G.cap;
+    e = cudaMemsetAsync(ws + L.cnt, 0, L.biglist - L.cnt, st);
+    if (e != cudaSuccess) return cuda_fail(e, "clearing counters");
+    e = lmg::launch_emit(E, st);
+    if (e != cudaSuccess) return cuda_fail(e, "emit");
+    e = lmg::launch_scan_fill(E, st);
+    if (e != cudaSuccess) return cuda_fail(e, "scan/fill");
+    lmg::FwdArgs F;
+    std::memset(&F, 0, sizeof F);
+    F.gm = E.gm; F.b0 = b0; F.nb = nb; F.N = E.N; F.T = E.T;
+    F.vec = vec; F.precise = use_precise(g);
+    F.vec4_ok = (g->dim % 4 == 0) && ((uintptr_t)out % 16 == 0);
+    F.type_vector = a->type_vector;
+    F.centers = a->centers;
+    for (int i = 0; i < 3; i++) F.center_host[i] = a->center_host[i];
+    F.recs = E.recs; F.chanp = E.chanp; F.cnt = E.cnt; F.list = E.list;
+    F.bigcount = E.bigcount; F.biglist = E.biglist;
+    F.nrx = G.nrx; F.nry = G.nry; F.nrz = G.nrz; F.M = E.M; F.listcap = E.listcap;
+    F.out = out;
+    e = lmg::launch_forward(F, st);
+    if (e != cudaSuccess) return cuda_fail(e, "forward");
+  }
+  return LMG_OK;
+}
+
+static int backward_common(const lmg_gridmaker* g, const lmg_atoms* a, int op, int mode,
+                           const float* diff, const float* density, float* atom_gradients,
+                           float* type_gradients, float* relevance, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = (char*)workspace;
+  int vec = a->type_vector != nullptr;
+  cudaError_t e = cudaMemsetAsync(ws, 0, STATUS_BYTES, st);
+  if (e != cudaSuccess) return cuda_fail(e, "clearing status");
+  if (a->max_atoms == 0) return LMG_OK;
+  Layout one = layout(g, op, 1, a->max_atoms, a->ntypes, vec);
+  int per_pass = examples_per_pass(one, workspace_bytes, a->batch);
+  if (per_pass == 0)
+    return fail(LMG_ERR_WORKSPACE, "workspace too small for one example: need " +
+                                       std::to_string(STATUS_BYTES + one.per_example) + " bytes");
+  for (int b0 = 0; b0 < a->batch; b0 += per_pass) {
+    int nb = std::min(per_pass, a->batch - b0);
+    Layout L = layout(g, op, nb, a->max_atoms, a->ntypes, vec);
+    lmg::EmitArgs E;
+    fill_emit(E, g, a);
+    carve(E, L, ws, nb);
+    E.b0 = b0; E.nb = nb;
+    E.round_types = 1;
+    E.cnt = nullptr;
+    e = lmg::launch_emit(E, st);
+    if (e != cudaSuccess) return cuda_fail(e, "emit");
+    lmg::BwdArgs B;
+    std::memset(&B, 0, sizeof B);
+    B.gm = E.gm; B.b0 = b0; B.nb = nb; B.N = E.N; B.T = E.T;
+    B.type_vector = a->type_vector;
+    B.centers = a->centers;
+    for (int i = 0; i < 3; i++) B.center_host[i] = a->center_host[i];
+    B.recs = E.recs; B.chanp = E.chanp;
+    B.diff = diff; B.density = density;
+    B.atom_gradients = atom_gradients; B.type_gradients = type_gradients; B.relevance = relevance;
+    B.partial = reinterpret_cast<float*>(ws + L.partial);
+    e = lmg::launch_backward(B, mode, st);
+    if (e != cudaSuccess) return cuda_fail(e, "backward");
+  }
+  return LMG_OK;
+}
+
+int lmg_backward(const lmg_gridmaker* g, const lmg_atoms* a, const float* diff, float* atom_gradients,
+                 float* type_gradients, void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_common(g, a, workspace);
+  if (rc) return rc;
+  if (a->batch == 0) return LMG_OK;
+  int vec = a->type_vector != nullptr;
+  if (diff == nullptr || atom_gradients == nullptr)
+    return fail(LMG_ERR_INVALID_ARGUMENT, "diff/atom_gradients missing memory");
+  if (vec && type_gradients == nullptr)
+    return fail(LMG_ERR_INVALID_ARGUMENT, "type_gradients missing memory");
+  if (!vec && type_gradients != nullptr)
+    return fail(LMG_ERR_INVALID_ARGUMENT, "type_gradients given with index types");
+  return backward_common(g, a, LMG_OP_BACKWARD, vec ? 1 : 0, diff, nullptr, atom_gradients,
+                         type_gradients, nullptr, workspace, workspace_bytes, stream);
+}
+
+int lmg_backward_relevance(const lmg_gridmaker* g, const lmg_atoms* a, const float* density,
+                           const float* diff, float* relevance, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+  int rc = check_common(g, a, workspace);
+  if (rc) return rc;
+  if (a->batch == 0) return LMG_OK;
+  if (a->type_index == nullptr)
+    return fail(LMG_ERR_INVALID_ARGUMENT, "backward_relevance needs index types");
+  if (density == nullptr || diff == nullptr || relevance == nullptr)
+    return fail(LMG_ERR_INVALID_ARGUMENT, "density/diff/relevance missing memory");
+  return backward_common(g, a, LMG_OP_BACKWARD_RELEVANCE, 2, diff, density, nullptr, nullptr,
+                         relevance, workspace, workspace_bytes, stream);
+}
+
+int lmg_backward_gradients(const lmg_gridmaker* g, const lmg_atoms* a, const float* diff,
+                           const float* atom_gradients, const float* type_gradients, float* diffdiff,
+                           float* atom_diffdiff, float* type_diffdiff, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+  (void)diff; (void)atom_gradients; (void)type_gradients; (void)diffdiff; (void)atom_diffdiff;
+  (void)type_diffdiff; (void)workspace_bytes; (void)stream;
+  int rc = check_common(g, a, workspace);
+  if (rc) return rc;
+  if (g->binary) return fail(LMG_ERR_INVALID_ARGUMENT, "Binary densities not supported");
+  return fail(LMG_ERR_INVALID_ARGUMENT, "backward_gradients is not built yet");
+}
+
+static int transform_common(const lmg_transform* t, int n, const float* in, float* out, int dotranslate,
+                            bool forward, void* stream) {
+  if (t == nullptr) return fail(LMG_ERR_INVALID_ARGUMENT, "null transform");
+  if (n < 0) return fail(LMG_ERR_INVALID_ARGUMENT, "negative size");
+  if (n == 0) return LMG_OK;
+  // Transform::checkGrids, include/libmolgrid/transform.h:130-147
+  if (in == nullptr) return fail(LMG_ERR_INVALID_ARGUMENT, "Input coordinates missing memory");
+  if (out == nullptr) return fail(LMG_ERR_INVALID_ARGUMENT, "Output coordinates missing memory");
+  cudaError_t e = lmg::launch_transform(to_xform(t), n, in, out, dotranslate, forward, (cudaStream_t)stream);
+  return e == cudaSuccess ? LMG_OK : cuda_fail(e, "transform");
+}
+
+int lmg_transform_forward(const lmg_transform* t, int n, const float* in, float* out, int dotranslate,
+                          void* stream) {
+  return transform_common(t, n, in, out, dotranslate, true, stream);
+}
+
+int lmg_transform_backward(const lmg_transform* t, int n, const float* in, float* out, int dotranslate,
+                           void* stream) {
+  return transform_common(t, n, in, out, dotranslate, false, stream);
+}
+
+int lmg_interpolate(const lmg_interpolater* gi, int batch, int nchannels, const float* in,
+                    const lmg_transform* transforms, const float* in_centers, const float* out_centers,
+                    float* out, void* stream) {
+  if (gi == nullptr || transforms == nullptr || in_centers == nullptr || out_centers == nullptr)
+    return fail(LMG_ERR_INVALID_ARGUMENT, "null interpolater arguments");
+  if (batch < 0 || nchannels < 0) return fail(LMG_ERR_INVALID_ARGUMENT, "negative size");
+  // GridInterpolater::checkGrids, src/grid_interpolater.cpp:55-76
+  if (in == out && in != nullptr)
+    return fail(LMG_ERR_INVALID_ARGUMENT, "Input and output grid can not be the same in GridInterpolator.");
+  if (in == nullptr) return fail(LMG_ERR_INVALID_ARGUMENT, "Input grid not allocated");
+  if (out == nullptr) return fail(LMG_ERR_INVALID_ARGUMENT, "Output grid not allocated");
+  lmg::InterpArgs I;
+  I.in_res = gi->in_resolution;
+  I.out_res = gi->out_resolution;
+  I.in_half = (float)(gi->in_dimension / 2.0);
+  I.out_half = (float)(gi->out_dimension / 2.0);
+  I.in_dim = gi->in_dim;
+  I.out_dim = gi->out_dim;
+  I.K = nchannels;
+  I.in = in;
+  I.out = out;
+  for (int b0 = 0; b0 < batch; b0 += lmg::INTERP_MAX_EX) {
+    int nb = std::min(lmg::INTERP_MAX_EX, batch - b0);
+    I.b0 = b0;
+    for (int i = 0; i < nb; i++) {
+      I.ex[i].X = to_xform(&transforms[b0 + i]);
+      for (int k = 0; k < 3; k++) {
+        I.ex[i].in_center[k] = in_centers[(size_t)(b0 + i) * 3 + k];
+        I.ex[i].out_center[k] = out_centers[(size_t)(b0 + i) * 3 + k];
+      }
+    }
+    cudaError_t e = lmg::launch_interpolate(I, nb, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "interpolate");
+  }
+  return LMG_OK;
+}
+
+}  // extern "C"

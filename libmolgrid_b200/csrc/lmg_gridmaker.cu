@@ -1,0 +1,660 @@
+// sm_100a kernels for GridMaker forward / backward / backward_relevance.
+//
+// Pipeline of one forward pass over a batch:
+//   emit   : one thread per atom - fused Transform, exact footprint bounds and distance thresholds
+//            -> 64-byte atom record; counts the atom into every voxel region its footprint touches
+//   scan   : per-example exclusive scan of the (region, channel) counts
+//   fill   : writes atom indices into per-(region, channel) lists
+//   forward: one warp per 4x8x4-voxel region; per channel the warp turns its list into a per-lane
+//            bit mask of atoms whose footprint crosses the lane's z-column, then every lane walks
+//            its own mask and accumulates 4 voxels in registers; each output voxel is written
+//            exactly once with a 16-byte store (no memset, no read-modify-write of the grid).
+// Backward passes read the atom records directly: 8 lanes sweep one atom's footprint along z and
+// reduce with shuffles, so no global atomics are needed.
+#include "lmg_device.cuh"
+#include "lmg_launch.h"
+
+namespace lmg {
+
+// ---------------------------------------------------------------------------------------------
+// emit
+// ---------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ void region_box(const uint4& c, int& rx0, int& rx1, int& ry0, int& ry1,
+                                           int& rz0, int& rz1) {
+  unsigned lox = lo16(c.x), loy = hi16(c.x), hix = lo16(c.y), hiy = hi16(c.y);
+  unsigned loz = lo16(c.z), hiz = hi16(c.z);
+  rx0 = lox / REG_X; rx1 = (hix - 1) / REG_X;
+  ry0 = loy / REG_Y; ry1 = (hiy - 1) / REG_Y;
+  rz0 = loz / REG_Z; rz1 = (hiz - 1) / REG_Z;
+}
+
+// Type-indexed radii: constants of channel t of example b.
+__device__ __forceinline__ void make_chan_param(const GMParams& gm, float radius, ChanParam& cp) {
+  float ar = __fmul_rn(radius, gm.rscale);
+  float densityrad = __fmul_rn(ar, gm.finalm);
+  float Tcut = sqrt_threshold(densityrad);
+  float Tg = sqrt_threshold(__fmul_rn(ar, gm.G));
+  float Tbin = __fmul_rn(ar, ar);
+  bool ok = ar > 0.f;
+  float inv_ar = ok ? 1.f / ar : 0.f;
+  float inv_ar2 = ok ? 1.f / Tbin : 0.f;
+  if (!ok) { Tcut = -1.f; Tg = -1.f; Tbin = -1.f; }
+  cp.p = make_float4(inv_ar2, Tg, inv_ar, Tcut);
+  cp.q = make_float4(Tbin, ar, densityrad, fmaxf(Tcut, gm.binary ? Tbin : -1.f));
+}
+
+__global__ void __launch_bounds__(256) k_chan_params(EmitArgs A) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= A.nb * A.T) return;
+  int b = A.b0 + i / A.T, t = i % A.T;
+  ChanParam cp;
+  make_chan_param(A.gm, A.radii[(size_t)b * A.T + t], cp);
+  A.chanp[i] = cp;
+}
+
+// One thread per atom slot of the pass.
+__global__ void __launch_bounds__(256) k_emit(EmitArgs A) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= A.nb * A.N) return;
+  int bl = i / A.N, a = i - bl * A.N;
+  int b = A.b0 + bl;
+  const GMParams& gm = A.gm;
+
+  Rec r;
+  r.a = make_float4(0.f, 0.f, 0.f, -1.f);
+  r.b = make_float4(0.f, 0.f, -1.f, 0.f);
+  r.c = make_uint4(0u, 0u, 0u, 0u);
+  r.d = make_float4(-1.f, -1.f, 0.f, 0.f);
+
+  bool valid = A.n_atoms == nullptr || a < A.n_atoms[b];
+  int chan = 0;
+  if (valid && !A.vec) {
+    float tf = A.type_index[(size_t)b * A.N + a];
+    // forward takes floor (src/grid_maker.cpp:171), the backward passes round (:456, :698)
+    float tc = A.round_types ? roundf(tf) : floorf(tf);
+    if (!(tc >= 0.f)) {
+      valid = false;
+    } else if (tc >= (float)A.T) {
+      valid = false;
+      if (A.check_types) atomicMax(A.status, A.round_types ? 2 : 1);
+    } else {
+      chan = (int)tc;
+    }
+  }
+  if (valid) {
+    size_t ci = ((size_t)b * A.N + a) * 3;
+    float x = A.coords[ci], y = A.coords[ci + 1], z = A.coords[ci + 2];
+    if (A.transforms != nullptr || A.has_xform_host) {
+      Xform X = A.transforms != nullptr ? A.transforms[b] : A.xform_host;
+      float cn[4];
+      quat_conj_over_norm(X.q, cn);
+      xform_apply(X, cn, x, y, z, true);
+    }
+    float cx, cy, cz;
+    if (A.centers != nullptr) {
+      cx = A.centers[b * 3]; cy = A.centers[b * 3 + 1]; cz = A.centers[b * 3 + 2];
+    } else {
+      cx = A.center_host[0]; cy = A.center_host[1]; cz = A.center_host[2];
+    }
+    float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
+
+    float radius;
+    if (gm.rti) {
+      // footprint for binning = the largest channel radius of this example
+      radius = -CUDART_INF_F;
+      for (int t = 0; t < A.T; t++) radius = fmaxf(radius, A.radii[(size_t)b * A.T + t]);
+    } else {
+      radius = A.radii[(size_t)b * A.N + a];
+    }
+    ChanParam cp;
+    make_chan_param(gm, radius, cp);
+    float densityrad = cp.q.z;
+    // binary occupancy extends to ar, which exceeds densityrad only when final_radius_multiple < 1;
+    // the reference still clips it to the densityrad footprint, and so do the bounds below
+    unsigned lox, hix, loy, hiy, loz, hiz;
+    bounds_1d(ox, x, densityrad, gm.res, gm.dim, lox, hix);
+    bounds_1d(oy, y, densityrad, gm.res, gm.dim, loy, hiy);
+    bounds_1d(oz, z, densityrad, gm.res, gm.dim, loz, hiz);
+    bool any = cp.q.y > 0.f && hix > lox && hiy > loy && hiz > loz;
+    if (any) {
+      r.a = make_float4(x, y, z, cp.q.w);
+      r.b = make_float4(1.f, cp.p.x, cp.p.y, cp.p.z);
+      r.c = make_uint4(lox | (loy << 16), hix | (hiy << 16), loz | (hiz << 16),
+                       (unsigned)chan | (REC_VALID << 16));
+      r.d = make_float4(cp.p.w, cp.q.x, cp.q.y, cp.q.z);
+    }
+    valid = any;
+  }
+
+  if (valid && A.cnt != nullptr) {
+    int rx0, rx1, ry0, ry1, rz0, rz1;
+    region_box(r.c, rx0, rx1, ry0, ry1, rz0, rz1);
+    int nslots = (rx1 - rx0 + 1) * (ry1 - ry0 + 1) * (rz1 - rz0 + 1);
+    if (nslots > A.cap) {
+      r.c.w |= REC_BIG << 16;
+      unsigned p = atomicAdd(&A.bigcount[bl], 1u);
+      A.biglist[(size_t)bl * A.N + p] = (unsigned)a;
+    } else {
+      unsigned* cnt = A.cnt + (size_t)bl * A.M;
+      int tb = A.vec ? 1 : A.T;
+      int ch = A.vec ? 0 : chan;
+      for (int rx = rx0; rx <= rx1; rx++)
+        for (int ry = ry0; ry <= ry1; ry++)
+          for (int rz = rz0; rz <= rz1; rz++) {
+            int reg = (rx * A.nry + ry) * A.nrz + rz;
+            atomicAdd(&cnt[(size_t)reg * tb + ch], 1u);
+          }
+    }
+  }
+  A.recs[i] = r;
+}
+
+// ---------------------------------------------------------------------------------------------
+// scan: in-place exclusive prefix sum of the M counters of each example
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) k_scan(unsigned* cnt, int M) {
+  __shared__ unsigned warp_tot[32];
+  __shared__ unsigned carry_s;
+  unsigned* c = cnt + (size_t)blockIdx.x * M;
+  int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  if (tid == 0) carry_s = 0;
+  __syncthreads();
+  const int per = 8;
+  for (int base = 0; base < M; base += 1024 * per) {
+    unsigned v[per];
+    unsigned sum = 0;
+    int i0 = base + tid * per;
+#pragma unroll
+    for (int k = 0; k < per; k++) {
+      v[k] = (i0 + k < M) ? c[i0 + k] : 0u;
+      sum += v[k];
+    }
+    unsigned inc = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      unsigned n = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += n;
+    }
+    if (lane == 31) warp_tot[wid] = inc;
+    __syncthreads();
+    if (wid == 0) {
+      unsigned w = warp_tot[lane];
+      unsigned winc = w;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        unsigned n = __shfl_up_sync(0xffffffffu, winc, o);
+        if (lane >= o) winc += n;
+      }
+      warp_tot[lane] = winc - w;  // exclusive
+    }
+    __syncthreads();
+    unsigned carry = carry_s;
+    unsigned excl = carry + warp_tot[wid] + inc - sum;
+#pragma unroll
+    for (int k = 0; k < per; k++) {
+      if (i0 + k < M) c[i0 + k] = excl;
+      excl += v[k];
+    }
+    __syncthreads();
+    if (tid == 1023) carry_s = excl;
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// fill: after this kernel cnt[bin] holds the END offset of the bin (begin = end of the bin before)
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_fill(EmitArgs A) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= A.nb * A.N) return;
+  int bl = i / A.N, a = i - bl * A.N;
+  uint4 c = A.recs[i].c;
+  unsigned flags = c.w >> 16;
+  if (!(flags & REC_VALID) || (flags & REC_BIG)) return;
+  int rx0, rx1, ry0, ry1, rz0, rz1;
+  region_box(c, rx0, rx1, ry0, ry1, rz0, rz1);
+  unsigned* cnt = A.cnt + (size_t)bl * A.M;
+  unsigned* list = A.list + (size_t)bl * A.listcap;
+  int tb = A.vec ? 1 : A.T;
+  int ch = A.vec ? 0 : (int)(c.w & 0xffffu);
+  for (int rx = rx0; rx <= rx1; rx++)
+    for (int ry = ry0; ry <= ry1; ry++)
+      for (int rz = rz0; rz <= rz1; rz++) {
+        int reg = (rx * A.nry + ry) * A.nrz + rz;
+        unsigned p = atomicAdd(&cnt[(size_t)reg * tb + ch], 1u);
+        list[p] = (unsigned)a;
+      }
+}
+
+// ---------------------------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------------------------
+
+constexpr int FWD_WARPS = 4;
+
+// staged candidate in shared memory (48 bytes): what the column test and the voxel loop read
+struct __align__(16) Cand {
+  float4 a;  // x, y, z, Tcull
+  float4 b;  // w, inv_ar2 (or ar when PRECISE), Tg, Tcut
+  uint4 c;   // lo.x|lo.y<<16, hi.x|hi.y<<16, lo.z|hi.z<<16, unused
+};
+
+template <bool BINARY, bool PRECISE, bool VEC>
+__global__ void __launch_bounds__(FWD_WARPS * 32) k_forward(FwdArgs F) {
+  __shared__ Cand cand_s[FWD_WARPS][32];
+  const GMParams& gm = F.gm;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int reg = blockIdx.x * FWD_WARPS + wid;
+  int bl = blockIdx.y;
+  int b = F.b0 + bl;
+  int nreg = F.nrx * F.nry * F.nrz;
+  if (reg >= nreg) return;
+  Cand* cs = cand_s[wid];
+
+  int rz = reg % F.nrz;
+  int ry = (reg / F.nrz) % F.nry;
+  int rx = reg / (F.nrz * F.nry);
+  unsigned vx = rx * REG_X + (lane >> 3), vy = ry * REG_Y + (lane & 7), vz0 = rz * REG_Z;
+  bool col_ok = vx < gm.dim && vy < gm.dim;
+
+  float cx, cy, cz;
+  if (F.centers != nullptr) {
+    cx = F.centers[b * 3]; cy = F.centers[b * 3 + 1]; cz = F.centers[b * 3 + 2];
+  } else {
+    cx = F.center_host[0]; cy = F.center_host[1]; cz = F.center_host[2];
+  }
+  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
+  float gx = voxel_coord(ox, vx, gm.res), gy = voxel_coord(oy, vy, gm.res);
+  float gz[REG_Z];
+#pragma unroll
+  for (int k = 0; k < REG_Z; k++) gz[k] = voxel_coord(oz, vz0 + k, gm.res);
+
+  const Rec* recs = F.recs + (size_t)bl * F.N;
+  const unsigned* cnt = F.cnt + (size_t)bl * F.M;
+  const unsigned* list = F.list + (size_t)bl * F.listcap;
+  unsigned nbig = F.bigcount[bl];
+  const unsigned* biglist = F.biglist + (size_t)bl * F.N;
+  size_t dim = gm.dim;
+  float* outb = F.out + (size_t)b * F.T * dim * dim * dim;
+  bool vec4_ok = F.vec4_ok;
+
+  // VEC: one list per region shared by all channels; otherwise one list per (region, channel)
+  unsigned vbeg = 0, vend = 0;
+  if (VEC) {
+    vbeg = reg == 0 ? 0u : cnt[reg - 1];
+    vend = cnt[reg];
+  }
+
+  for (int c0 = 0; c0 < F.T; c0 += 32) {
+    unsigned my_end = 0, my_beg = 0;
+    if (!VEC) {
+      int c = c0 + lane;
+      if (c < F.T) {
+        size_t bin = (size_t)reg * F.T + c;
+        my_end = cnt[bin];
+        my_beg = bin == 0 ? 0u : cnt[bin - 1];
+      }
+    }
+    int cn = min(32, F.T - c0);
+    for (int cc = 0; cc < cn; cc++) {
+      int chan = c0 + cc;
+      unsigned beg, end;
+      if (VEC) {
+        beg = vbeg; end = vend;
+      } else {
+        beg = __shfl_sync(0xffffffffu, my_beg, cc);
+        end = __shfl_sync(0xffffffffu, my_end, cc);
+      }
+      float acc[REG_Z];
+#pragma unroll
+      for (int k = 0; k < REG_Z; k++) acc[k] = 0.f;
+
+      ChanParam cp;
+      if (VEC && gm.rti) cp = F.chanp[(size_t)bl * F.T + chan];
+
+      unsigned total = (end - beg) + nbig;
+      for (unsigned base = 0; base < total; base += 32) {
+        unsigned n = min(32u, total - base);
+        // ---- stage up to 32 candidates ----
+        bool have = false;
+        if (lane < n) {
+          unsigned e = base + lane;
+          unsigned ai = e < (end - beg) ? list[beg + e] : biglist[e - (end - beg)];
+          const Rec* rp = recs + ai;
+          float4 ra = rp->a, rb = rp->b;
+          uint4 rc = rp->c;
+          Cand cd;
+          bool use = true;
+          if (!VEC) {
+            // entries from the big list are not sorted by channel
+            if (e >= (end - beg)) use = (int)(rc.w & 0xffffu) == chan;
+            float Tcut = rp->d.x;
+            cd.a = ra;
+            cd.b = make_float4(1.f, PRECISE ? rp->d.z : rb.y, rb.z, Tcut);
+            if (BINARY) cd.b.w = rp->d.y;  // Tbin
+            cd.c = rc;
+          } else {
+            float w = F.type_vector[((size_t)b * F.N + ai) * F.T + chan];
+            use = w != 0.f;
+            if (!gm.rti) {
+              float Tcut = rp->d.x;
+              cd.a = ra;
+              cd.b = make_float4(w, PRECISE ? rp->d.z : rb.y, rb.z, BINARY ? rp->d.y : Tcut);
+              cd.c = rc;
+            } else {
+              // per-channel radius: footprint and thresholds of this (atom, channel)
+              unsigned lox, hix, loy, hiy, loz, hiz;
+              bounds_1d(ox, ra.x, cp.q.z, gm.res, gm.dim, lox, hix);
+              bounds_1d(oy, ra.y, cp.q.z, gm.res, gm.dim, loy, hiy);
+              bounds_1d(oz, ra.z, cp.q.z, gm.res, gm.dim, loz, hiz);
+              cd.a = make_float4(ra.x, ra.y, ra.z, cp.q.w);
+              cd.b = make_float4(w, PRECISE ? cp.q.y : cp.p.x, cp.p.y, BINARY ? cp.q.x : cp.p.w);
+              cd.c = make_uint4(lox | (loy << 16), hix | (hiy << 16), loz | (hiz << 16), 0u);
+              use = use && cp.q.y > 0.f;
+            }
+          }
+          if (!use) cd.a.w = -1.f;  // nothing passes a negative threshold
+          cs[lane] = cd;
+          have = use;
+        }
+        __syncwarp();
+        // ---- column test: bit i set when candidate i can touch this lane's z-column ----
+        unsigned mask = 0;
+        if (__any_sync(0xffffffffu, have)) {
+          for (unsigned i = 0; i < n; i++) {
+            float4 a = cs[i].a;
+            uint2 bb = *reinterpret_cast<const uint2*>(&cs[i].c);
+            float dx = __fsub_rn(gx, a.x), dy = __fsub_rn(gy, a.y);
+            float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
+            bool p = dxy2 <= a.w;
+            p = p && (vx - lo16(bb.x)) < (lo16(bb.y) - lo16(bb.x));
+            p = p && (vy - hi16(bb.x)) < (hi16(bb.y) - hi16(bb.x));
+            mask |= (p ? 1u : 0u) << i;
+          }
+        }
+        if (!col_ok) mask = 0;
+        // ---- each lane walks its own candidates ----
+        while (mask) {
+          int i = __ffs(mask) - 1;
+          mask &= mask - 1;
+          float4 a = cs[i].a, bq = cs[i].b;
+          unsigned bz = cs[i].c.z;
+          float dx = __fsub_rn(gx, a.x), dy = __fsub_rn(gy, a.y);
+          float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
+          unsigned loz = lo16(bz), nz = hi16(bz) - loz;
+#pragma unroll
+          for (int k = 0; k < REG_Z; k++) {
+            float dz = __fsub_rn(gz[k], a.z);
+            float rsq = __fadd_rn(dxy2, __fmul_rn(dz, dz));
+            bool inz = (vz0 + k - loz) < nz;
+            if (BINARY) {
+              bool hit = inz && rsq < bq.w;
+              if (VEC) {
+                if (hit) acc[k] = __fadd_rn(acc[k], bq.x);
+              } else {
+                if (hit) acc[k] = 1.f;
+              }
+            } else {
+              float v = PRECISE ? density_precise(rsq, bq.y, bq.z, bq.w, gm.A, gm.B, gm.C)
+                                : density_fast(rsq, bq.y, bq.z, bq.w, gm.A, gm.B, gm.C);
+              if (PRECISE) {
+                if (inz) acc[k] = __fadd_rn(acc[k], __fmul_rn(v, bq.x));
+              } else {
+                acc[k] = fmaf(inz ? v : 0.f, bq.x, acc[k]);
+              }
+            }
+          }
+        }
+        __syncwarp();
+      }
+
+      // ---- write this channel's 4 voxels ----
+      if (col_ok) {
+        float* o = outb + (((size_t)chan * dim + vx) * dim + vy) * dim + vz0;
+        if (vec4_ok) {
+          if (vz0 + REG_Z <= gm.dim) {
+            __stcs(reinterpret_cast<float4*>(o), make_float4(acc[0], acc[1], acc[2], acc[3]));
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < REG_Z; k++)
+            if (vz0 + k < gm.dim) o[k] = acc[k];
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward: 8 lanes per work item sweep the footprint along z
+// ---------------------------------------------------------------------------------------------
+
+struct ItemParams {
+  float x, y, z;
+  float inv_ar2, inv_ar, Tg, Tcut, Tbin, w;
+  unsigned lox, hix, loy, hiy, loz, hiz;
+  int chan;
+  bool valid;
+};
+
+// Loads the constants of work item `item` (an atom, or an (atom, channel) pair with VEC).
+template <bool VEC>
+__device__ __forceinline__ ItemParams load_item(const BwdArgs& G, int bl, int b, int item,
+                                                float ox, float oy, float oz) {
+  ItemParams P;
+  int ai = VEC ? item / G.T : item;
+  const Rec* rp = G.recs + (size_t)bl * G.N + ai;
+  float4 ra = rp->a, rb = rp->b, rd = rp->d;
+  uint4 rc = rp->c;
+  P.valid = ((rc.w >> 16) & REC_VALID) != 0;
+  P.x = ra.x; P.y = ra.y; P.z = ra.z;
+  P.chan = VEC ? item - ai * G.T : (int)(rc.w & 0xffffu);
+  P.w = 1.f;
+  if (VEC) P.w = G.type_vector[((size_t)b * G.N + ai) * G.T + P.chan];
+  if (VEC && G.gm.rti) {
+    ChanParam cp = G.chanp[(size_t)bl * G.T + P.chan];
+    P.inv_ar2 = cp.p.x; P.Tg = cp.p.y; P.inv_ar = cp.p.z; P.Tcut = cp.p.w; P.Tbin = cp.q.x;
+    bounds_1d(ox, P.x, cp.q.z, G.gm.res, G.gm.dim, P.lox, P.hix);
+    bounds_1d(oy, P.y, cp.q.z, G.gm.res, G.gm.dim, P.loy, P.hiy);
+    bounds_1d(oz, P.z, cp.q.z, G.gm.res, G.gm.dim, P.loz, P.hiz);
+    P.valid = P.valid && cp.q.y > 0.f;
+  } else {
+    P.inv_ar2 = rb.y; P.Tg = rb.z; P.inv_ar = rb.w; P.Tcut = rd.x; P.Tbin = rd.y;
+    P.lox = lo16(rc.x); P.loy = hi16(rc.x); P.hix = lo16(rc.y); P.hiy = hi16(rc.y);
+    P.loz = lo16(rc.z); P.hiz = hi16(rc.z);
+  }
+  return P;
+}
+
+constexpr int BWD_THREADS = 128;
+
+// MODE 0: atom gradient (index types)          -> atom_gradients[b][a][3]
+// MODE 1: atom + type gradient (vector types)  -> partial[b][a][t][3], type_gradients[b][a][t]
+// MODE 2: relevance (index types)              -> relevance[b][a]
+template <int MODE, bool BINARY>
+__global__ void __launch_bounds__(BWD_THREADS) k_backward(BwdArgs G) {
+  constexpr bool VEC = MODE == 1;
+  const GMParams& gm = G.gm;
+  int lane = threadIdx.x & 31, sub = lane & 7;
+  int group = (blockIdx.x * BWD_THREADS + threadIdx.x) >> 3;
+  int items_per_ex = VEC ? G.N * G.T : G.N;
+  bool in_range = group < G.nb * items_per_ex;
+  int bl = in_range ? group / items_per_ex : 0;
+  int item = in_range ? group - bl * items_per_ex : 0;
+  int b = G.b0 + bl;
+
+  float cx, cy, cz;
+  if (G.centers != nullptr) {
+    cx = G.centers[b * 3]; cy = G.centers[b * 3 + 1]; cz = G.centers[b * 3 + 2];
+  } else {
+    cx = G.center_host[0]; cy = G.center_host[1]; cz = G.center_host[2];
+  }
+  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
+
+  ItemParams P = load_item<VEC>(G, bl, b, item, ox, oy, oz);
+  if (!in_range) P.valid = false;
+
+  size_t dim = gm.dim;
+  size_t chan_off = ((size_t)b * G.T + P.chan) * dim * dim * dim;
+  const float* diff = G.diff + chan_off;
+  const float* dens = MODE == 2 ? G.density + chan_off : nullptr;
+
+  float agx = 0.f, agy = 0.f, agz = 0.f, tg = 0.f;
+  // vector types skip the atom gradient of zero-weight channels (src/grid_maker.cpp:510-515) but
+  // still produce their type gradient
+  bool want_ag = MODE == 0 || (MODE == 1 && P.w != 0.f);
+  float Tcull = MODE == 0 ? P.Tcut : fmaxf(P.Tcut, BINARY ? P.Tbin : -1.f);
+  const float k4 = -4.f * P.inv_ar2, kD = gm.D * P.inv_ar2, kE = gm.E * P.inv_ar;
+
+  if (P.valid) {
+    for (unsigned x = P.lox; x < P.hix; x++) {
+      float dx = __fsub_rn(voxel_coord(ox, x, gm.res), P.x);
+      float dx2 = __fmul_rn(dx, dx);
+      for (unsigned y = P.loy; y < P.hiy; y++) {
+        float dy = __fsub_rn(voxel_coord(oy, y, gm.res), P.y);
+        float dxy2 = __fadd_rn(dx2, __fmul_rn(dy, dy));
+        if (!(dxy2 <= Tcull)) continue;
+        const float* row = diff + (x * dim + y) * dim;
+        for (unsigned z = P.loz + sub; z < P.hiz; z += 8) {
+          float dz = __fsub_rn(voxel_coord(oz, z, gm.res), P.z);
+          float rsq = __fadd_rn(dxy2, __fmul_rn(dz, dz));
+          float dv = __ldg(row + z);
+          if (MODE != 2) {
+            if (want_ag && rsq <= P.Tcut && rsq > 0.f) {
+              // (d density / d dist) / dist, src/grid_maker.cu:881-896
+              float s = rsq <= P.Tg ? k4 * ex2_approx(rsq * P.inv_ar2 * NEG2_LOG2E)
+                                    : fmaf(kE, rsqrt_approx(rsq), kD);
+              float f = -(s * dv);
+              agx = fmaf(f, dx, agx);
+              agy = fmaf(f, dy, agy);
+              agz = fmaf(f, dz, agz);
+            }
+          }
+          if (MODE != 0) {
+            float v = BINARY ? (rsq < P.Tbin ? 1.f : 0.f)
+                             : density_fast(rsq, P.inv_ar2, P.Tg, P.Tcut, gm.A, gm.B, gm.C);
+            if (MODE == 1) {
+              tg = fmaf(v, dv, tg);
+            } else if (v > 0.f) {
+              float de = __ldg(dens + (x * dim + y) * dim + z);
+              if (de > 0.f) tg += __fdividef(dv * v, de);
+            }
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 4; o >= 1; o >>= 1) {
+    if (MODE != 2) {
+      agx += __shfl_xor_sync(0xffffffffu, agx, o);
+      agy += __shfl_xor_sync(0xffffffffu, agy, o);
+      agz += __shfl_xor_sync(0xffffffffu, agz, o);
+    }
+    if (MODE != 0) tg += __shfl_xor_sync(0xffffffffu, tg, o);
+  }
+  if (in_range && sub == 0) {
+    size_t ai = (size_t)b * G.N + (VEC ? item / G.T : item);
+    if (MODE == 0) {
+      G.atom_gradients[ai * 3] = agx;
+      G.atom_gradients[ai * 3 + 1] = agy;
+      G.atom_gradients[ai * 3 + 2] = agz;
+    } else if (MODE == 1) {
+      size_t pi = (size_t)bl * G.N * G.T + item;
+      G.partial[pi * 3] = agx;
+      G.partial[pi * 3 + 1] = agy;
+      G.partial[pi * 3 + 2] = agz;
+      G.type_gradients[ai * G.T + P.chan] = tg;
+    } else {
+      G.relevance[ai] = tg;
+    }
+  }
+}
+
+// atom_gradients[a] = sum over channels in ascending order of partial[a][t] * w[a][t] for w != 0
+// (src/grid_maker.cpp:508-515)
+__global__ void __launch_bounds__(256) k_reduce_types(BwdArgs G) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= G.nb * G.N) return;
+  int bl = i / G.N, a = i - bl * G.N;
+  int b = G.b0 + bl;
+  const float* w = G.type_vector + ((size_t)b * G.N + a) * G.T;
+  const float* p = G.partial + (size_t)i * G.T * 3;
+  float gx = 0.f, gy = 0.f, gz = 0.f;
+  for (int t = 0; t < G.T; t++) {
+    float wt = w[t];
+    if (wt != 0.f) {
+      gx = __fadd_rn(gx, __fmul_rn(p[t * 3], wt));
+      gy = __fadd_rn(gy, __fmul_rn(p[t * 3 + 1], wt));
+      gz = __fadd_rn(gz, __fmul_rn(p[t * 3 + 2], wt));
+    }
+  }
+  size_t ai = (size_t)b * G.N + a;
+  G.atom_gradients[ai * 3] = gx;
+  G.atom_gradients[ai * 3 + 1] = gy;
+  G.atom_gradients[ai * 3 + 2] = gz;
+}
+
+// ---------------------------------------------------------------------------------------------
+// launchers
+// ---------------------------------------------------------------------------------------------
+
+cudaError_t launch_emit(const EmitArgs& A, cudaStream_t st) {
+  if (A.gm.rti && A.vec) {
+    int n = A.nb * A.T;
+    k_chan_params<<<(n + 255) / 256, 256, 0, st>>>(A);
+  }
+  int n = A.nb * A.N;
+  k_emit<<<(n + 255) / 256, 256, 0, st>>>(A);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_scan_fill(const EmitArgs& A, cudaStream_t st) {
+  k_scan<<<A.nb, 1024, 0, st>>>(A.cnt, A.M);
+  int n = A.nb * A.N;
+  k_fill<<<(n + 255) / 256, 256, 0, st>>>(A);
+  return cudaGetLastError();
+}
+
+template <bool BINARY, bool PRECISE>
+static void launch_forward_t(const FwdArgs& F, dim3 grid, cudaStream_t st) {
+  if (F.vec)
+    k_forward<BINARY, PRECISE, true><<<grid, FWD_WARPS * 32, 0, st>>>(F);
+  else
+    k_forward<BINARY, PRECISE, false><<<grid, FWD_WARPS * 32, 0, st>>>(F);
+}
+
+cudaError_t launch_forward(const FwdArgs& F, cudaStream_t st) {
+  int nreg = F.nrx * F.nry * F.nrz;
+  dim3 grid((nreg + FWD_WARPS - 1) / FWD_WARPS, F.nb);
+  if (F.gm.binary)
+    launch_forward_t<true, false>(F, grid, st);
+  else if (F.precise)
+    launch_forward_t<false, true>(F, grid, st);
+  else
+    launch_forward_t<false, false>(F, grid, st);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st) {
+  long items = (long)G.nb * G.N * (mode == 1 ? G.T : 1);
+  long threads = items * 8;
+  unsigned blocks = (unsigned)((threads + BWD_THREADS - 1) / BWD_THREADS);
+  if (blocks == 0) return cudaSuccess;
+  bool bin = G.gm.binary != 0;
+  if (mode == 0) {
+    k_backward<0, false><<<blocks, BWD_THREADS, 0, st>>>(G);
+  } else if (mode == 1) {
+    if (bin) k_backward<1, true><<<blocks, BWD_THREADS, 0, st>>>(G);
+    else k_backward<1, false><<<blocks, BWD_THREADS, 0, st>>>(G);
+    int n = G.nb * G.N;
+    k_reduce_types<<<(n + 255) / 256, 256, 0, st>>>(G);
+  } else {
+    if (bin) k_backward<2, true><<<blocks, BWD_THREADS, 0, st>>>(G);
+    else k_backward<2, false><<<blocks, BWD_THREADS, 0, st>>>(G);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace lmg

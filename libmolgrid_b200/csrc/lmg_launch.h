@@ -1,0 +1,78 @@
+// Argument blocks passed by value to the gridding kernels, and their host-side launchers.
+#pragma once
+#include <cuda_runtime.h>
+
+#include "lmg_device.cuh"
+
+namespace lmg {
+
+// A pass covers examples [b0, b0+nb) of the caller's batch; scratch arrays are indexed by the
+// example's position in the pass (bl = b - b0), caller arrays by b.
+struct EmitArgs {
+  GMParams gm;
+  int b0, nb, N, T;
+  int vec;          // type vectors (1) or type indices (0)
+  int round_types;  // 1: round the type index (backward passes), 0: floor (forward)
+  int check_types;  // report type >= T through the status word
+  const int* n_atoms;
+  const float* coords;
+  const float* type_index;
+  const float* type_vector;
+  const float* radii;
+  const float* centers;
+  float center_host[3];
+  const Xform* transforms;
+  Xform xform_host;
+  int has_xform_host;
+  // scratch
+  Rec* recs;          // [nb][N]
+  ChanParam* chanp;   // [nb][T], type-indexed radii only
+  unsigned* cnt;      // [nb][M] region(/channel) counters, NULL when no lists are needed
+  unsigned* list;     // [nb][listcap]
+  unsigned* bigcount; // [nb]
+  unsigned* biglist;  // [nb][N]
+  int* status;
+  int nrx, nry, nrz, M, cap;
+  size_t listcap;
+};
+
+struct FwdArgs {
+  GMParams gm;
+  int b0, nb, N, T;
+  int vec, precise, vec4_ok;
+  const float* type_vector;
+  const float* centers;
+  float center_host[3];
+  const Rec* recs;
+  const ChanParam* chanp;
+  const unsigned* cnt;
+  const unsigned* list;
+  const unsigned* bigcount;
+  const unsigned* biglist;
+  int nrx, nry, nrz, M;
+  size_t listcap;
+  float* out;
+};
+
+struct BwdArgs {
+  GMParams gm;
+  int b0, nb, N, T;
+  const float* type_vector;
+  const float* centers;
+  float center_host[3];
+  const Rec* recs;
+  const ChanParam* chanp;
+  const float* diff;
+  const float* density;
+  float* atom_gradients;
+  float* type_gradients;
+  float* relevance;
+  float* partial;  // [nb][N][T][3] scratch, vector types
+};
+
+cudaError_t launch_emit(const EmitArgs& A, cudaStream_t st);
+cudaError_t launch_scan_fill(const EmitArgs& A, cudaStream_t st);
+cudaError_t launch_forward(const FwdArgs& F, cudaStream_t st);
+cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st);
+
+}  // namespace lmg

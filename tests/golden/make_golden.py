@@ -1,0 +1,98 @@
+"""Generates tests/golden/golden.npz from the reference's own CPU code.
+
+Needs oracle/_ref/liblmg_ref.so (``make -C oracle ref``, which compiles the reference's sources
+where the reference tree is mounted).  The stored arrays are the reference's outputs on the small
+seeded cases of :func:`golden_cases`; tests compare the C restatement (on CPU) and the CUDA path
+(on a GPU) with them, so the vectors travel to machines that do not have the reference tree.
+
+    python tests/golden/make_golden.py
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+from tests import cases  # noqa: E402
+
+OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden.npz")
+
+# name -> GridMaker settings
+SETTINGS = {
+    "g1": dict(resolution=0.5, dimension=5.5),
+    "g1bin": dict(resolution=0.5, dimension=5.5, binary=True),
+    "g3": dict(resolution=0.25, dimension=3.75, radius_scale=0.5, gaussian_radius_multiple=3.0),
+    "gneg": dict(resolution=0.5, dimension=5.0, radius_scale=1.2, gaussian_radius_multiple=-2.0),
+}
+CENTER = (0.1, -0.2, 0.3)
+NT = 4
+
+
+def golden_inputs(name):
+    """Inputs of one golden case, regenerated identically by the tests."""
+    kw = SETTINGS[name]
+    ext = kw["dimension"] / 2 + 1
+    seed = sorted(SETTINGS).index(name) + 50
+    coords, types, radii = cases.index_case(seed, 40, NT, ext, rmin=0.8, rmax=1.8)
+    vcoords, tv, vradii = cases.vector_case(seed + 100, 30, NT, ext, rti=False)
+    _, _, tradii = cases.vector_case(seed + 100, 30, NT, ext, rti=True)
+    rng = np.random.default_rng(seed + 200)
+    dim = int(np.round(np.float32(kw["dimension"]) / np.float32(kw["resolution"])) + 1)
+    diff = rng.normal(size=(NT, dim, dim, dim)).astype(np.float32)
+    return dict(coords=coords, types=types, radii=radii, vcoords=vcoords, tv=tv, vradii=vradii,
+                tradii=tradii, diff=diff)
+
+
+def transform_inputs():
+    rng = np.random.default_rng(77)
+    q = rng.normal(size=4).astype(np.float32)
+    q2 = cases.random_quaternion(rng, 1)[0]
+    c = rng.uniform(-2, 2, 3).astype(np.float32)
+    t = rng.uniform(-2, 2, 3).astype(np.float32)
+    pts = (rng.normal(size=(64, 3)) * 6).astype(np.float32)
+    grid = rng.uniform(size=(3, 16, 16, 16)).astype(np.float32)
+    return q, q2, c, t, pts, grid
+
+
+def main():
+    from oracle.oracle import CpuOracle
+    R = CpuOracle("ref")
+    out = {}
+    for name, kw in SETTINGS.items():
+        gm = R.gm(**kw)
+        out[name + "/consts"] = R.consts(gm)
+        x = golden_inputs(name)
+        dens = R.forward_index(gm, CENTER, x["coords"], x["types"], x["radii"], NT)
+        out[name + "/forward_index"] = dens
+        out[name + "/backward_index"] = R.backward_index(gm, CENTER, x["coords"], x["types"], x["radii"], x["diff"])
+        out[name + "/relevance"] = R.backward_relevance(gm, CENTER, x["coords"], x["types"], x["radii"], dens,
+                                                        x["diff"])
+        for rti in (0, 1):
+            gmv = R.gm(**dict(kw, radii_type_indexed=bool(rti)))
+            rad = x["tradii"] if rti else x["vradii"]
+            tag = "%s/rti%d/" % (name, rti)
+            out[tag + "forward_vector"] = R.forward_vector(gmv, CENTER, x["vcoords"], x["tv"], rad)
+            ag, tg = R.backward_vector(gmv, CENTER, x["vcoords"], x["tv"], rad, x["diff"])
+            out[tag + "atom_gradients"], out[tag + "type_gradients"] = ag, tg
+            if not kw.get("binary"):
+                dd, add, tdd = R.backward_gradients(gmv, CENTER, x["vcoords"], x["tv"], rad, x["diff"], ag, tg)
+                out[tag + "diffdiff"], out[tag + "atom_diffdiff"], out[tag + "type_diffdiff"] = dd, add, tdd
+    q, q2, c, t, pts, grid = transform_inputs()
+    out["quat/ops"] = R.quaternion_ops(q, q2, pts[0])
+    for name, qq in (("nonunit", q), ("unit", q2)):
+        tr = R.tr(qq, c, t)
+        for dt in (0, 1):
+            out["transform/%s/forward%d" % (name, dt)] = R.transform_forward(tr, pts, bool(dt))
+            out["transform/%s/backward%d" % (name, dt)] = R.transform_backward(tr, pts, bool(dt))
+    out["interp/same"] = R.interpolate([0.5, 7.5, 0.5, 7.5], c, grid, R.tr(q2, c, t), c)
+    out["interp/resample"] = R.interpolate([0.5, 7.5, 0.25, 5.0], (0, 0, 0), grid, R.tr(q2, (0, 0, 0), t), (0.5, 0, 0))
+    # the reference's seeded random transforms: 4 draws with rotation, 2 without
+    out["random/rot"] = R.random_transform(1234, (1, 2, 3), 2.5, True, 4)
+    out["random/norot"] = R.random_transform(99, (0, 0, 0), 1.0, False, 2)
+    np.savez_compressed(OUT, **out)
+    print("wrote", OUT, os.path.getsize(OUT), "bytes,", len(out), "arrays")
+
+
+if __name__ == "__main__":
+    main()

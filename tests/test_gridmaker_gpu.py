@@ -1,0 +1,284 @@
+"""GPU parity of GridMaker forward/backward/relevance against the CPU oracle.
+
+Every call goes through the C ABI (libmolgrid_b200.api is a ctypes wrapper over it).
+Tolerances are the ones the path states: binary grids and channel assignment bit-exact, densities
+rel 1e-5 / abs 1e-6, gradients and relevance rel 1e-4 (abs floor 1e-5 x the gradient scale).
+"""
+import numpy as np
+import pytest
+import torch
+
+from tests import cases
+
+pytestmark = pytest.mark.gpu
+
+DENS = dict(rtol=1e-5, atol=1e-6)
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def gm_pair(port, **kw):
+    import libmolgrid_b200 as lmg
+    g = lmg.GridMaker(kw.get("resolution", 0.5), kw.get("dimension", 23.5), kw.get("binary", False),
+                      kw.get("radius_type_indexed", False), kw.get("radius_scale", 1.0),
+                      kw.get("gaussian_radius_multiple", 1.0))
+    og = port.gm(kw.get("resolution", 0.5), kw.get("dimension", 23.5), kw.get("binary", False),
+                 kw.get("radius_type_indexed", False), kw.get("radius_scale", 1.0),
+                 kw.get("gaussian_radius_multiple", 1.0))
+    return g, og
+
+
+def grad_close(a, b, what):
+    scale = max(1.0, float(np.abs(b).max()))
+    assert np.allclose(a, b, rtol=1e-4, atol=1e-5 * scale), \
+        "%s: max abs diff %g (scale %g)" % (what, np.abs(a - b).max(), scale)
+
+
+SETTINGS = [
+    dict(),                                                           # the benchmark's settings
+    dict(resolution=0.5, dimension=6.0),                              # 13 points: not a multiple of 4
+    dict(resolution=0.25, dimension=7.75, radius_scale=0.5, gaussian_radius_multiple=3.0),
+    dict(resolution=0.5, dimension=11.5, radius_scale=1.2, gaussian_radius_multiple=-2.0),
+    dict(resolution=0.5, dimension=11.5, gaussian_radius_multiple=-1.5),
+    dict(resolution=0.375, dimension=9.0, gaussian_radius_multiple=0.7),
+]
+
+
+@pytest.mark.parametrize("kw", SETTINGS)
+@pytest.mark.parametrize("binary", [False, True])
+def test_forward_index(port, kw, binary):
+    kw = dict(kw, binary=binary)
+    g, og = gm_pair(port, **kw)
+    T = 28 if not kw.get("dimension") else 5
+    ext = 10.0 if not kw.get("dimension") else kw["dimension"] / 2 + 1
+    coords, types, radii = cases.index_case(1000, 300, T, ext)
+    center = (0.1, -0.2, 0.3)
+    want = port.forward_index(og, center, coords, types, radii, T)
+    out = torch.full(g.grid_dimensions(T), -7.0, device="cuda")
+    g.forward(center, dev(coords), dev(types), dev(radii), out)
+    g.check_types()
+    got = out.cpu().numpy()
+    if binary:
+        assert np.array_equal(got, want)
+    else:
+        assert np.array_equal(got != 0, want != 0) or kw.get("gaussian_radius_multiple", 1) > 0
+        assert np.allclose(got, want, **DENS), np.abs(got - want).max()
+
+
+def test_forward_c0_known_answers(port):
+    """Line profile of one atom (test/test_gridmaker.py:131-164 of the reference)."""
+    g, og = gm_pair(port, resolution=0.1, dimension=6.0)
+    out = torch.zeros(g.grid_dimensions(1), device="cuda")
+    g.forward((0, 0, 0), dev(np.zeros((1, 3), np.float32)), dev(np.zeros(1, np.float32)),
+              dev(np.ones(1, np.float32)), out)
+    o = out.cpu().numpy()[0]
+    c = o.shape[0] // 2
+    assert o[c, c, c] == pytest.approx(1.0, abs=1e-6)
+    assert o[c + 5, c, c] == pytest.approx(0.60653066, rel=1e-5)
+    assert o[c, c - 12, c] == pytest.approx(0.0487206, rel=1e-4)
+    assert o[c, c, c + 15] == pytest.approx(0.0, abs=1e-6)
+
+
+def test_forward_transform_fused(port):
+    g, og = gm_pair(port)
+    T = 28
+    coords, types, radii = cases.index_case(7, 500, T, 10.0)
+    rng = np.random.default_rng(3)
+    q = cases.random_quaternion(rng, 1)[0]
+    tr = port.tr(q, (0.5, 1.0, -0.5), rng.uniform(-2, 2, 3))
+    moved = port.transform_forward(tr, coords)
+    for binary in (False, True):
+        g.set_binary(binary)
+        og[2] = float(binary)
+        want = port.forward_index(og, (0.5, 1.0, -0.5), moved, types, radii, T)
+        import libmolgrid_b200 as lmg
+        t = lmg.Transform(lmg.Quaternion(*q), tuple(tr[4:7]), tuple(tr[7:10]))
+        out = torch.empty(g.grid_dimensions(T), device="cuda")
+        g.forward((0.5, 1.0, -0.5), dev(coords), dev(types), dev(radii), out, transforms=t)
+        got = out.cpu().numpy()
+        if binary:
+            assert np.array_equal(got, want)
+        else:
+            assert np.allclose(got, want, **DENS)
+
+
+@pytest.mark.parametrize("binary", [False, True])
+def test_forward_batched_blob(port, binary):
+    """A small batch with the benchmark's atom statistics, ragged sizes, per-example transforms."""
+    g, og = gm_pair(port, binary=binary)
+    B, T = 3, 28
+    coords, types, radii, ns, tr = cases.blob_batch(1001, B, 2000, 4000, T)
+    out = torch.empty((B,) + g.grid_dimensions(T), device="cuda")
+    centers = np.zeros((B, 3), np.float32)
+    g.forward(dev(centers), dev(coords), dev(types), dev(radii), out, transforms=dev(tr),
+              n_atoms=torch.from_numpy(ns))
+    got = out.cpu().numpy()
+    for b in range(B):
+        n = ns[b]
+        moved = port.transform_forward(tr[b], coords[b, :n])
+        want = port.forward_index(og, (0, 0, 0), moved, types[b, :n], radii[b, :n], T)
+        if binary:
+            assert np.array_equal(got[b], want)
+        else:
+            assert np.allclose(got[b], want, **DENS), np.abs(got[b] - want).max()
+
+
+@pytest.mark.parametrize("rti", [False, True])
+@pytest.mark.parametrize("binary", [False, True])
+@pytest.mark.parametrize("kw", [dict(resolution=0.5, dimension=11.5),
+                                dict(resolution=0.25, dimension=7.75),
+                                dict(resolution=0.5, dimension=6.0, gaussian_radius_multiple=-1.5)])
+def test_forward_vector(port, kw, rti, binary):
+    kw = dict(kw, binary=binary, radius_type_indexed=rti)
+    g, og = gm_pair(port, **kw)
+    T = 6
+    coords, tv, radii = cases.vector_case(11, 200, T, kw["dimension"] / 2 + 1, rti=rti)
+    want = port.forward_vector(og, (0, 0, 0), coords, tv, radii)
+    out = torch.empty(g.grid_dimensions(T), device="cuda")
+    g.forward((0, 0, 0), dev(coords), dev(tv), dev(radii), out)
+    got = out.cpu().numpy()
+    assert np.allclose(got, want, **DENS), np.abs(got - want).max()
+    if binary:
+        assert np.array_equal(got != 0, want != 0)
+
+
+def test_vector_equals_index(port):
+    """One-hot type vectors give the index-typed grid (test/test_gridmaker.py:217-240)."""
+    g, og = gm_pair(port, resolution=0.5, dimension=11.5)
+    T = 5
+    coords, types, radii = cases.index_case(5, 100, T, 6.0, ties=False)
+    tv = np.zeros((100, T), np.float32)
+    tv[np.arange(100), types.astype(int)] = 1
+    a = torch.empty(g.grid_dimensions(T), device="cuda")
+    b = torch.empty(g.grid_dimensions(T), device="cuda")
+    g.forward((0, 0, 0), dev(coords), dev(types), dev(radii), a)
+    g.forward((0, 0, 0), dev(coords), dev(tv), dev(radii), b)
+    assert torch.allclose(a, b, rtol=1e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("kw", SETTINGS)
+def test_backward_index_and_relevance(port, kw):
+    g, og = gm_pair(port, **kw)
+    T = 28 if not kw.get("dimension") else 5
+    ext = 10.0 if not kw.get("dimension") else kw["dimension"] / 2 + 1
+    coords, types, radii = cases.index_case(1002, 300, T, ext)
+    rng = np.random.default_rng(5)
+    diff = rng.normal(size=g.grid_dimensions(T)).astype(np.float32)
+    want = port.backward_index(og, (0, 0, 0), coords, types, radii, diff)
+    ag = torch.full((300, 3), 9.0, device="cuda")
+    g.backward((0, 0, 0), dev(coords), dev(types), dev(radii), dev(diff), ag)
+    grad_close(ag.cpu().numpy(), want, "atom gradients")
+
+    dens = port.forward_index(og, (0, 0, 0), coords, types, radii, T)
+    wantr = port.backward_relevance(og, (0, 0, 0), coords, types, radii, dens, diff)
+    rel = torch.full((300,), 9.0, device="cuda")
+    g.backward_relevance((0, 0, 0), dev(coords), dev(types), dev(radii), dev(dens), dev(diff), rel)
+    grad_close(rel.cpu().numpy(), wantr, "relevance")
+
+
+def test_backward_known_answer(port):
+    """d/dx of one atom at (1,0,0), r=2, upstream 1 at the centre voxel: -0.60653
+    (test/test_gridmaker.py:186-214, test/test_torch.py:128-140 of the reference)."""
+    g, og = gm_pair(port, resolution=0.5, dimension=29.5 + 0.5)
+    d = g.spatial_grid_dimensions()[0]
+    diff = np.zeros((1, d, d, d), np.float32)
+    diff[0, d // 2, d // 2, d // 2] = 1.0
+    coords = np.array([[1, 0, 0]], np.float32)
+    ag = torch.zeros((1, 3), device="cuda")
+    g.backward((0, 0, 0), dev(coords), dev(np.zeros(1, np.float32)), dev(np.full(1, 2.0, np.float32)),
+               dev(diff), ag)
+    want = port.backward_index(og, (0, 0, 0), coords, [0], [2.0], diff)
+    grad_close(ag.cpu().numpy(), want, "single atom")
+    if d % 2 == 1:
+        assert ag[0, 0].item() == pytest.approx(-0.60653066, rel=1e-4)
+
+
+@pytest.mark.parametrize("rti", [False, True])
+@pytest.mark.parametrize("binary", [False, True])
+def test_backward_vector(port, rti, binary):
+    kw = dict(resolution=0.5, dimension=11.5, binary=binary, radius_type_indexed=rti)
+    g, og = gm_pair(port, **kw)
+    T = 6
+    coords, tv, radii = cases.vector_case(13, 150, T, 6.5, rti=rti)
+    rng = np.random.default_rng(6)
+    diff = rng.normal(size=g.grid_dimensions(T)).astype(np.float32)
+    wag, wtg = port.backward_vector(og, (0, 0, 0), coords, tv, radii, diff)
+    ag = torch.full((150, 3), 9.0, device="cuda")
+    tg = torch.full((150, T), 9.0, device="cuda")
+    g.backward((0, 0, 0), dev(coords), dev(tv), dev(radii), dev(diff), ag, tg)
+    grad_close(ag.cpu().numpy(), wag, "atom gradients")
+    grad_close(tg.cpu().numpy(), wtg, "type gradients")
+
+
+def test_backward_batched(port):
+    g, og = gm_pair(port)
+    B, T = 2, 28
+    coords, types, radii, ns, tr = cases.blob_batch(1002, B, 2000, 2500, T)
+    rng = np.random.default_rng(8)
+    diff = rng.normal(size=(B,) + g.grid_dimensions(T)).astype(np.float32)
+    N = coords.shape[1]
+    ag = torch.full((B, N, 3), 9.0, device="cuda")
+    g.backward(dev(np.zeros((B, 3), np.float32)), dev(coords), dev(types), dev(radii), dev(diff), ag,
+               transforms=dev(tr), n_atoms=torch.from_numpy(ns))
+    got = ag.cpu().numpy()
+    for b in range(B):
+        n = ns[b]
+        moved = port.transform_forward(tr[b], coords[b, :n])
+        want = port.backward_index(og, (0, 0, 0), moved, types[b, :n], radii[b, :n], diff[b])
+        grad_close(got[b, :n], want, "example %d" % b)
+        assert np.all(got[b, n:] == 0)
+
+
+def test_errors(port):
+    import libmolgrid_b200 as lmg
+    g = lmg.GridMaker(0.5, 5.5)
+    c = torch.zeros((4, 3), device="cuda")
+    t = torch.zeros(4, device="cuda")
+    r = torch.ones(4, device="cuda")
+    with pytest.raises(IndexError):          # wrong grid size -> std::out_of_range
+        g.forward((0, 0, 0), c, t, r, torch.zeros((2, 11, 11, 11), device="cuda"))
+    with pytest.raises(IndexError):          # radii length
+        g.forward((0, 0, 0), c, t, torch.ones(3, device="cuda"), torch.zeros((2, 12, 12, 12), device="cuda"))
+    with pytest.raises(ValueError):          # non-contiguous
+        g.forward((0, 0, 0), torch.zeros((3, 4), device="cuda").t(), t, r,
+                  torch.zeros((2, 12, 12, 12), device="cuda"))
+    g2 = lmg.GridMaker(0.5, 5.5, False, True)
+    with pytest.raises(ValueError):          # type-indexed radii with index types
+        g2.forward((0, 0, 0), c, t, r, torch.zeros((2, 12, 12, 12), device="cuda"))
+    # a type index beyond the channels is reported through the status word
+    out = torch.zeros((2, 12, 12, 12), device="cuda")
+    g.forward((0, 0, 0), c, torch.full((4,), 2.0, device="cuda"), r, out)
+    with pytest.raises(IndexError):
+        g.check_types()
+    # negative types are skipped silently
+    g.forward((0, 0, 0), c, torch.full((4,), -1.0, device="cuda"), r, out)
+    g.check_types()
+    assert float(out.abs().sum()) == 0.0
+
+
+def test_small_workspace_runs_in_passes(port):
+    """A workspace that holds one example at a time gives the same grids."""
+    import libmolgrid_b200.api as api
+    g, og = gm_pair(port, resolution=0.5, dimension=11.5)
+    B, T, N = 5, 4, 64
+    rng = np.random.default_rng(0)
+    coords = rng.uniform(-6, 6, (B, N, 3)).astype(np.float32)
+    types = rng.integers(0, T, (B, N)).astype(np.float32)
+    radii = rng.uniform(1, 2, (B, N)).astype(np.float32)
+    centers = np.zeros((B, 3), np.float32)
+    a = torch.empty((B,) + g.grid_dimensions(T), device="cuda")
+    g.forward(dev(centers), dev(coords), dev(types), dev(radii), a)
+    old = api.MAX_WORKSPACE_BYTES
+    try:
+        one = api._cabi.lib().lmg_workspace_bytes(g.s, 0, 1, N, T, 0)
+        api.MAX_WORKSPACE_BYTES = one + 1024
+        api._workspaces.clear()
+        b = torch.empty_like(a)
+        g.forward(dev(centers), dev(coords), dev(types), dev(radii), b)
+    finally:
+        api.MAX_WORKSPACE_BYTES = old
+        api._workspaces.clear()
+    assert torch.equal(a != 0, b != 0)
+    assert torch.allclose(a, b, rtol=1e-6, atol=1e-7)

@@ -124,7 +124,7 @@ class _Arg(object):
             if obj.dtype != np.float32 or not obj.flags["C_CONTIGUOUS"]:
                 raise ValueError("%s: numpy arrays must be C-contiguous float32" % name)
             self.host = torch.from_numpy(obj)
-            t = self.host.to(device, non_blocking=True)
+            t = self._stage(self.host, device, output)
         elif torch.is_tensor(obj):
             if obj.dtype != torch.float32:
                 raise ValueError("%s: tensors must be float32 (double grids are not supported on the GPU path)" % name)
@@ -136,13 +136,20 @@ class _Arg(object):
                 t = obj
             else:
                 self.host = obj
-                t = obj.to(device, non_blocking=True)
+                t = self._stage(obj, device, output)
         else:
             raise TypeError("%s: expected a torch tensor or numpy array" % name)
         if t.dim() != ndim:
             raise TypeError("%s: expected %d dimensions, got %d" % (name, ndim, t.dim()))
         self.t = t
         self.output = output
+
+    @staticmethod
+    def _stage(host, device, output):
+        # outputs are fully overwritten by the kernels, so only inputs are copied in
+        if output:
+            return torch.empty(host.shape, dtype=host.dtype, device=device)
+        return host.to(device, non_blocking=True)
 
     @property
     def ptr(self):

@@ -5,6 +5,7 @@
 #include <cstring>
 #include <random>
 #include <string>
+#include <vector>
 
 #include "../../include/lmg_b200.h"
 #include "lmg_launch.h"
@@ -16,6 +17,26 @@ thread_local std::string g_err;
 std::default_random_engine g_engine;  // same engine type as libmolgrid::random_engine
 float g_radius_hint = 3.5f;           // largest radius*radius_scale*final_radius_multiple expected
 int g_precise = -1;                   // -1 auto, 0 fast density, 1 reference-order density
+
+// ---- optional per-kernel timing (bench support; off by default) --------------------------------
+// When enabled, the forward and backward kernels of each pass are bracketed by CUDA events on the
+// launching stream; lmg_profile_collect() synchronises and returns the summed durations.
+struct ProfRec { cudaEvent_t e0, e1; int kind; };
+std::vector<ProfRec> g_prof;
+size_t g_prof_used = 0;
+bool g_prof_on = false;
+long g_launches = 0;  // kernels launched by this library since load (memsets not counted)
+
+ProfRec* prof_begin(int kind, cudaStream_t st) {
+  if (!g_prof_on || g_prof_used >= g_prof.size()) return nullptr;
+  ProfRec* r = &g_prof[g_prof_used++];
+  r->kind = kind;
+  cudaEventRecord(r->e0, st);
+  return r;
+}
+void prof_end(ProfRec* r, cudaStream_t st) {
+  if (r != nullptr) cudaEventRecord(r->e1, st);
+}
 
 int fail(int code, const std::string& msg) {
   g_err = msg;
@@ -183,6 +204,40 @@ int lmg_version(void) { return 100; }
 
 void lmg_set_random_seed(unsigned seed) { g_engine.seed(seed); }
 
+// Bench support (not part of the reference interface): per-kernel durations and launch counts.
+int lmg_profile_enable(int max_records) {
+  for (auto& r : g_prof) { cudaEventDestroy(r.e0); cudaEventDestroy(r.e1); }
+  g_prof.clear();
+  g_prof_used = 0;
+  g_prof_on = max_records > 0;
+  for (int i = 0; i < max_records; i++) {
+    ProfRec r;
+    r.kind = 0;
+    if (cudaEventCreate(&r.e0) != cudaSuccess || cudaEventCreate(&r.e1) != cudaSuccess)
+      return fail(LMG_ERR_CUDA, "creating profiling events");
+    g_prof.push_back(r);
+  }
+  return LMG_OK;
+}
+
+// ms[k], count[k] for k = 0 (forward kernel) and 1 (backward kernels); resets the records
+int lmg_profile_collect(double* ms, int* count) {
+  ms[0] = ms[1] = 0;
+  count[0] = count[1] = 0;
+  for (size_t i = 0; i < g_prof_used; i++) {
+    cudaError_t e = cudaEventSynchronize(g_prof[i].e1);
+    float t = 0;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&t, g_prof[i].e0, g_prof[i].e1);
+    if (e != cudaSuccess) return cuda_fail(e, "reading profiling events");
+    ms[g_prof[i].kind] += t;
+    count[g_prof[i].kind] += 1;
+  }
+  g_prof_used = 0;
+  return LMG_OK;
+}
+
+long lmg_launch_count(void) { return g_launches; }
+
 // Tuning knobs (not part of the reference interface).
 void lmg_set_max_radius_hint(float angstroms) { g_radius_hint = angstroms > 0 ? angstroms : 3.5f; }
 void lmg_set_precise(int mode) { g_precise = mode; }
@@ -300,6 +355,7 @@ int lmg_forward(const lmg_gridmaker* g, const lmg_atoms* a, float* out, void* wo
     if (e != cudaSuccess) return cuda_fail(e, "emit");
     e = lmg::launch_scan_fill(E, st);
     if (e != cudaSuccess) return cuda_fail(e, "scan/fill");
+    g_launches += 3 + ((vec && g->radii_type_indexed) ? 1 : 0);
     lmg::FwdArgs F;
     std::memset(&F, 0, sizeof F);
     F.gm = E.gm; F.b0 = b0; F.nb = nb; F.N = E.N; F.T = E.T;
@@ -312,7 +368,10 @@ int lmg_forward(const lmg_gridmaker* g, const lmg_atoms* a, float* out, void* wo
     F.bigcount = E.bigcount; F.biglist = E.biglist;
     F.nrx = G.nrx; F.nry = G.nry; F.nrz = G.nrz; F.M = E.M; F.listcap = E.listcap;
     F.out = out;
+    ProfRec* pr = prof_begin(0, st);
     e = lmg::launch_forward(F, st);
+    prof_end(pr, st);
+    g_launches += 1;
     if (e != cudaSuccess) return cuda_fail(e, "forward");
   }
   return LMG_OK;
@@ -354,7 +413,11 @@ static int backward_common(const lmg_gridmaker* g, const lmg_atoms* a, int op, i
     B.diff = diff; B.density = density;
     B.atom_gradients = atom_gradients; B.type_gradients = type_gradients; B.relevance = relevance;
     B.partial = reinterpret_cast<float*>(ws + L.partial);
+    g_launches += 1 + ((vec && g->radii_type_indexed) ? 1 : 0);
+    ProfRec* pr = prof_begin(1, st);
     e = lmg::launch_backward(B, mode, st);
+    prof_end(pr, st);
+    g_launches += mode == 1 ? 2 : 1;
     if (e != cudaSuccess) return cuda_fail(e, "backward");
   }
   return LMG_OK;

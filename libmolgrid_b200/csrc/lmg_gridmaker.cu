@@ -432,7 +432,7 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) k_forward(FwdArgs F) {
 
 struct ItemParams {
   float x, y, z;
-  float inv_ar2, inv_ar, Tg, Tcut, Tbin, w;
+  float inv_ar2, inv_ar, Tg, Tcut, Tbin, w, ar;
   unsigned lox, hix, loy, hiy, loz, hiz;
   int chan;
   bool valid;
@@ -455,12 +455,13 @@ __device__ __forceinline__ ItemParams load_item(const BwdArgs& G, int bl, int b,
   if (VEC && G.gm.rti) {
     ChanParam cp = G.chanp[(size_t)bl * G.T + P.chan];
     P.inv_ar2 = cp.p.x; P.Tg = cp.p.y; P.inv_ar = cp.p.z; P.Tcut = cp.p.w; P.Tbin = cp.q.x;
+    P.ar = cp.q.y;
     bounds_1d(ox, P.x, cp.q.z, G.gm.res, G.gm.dim, P.lox, P.hix);
     bounds_1d(oy, P.y, cp.q.z, G.gm.res, G.gm.dim, P.loy, P.hiy);
     bounds_1d(oz, P.z, cp.q.z, G.gm.res, G.gm.dim, P.loz, P.hiz);
     P.valid = P.valid && cp.q.y > 0.f;
   } else {
-    P.inv_ar2 = rb.y; P.Tg = rb.z; P.inv_ar = rb.w; P.Tcut = rd.x; P.Tbin = rd.y;
+    P.inv_ar2 = rb.y; P.Tg = rb.z; P.inv_ar = rb.w; P.Tcut = rd.x; P.Tbin = rd.y; P.ar = rd.z;
     P.lox = lo16(rc.x); P.loy = hi16(rc.x); P.hix = lo16(rc.y); P.hiy = hi16(rc.y);
     P.loz = lo16(rc.z); P.hiz = hi16(rc.z);
   }
@@ -532,13 +533,16 @@ __global__ void __launch_bounds__(BWD_THREADS) k_backward(BwdArgs G) {
             }
           }
           if (MODE != 0) {
+            // relevance divides by the density grid, which amplifies any relative error of a
+            // near-zero tail value: it uses the reference's own operation order
             float v = BINARY ? (rsq < P.Tbin ? 1.f : 0.f)
-                             : density_fast(rsq, P.inv_ar2, P.Tg, P.Tcut, gm.A, gm.B, gm.C);
+                      : MODE == 2 ? density_precise(rsq, P.ar, P.Tg, P.Tcut, gm.A, gm.B, gm.C)
+                                  : density_fast(rsq, P.inv_ar2, P.Tg, P.Tcut, gm.A, gm.B, gm.C);
             if (MODE == 1) {
               tg = fmaf(v, dv, tg);
             } else if (v > 0.f) {
               float de = __ldg(dens + (x * dim + y) * dim + z);
-              if (de > 0.f) tg += __fdividef(dv * v, de);
+              if (de > 0.f) tg += __fdiv_rn(__fmul_rn(dv, v), de);
             }
           }
         }

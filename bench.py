@@ -122,7 +122,7 @@ class ClockSampler(threading.Thread):
     def __init__(self, index):
         super().__init__(daemon=True)
         self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
-        self._stop = threading.Event()
+        self._halt = threading.Event()
         self.ok = False
         try:
             import pynvml
@@ -137,7 +137,7 @@ class ClockSampler(threading.Thread):
     def run(self):
         if not self.ok:
             return
-        while not self._stop.is_set():
+        while not self._halt.is_set():
             try:
                 self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
                 r = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
@@ -146,10 +146,10 @@ class ClockSampler(threading.Thread):
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.02)
+            self._halt.wait(0.02)
 
     def stop(self):
-        self._stop.set()
+        self._halt.set()
         self.join(timeout=2)
         med = float(np.median(self.samples)) if self.samples else None
         return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
@@ -180,7 +180,7 @@ def run_gpu_arm(args, rank, world, local_rank):
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         kind = _cpu_kind()
         cores = os.cpu_count() or 1
-        per_core = 2
+        per_core = 8   # about 0.1 s of CPU work per example
         rate, wall = cpu_examples_per_s(kind, cores, per_core)
         cpu = {"value": rate, "unit": "examples/s", "cores": cores, "kind": kind,
                "sample": "%d examples of the same workload (%d per core, one process per core), %.1f s wall"
@@ -316,6 +316,7 @@ def run_gpu_arm(args, rank, world, local_rank):
 
 
 def main():
+    global BATCH
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
@@ -331,7 +332,6 @@ def main():
     if args.impl == "reference":
         run_reference_arm(args, rank)
         return
-    global BATCH
     BATCH = args.batch
     run_gpu_arm(args, rank, world, local_rank)
 

@@ -156,17 +156,17 @@ __device__ __forceinline__ float voxel_coord(float origin, unsigned i, float res
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
-  asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 __device__ __forceinline__ float sqrt_approx(float x) {
   float y;
-  asm("sqrt.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 __device__ __forceinline__ float rsqrt_approx(float x) {
   float y;
-  asm("rsqrt.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 

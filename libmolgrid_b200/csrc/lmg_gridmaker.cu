@@ -9,8 +9,8 @@
 //            bit mask of atoms whose footprint crosses the lane's z-column, then every lane walks
 //            its own mask and accumulates 4 voxels in registers; each output voxel is written
 //            exactly once with a 16-byte store (no memset, no read-modify-write of the grid).
-// Backward passes read the atom records directly: 8 lanes sweep one atom's footprint along z and
-// reduce with shuffles, so no global atomics are needed.
+// Backward passes read the atom records directly: one warp per atom sweeps the footprint (four
+// lanes along z, eight columns at a time) and reduces with shuffles, so no global atomics are needed.
 #include "lmg_device.cuh"
 #include "lmg_launch.h"
 
@@ -27,6 +27,23 @@ __device__ __forceinline__ void region_box(const uint4& c, int& rx0, int& rx1, i
   rx0 = lox / REG_X; rx1 = (hix - 1) / REG_X;
   ry0 = loy / REG_Y; ry1 = (hiy - 1) / REG_Y;
   rz0 = loz / REG_Z; rz1 = (hiz - 1) / REG_Z;
+}
+
+// True when the axis-aligned box of region (rx,ry,rz) can hold a voxel within sqrt(Tcull) of the
+// atom.  Conservative (the threshold is widened by a few ulps' worth), and a pure function of its
+// arguments so that the counting and the filling pass agree.
+__device__ __forceinline__ bool region_in_reach(const GMParams& gm, float ox, float oy, float oz,
+                                                float ax, float ay, float az, float Tcull,
+                                                int rx, int ry, int rz) {
+  unsigned last = gm.dim - 1;
+  float x0 = voxel_coord(ox, rx * REG_X, gm.res), x1 = voxel_coord(ox, min((unsigned)(rx * REG_X + REG_X - 1), last), gm.res);
+  float y0 = voxel_coord(oy, ry * REG_Y, gm.res), y1 = voxel_coord(oy, min((unsigned)(ry * REG_Y + REG_Y - 1), last), gm.res);
+  float z0 = voxel_coord(oz, rz * REG_Z, gm.res), z1 = voxel_coord(oz, min((unsigned)(rz * REG_Z + REG_Z - 1), last), gm.res);
+  float dx = fmaxf(fmaxf(x0 - ax, ax - x1), 0.f);
+  float dy = fmaxf(fmaxf(y0 - ay, ay - y1), 0.f);
+  float dz = fmaxf(fmaxf(z0 - az, az - z1), 0.f);
+  float d2 = dx * dx + dy * dy + dz * dz;
+  return d2 <= Tcull * 1.0001f + 1e-12f;
 }
 
 // Type-indexed radii: constants of channel t of example b.
@@ -69,6 +86,7 @@ __global__ void __launch_bounds__(256) k_emit(EmitArgs A) {
 
   bool valid = A.n_atoms == nullptr || a < A.n_atoms[b];
   int chan = 0;
+  float ox = 0.f, oy = 0.f, oz = 0.f;
   if (valid && !A.vec) {
     float tf = A.type_index[(size_t)b * A.N + a];
     // forward takes floor (src/grid_maker.cpp:171), the backward passes round (:456, :698)
@@ -97,7 +115,7 @@ __global__ void __launch_bounds__(256) k_emit(EmitArgs A) {
     } else {
       cx = A.center_host[0]; cy = A.center_host[1]; cz = A.center_host[2];
     }
-    float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
+    ox = __fsub_rn(cx, gm.half); oy = __fsub_rn(cy, gm.half); oz = __fsub_rn(cz, gm.half);
 
     float radius;
     if (gm.rti) {
@@ -142,6 +160,7 @@ __global__ void __launch_bounds__(256) k_emit(EmitArgs A) {
       for (int rx = rx0; rx <= rx1; rx++)
         for (int ry = ry0; ry <= ry1; ry++)
           for (int rz = rz0; rz <= rz1; rz++) {
+            if (!region_in_reach(gm, ox, oy, oz, r.a.x, r.a.y, r.a.z, r.a.w, rx, ry, rz)) continue;
             int reg = (rx * A.nry + ry) * A.nrz + rz;
             atomicAdd(&cnt[(size_t)reg * tb + ch], 1u);
           }
@@ -212,6 +231,15 @@ __global__ void __launch_bounds__(256) k_fill(EmitArgs A) {
   uint4 c = A.recs[i].c;
   unsigned flags = c.w >> 16;
   if (!(flags & REC_VALID) || (flags & REC_BIG)) return;
+  float4 ra = A.recs[i].a;
+  int b = A.b0 + bl;
+  float cx, cy, cz;
+  if (A.centers != nullptr) {
+    cx = A.centers[b * 3]; cy = A.centers[b * 3 + 1]; cz = A.centers[b * 3 + 2];
+  } else {
+    cx = A.center_host[0]; cy = A.center_host[1]; cz = A.center_host[2];
+  }
+  float ox = __fsub_rn(cx, A.gm.half), oy = __fsub_rn(cy, A.gm.half), oz = __fsub_rn(cz, A.gm.half);
   int rx0, rx1, ry0, ry1, rz0, rz1;
   region_box(c, rx0, rx1, ry0, ry1, rz0, rz1);
   unsigned* cnt = A.cnt + (size_t)bl * A.M;
@@ -221,6 +249,7 @@ __global__ void __launch_bounds__(256) k_fill(EmitArgs A) {
   for (int rx = rx0; rx <= rx1; rx++)
     for (int ry = ry0; ry <= ry1; ry++)
       for (int rz = rz0; rz <= rz1; rz++) {
+        if (!region_in_reach(A.gm, ox, oy, oz, ra.x, ra.y, ra.z, ra.w, rx, ry, rz)) continue;
         int reg = (rx * A.nry + ry) * A.nrz + rz;
         unsigned p = atomicAdd(&cnt[(size_t)reg * tb + ch], 1u);
         list[p] = (unsigned)a;
@@ -427,7 +456,241 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) k_forward(FwdArgs F) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// backward: 8 lanes per work item sweep the footprint along z
+// forward, index types: the lists of one region are contiguous over channels, so the warp walks
+// them in chunks of 32 atoms regardless of channel.  Each lane keeps the 4 voxels of the channel
+// it is currently in and stores them when its next atom belongs to another channel.
+// ---------------------------------------------------------------------------------------------
+
+// out[lane j] bit i = in[lane i] bit j
+__device__ __forceinline__ unsigned warp_transpose32(unsigned x, int lane) {
+  unsigned m = 0x0000ffffu;
+#pragma unroll
+  for (int j = 16; j >= 1; j >>= 1) {
+    unsigned p = __shfl_xor_sync(0xffffffffu, x, j);
+    x = (lane & j) ? (((p >> j) & m) | (x & ~m)) : ((x & m) | ((p & m) << j));
+    m ^= m << (j >> 1);
+  }
+  return x;
+}
+
+struct __align__(16) CandI {
+  float4 a;  // x, y, z, Tcull
+  float4 b;  // kexp (ar when PRECISE), inv_ar2, Tg, Tcut (Tbin when BINARY)
+  uint4 c;   // lo.z|hi.z<<16, channel, unused, unused
+};
+
+template <bool BINARY, bool PRECISE>
+__global__ void __launch_bounds__(FWD_WARPS * 32) k_forward_index(FwdArgs F) {
+  __shared__ CandI cand_s[FWD_WARPS][32];
+  const GMParams& gm = F.gm;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  // one block per region; its warps split the channels so that a crowded region is worked on by
+  // several warps, each owning whole channels (no two warps ever write the same voxel)
+  int reg = blockIdx.x;
+  int bl = blockIdx.y;
+  int b = F.b0 + bl;
+  int chans_per_warp = (F.T + FWD_WARPS - 1) / FWD_WARPS;
+  int cbeg = wid * chans_per_warp, cend = min(F.T, cbeg + chans_per_warp);
+  if (cbeg >= cend) return;
+  CandI* cs = cand_s[wid];
+
+  int rz = reg % F.nrz;
+  int ry = (reg / F.nrz) % F.nry;
+  int rx = reg / (F.nrz * F.nry);
+  unsigned x0 = rx * REG_X, y0 = ry * REG_Y;
+  unsigned vx = x0 + (lane >> 3), vy = y0 + (lane & 7), vz0 = rz * REG_Z;
+  bool col_ok = vx < gm.dim && vy < gm.dim;
+
+  float cx, cy, cz;
+  if (F.centers != nullptr) {
+    cx = F.centers[b * 3]; cy = F.centers[b * 3 + 1]; cz = F.centers[b * 3 + 2];
+  } else {
+    cx = F.center_host[0]; cy = F.center_host[1]; cz = F.center_host[2];
+  }
+  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
+  float gx = voxel_coord(ox, vx, gm.res), gy = voxel_coord(oy, vy, gm.res);
+  float gz[REG_Z];
+#pragma unroll
+  for (int k = 0; k < REG_Z; k++) gz[k] = voxel_coord(oz, vz0 + k, gm.res);
+  float gxr[REG_X];
+#pragma unroll
+  for (int k = 0; k < REG_X; k++) gxr[k] = voxel_coord(ox, x0 + k, gm.res);
+
+  const Rec* recs = F.recs + (size_t)bl * F.N;
+  const unsigned* cnt = F.cnt + (size_t)bl * F.M;
+  const unsigned* list = F.list + (size_t)bl * F.listcap;
+  size_t dim = gm.dim;
+  float* outb = F.out + (size_t)b * F.T * dim * dim * dim;
+  float* ocol = outb + ((size_t)vx * dim + vy) * dim + vz0;  // + chan * dim^3
+  size_t chan_stride = dim * dim * dim;
+  bool vec4_ok = F.vec4_ok;
+  float A_ = gm.A, B_ = gm.B, C_ = gm.C;
+
+  for (int g0 = cbeg; g0 < cend; g0 += 32) {
+    int g1 = min(g0 + 32, cend);
+    size_t bin0 = (size_t)reg * F.T + g0;
+    unsigned beg = bin0 == 0 ? 0u : cnt[bin0 - 1];
+    unsigned end = cnt[(size_t)reg * F.T + g1 - 1];
+    int cur = -1;
+    unsigned written = 0;
+    float acc[REG_Z];
+#pragma unroll
+    for (int k = 0; k < REG_Z; k++) acc[k] = 0.f;
+
+    auto flush = [&]() {
+      if (cur >= 0 && col_ok) {
+        float* o = ocol + (size_t)cur * chan_stride;
+        if (vec4_ok) {
+          __stcs(reinterpret_cast<float4*>(o), make_float4(acc[0], acc[1], acc[2], acc[3]));
+        } else {
+#pragma unroll
+          for (int k = 0; k < REG_Z; k++)
+            if (vz0 + k < gm.dim) o[k] = acc[k];
+        }
+        written |= 1u << (cur - g0);
+      }
+    };
+
+    // the records of the next chunk are fetched while the current one is being evaluated
+    float4 pa = make_float4(0.f, 0.f, 0.f, -1.f), pb = pa, pd = pa;
+    uint4 pc = make_uint4(0u, 0u, 0u, 0u);
+    if (beg + lane < end) {
+      const Rec* rp = recs + list[beg + lane];
+      pa = rp->a; pb = rp->b; pc = rp->c; pd = rp->d;
+    }
+    for (unsigned base = beg; base < end; base += 32) {
+      unsigned n = min(32u, end - base);
+      unsigned bm = 0;
+      float4 ra = pa, rb = pb, rd = pd;
+      uint4 rc = pc;
+      if (base + 32 + lane < end) {
+        const Rec* rp = recs + list[base + 32 + lane];
+        pa = rp->a; pb = rp->b; pc = rp->c; pd = rp->d;
+      }
+      if (lane < n) {
+        CandI cd;
+        cd.a = ra;
+        cd.b = make_float4(PRECISE ? rd.z : rb.y * NEG2_LOG2E, rb.y, rb.z, BINARY ? rd.y : rd.x);
+        cd.c = make_uint4(rc.z, rc.w & 0xffffu, 0u, 0u);
+        cs[lane] = cd;
+        // columns of this region inside the atom's integer footprint, minus x-rows that are
+        // farther than the cut-off by their x distance alone
+        int lx = max((int)lo16(rc.x) - (int)x0, 0), hx = min((int)lo16(rc.y) - (int)x0, REG_X);
+        int ly = max((int)hi16(rc.x) - (int)y0, 0), hy = min((int)hi16(rc.y) - (int)y0, REG_Y);
+        unsigned ym = (hy > ly) ? (((1u << hy) - 1u) & ~((1u << ly) - 1u)) : 0u;
+#pragma unroll
+        for (int k = 0; k < REG_X; k++) {
+          float dxr = __fsub_rn(gxr[k], ra.x);
+          bool rowin = k >= lx && k < hx && __fmul_rn(dxr, dxr) <= ra.w;
+          if (rowin) bm |= ym << (8 * k);
+        }
+      }
+      __syncwarp();
+      unsigned mask = warp_transpose32(bm, lane);
+      while (mask) {
+        int i = __ffs(mask) - 1;
+        mask &= mask - 1;
+        float4 a = cs[i].a;
+        float4 bq = cs[i].b;
+        uint2 cc = *reinterpret_cast<const uint2*>(&cs[i].c);
+        int ch = (int)cc.y;
+        if (ch != cur) {
+          flush();
+          cur = ch;
+#pragma unroll
+          for (int k = 0; k < REG_Z; k++) acc[k] = 0.f;
+        }
+        float dx = __fsub_rn(gx, a.x), dy = __fsub_rn(gy, a.y);
+        float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
+        if (!(dxy2 <= a.w)) continue;
+        unsigned loz = lo16(cc.x), nz = hi16(cc.x) - loz;
+#pragma unroll
+        for (int k = 0; k < REG_Z; k++) {
+          float dz = __fsub_rn(gz[k], a.z);
+          float rsq = __fadd_rn(dxy2, __fmul_rn(dz, dz));
+          bool inz = (vz0 + k - loz) < nz;
+          if (BINARY) {
+            if (inz && rsq < bq.w) acc[k] = 1.f;
+          } else if (PRECISE) {
+            float v = density_precise(rsq, bq.x, bq.z, bq.w, A_, B_, C_);
+            if (inz) acc[k] = __fadd_rn(acc[k], v);
+          } else {
+            float g = ex2_approx(rsq * bq.x);
+            float sq = sqrt_approx(rsq * bq.y);
+            float q = fmaxf(fmaf(fmaf(A_, sq, B_), sq, C_), 0.f);
+            float v = rsq <= bq.z ? g : q;
+            acc[k] += (inz && rsq <= bq.w) ? v : 0.f;
+          }
+        }
+      }
+      __syncwarp();
+    }
+    flush();
+    // channels of this group that no atom of this column touched are zero
+    if (col_ok) {
+      for (int c = g0; c < g1; c++) {
+        if (!((written >> (c - g0)) & 1u)) {
+          float* o = ocol + (size_t)c * chan_stride;
+          if (vec4_ok) {
+            __stcs(reinterpret_cast<float4*>(o), make_float4(0.f, 0.f, 0.f, 0.f));
+          } else {
+#pragma unroll
+            for (int k = 0; k < REG_Z; k++)
+              if (vz0 + k < gm.dim) o[k] = 0.f;
+          }
+        }
+      }
+    }
+  }
+}
+
+// Atoms whose footprint spans more regions than the list capacity (far larger than the expected
+// radius) are not binned; after the main kernel one block per such atom adds its density into
+// the finished grid.  This path only exists so that any radius is handled correctly.
+template <bool BINARY, bool PRECISE>
+__global__ void __launch_bounds__(128) k_forward_big(FwdArgs F) {
+  const GMParams& gm = F.gm;
+  int bl = blockIdx.y;
+  int b = F.b0 + bl;
+  unsigned nbig = F.bigcount[bl];
+  if (nbig == 0) return;
+  float cx, cy, cz;
+  if (F.centers != nullptr) {
+    cx = F.centers[b * 3]; cy = F.centers[b * 3 + 1]; cz = F.centers[b * 3 + 2];
+  } else {
+    cx = F.center_host[0]; cy = F.center_host[1]; cz = F.center_host[2];
+  }
+  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
+  size_t dim = gm.dim;
+  for (unsigned e = blockIdx.x; e < nbig; e += gridDim.x) {
+    const Rec* rp = F.recs + (size_t)bl * F.N + F.biglist[(size_t)bl * F.N + e];
+    float4 ra = rp->a, rb = rp->b, rd = rp->d;
+    uint4 rc = rp->c;
+    unsigned lox = lo16(rc.x), loy = hi16(rc.x), hix = lo16(rc.y), hiy = hi16(rc.y);
+    unsigned loz = lo16(rc.z), hiz = hi16(rc.z);
+    unsigned nx = hix - lox, ny = hiy - loy, nz = hiz - loz;
+    float* o = F.out + ((size_t)b * F.T + (rc.w & 0xffffu)) * dim * dim * dim;
+    size_t total = (size_t)nx * ny * nz;
+    for (size_t v = threadIdx.x; v < total; v += blockDim.x) {
+      unsigned z = loz + (unsigned)(v % nz), y = loy + (unsigned)((v / nz) % ny), x = lox + (unsigned)(v / ((size_t)nz * ny));
+      float dx = __fsub_rn(voxel_coord(ox, x, gm.res), ra.x);
+      float dy = __fsub_rn(voxel_coord(oy, y, gm.res), ra.y);
+      float dz = __fsub_rn(voxel_coord(oz, z, gm.res), ra.z);
+      float rsq = __fadd_rn(__fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy)), __fmul_rn(dz, dz));
+      float* p = o + ((size_t)x * dim + y) * dim + z;
+      if (BINARY) {
+        if (rsq < rd.y) *p = 1.f;
+      } else {
+        float val = PRECISE ? density_precise(rsq, rd.z, rb.z, rd.x, gm.A, gm.B, gm.C)
+                            : density_fast(rsq, rb.y, rb.z, rd.x, gm.A, gm.B, gm.C);
+        if (val != 0.f) atomicAdd(p, val);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward
 // ---------------------------------------------------------------------------------------------
 
 struct ItemParams {
@@ -468,22 +731,25 @@ __device__ __forceinline__ ItemParams load_item(const BwdArgs& G, int bl, int b,
   return P;
 }
 
-constexpr int BWD_THREADS = 128;
+// Backward kernels: one warp per work item.  The warp first compacts the
+// columns (x,y) of the item's footprint that lie within the cut-off circle, then sweeps eight
+// columns at a time with four lanes along z each, and finally reduces with shuffles.  All lanes
+// work on the same atom, so footprints of different size do not idle each other.
+constexpr int BWD2_WARPS = 4;
+constexpr int BWD2_COLS = 256;  // compacted columns held per warp at a time
 
-// MODE 0: atom gradient (index types)          -> atom_gradients[b][a][3]
-// MODE 1: atom + type gradient (vector types)  -> partial[b][a][t][3], type_gradients[b][a][t]
-// MODE 2: relevance (index types)              -> relevance[b][a]
 template <int MODE, bool BINARY>
-__global__ void __launch_bounds__(BWD_THREADS) k_backward(BwdArgs G) {
+__global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_warp(BwdArgs G) {
   constexpr bool VEC = MODE == 1;
+  __shared__ unsigned cols_s[BWD2_WARPS][BWD2_COLS];
   const GMParams& gm = G.gm;
-  int lane = threadIdx.x & 31, sub = lane & 7;
-  int group = (blockIdx.x * BWD_THREADS + threadIdx.x) >> 3;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   int items_per_ex = VEC ? G.N * G.T : G.N;
-  bool in_range = group < G.nb * items_per_ex;
-  int bl = in_range ? group / items_per_ex : 0;
-  int item = in_range ? group - bl * items_per_ex : 0;
+  int item = blockIdx.x * BWD2_WARPS + wid;
+  int bl = blockIdx.y;
   int b = G.b0 + bl;
+  if (item >= items_per_ex) return;
+  unsigned* cols = cols_s[wid];
 
   float cx, cy, cz;
   if (G.centers != nullptr) {
@@ -492,9 +758,7 @@ __global__ void __launch_bounds__(BWD_THREADS) k_backward(BwdArgs G) {
     cx = G.center_host[0]; cy = G.center_host[1]; cz = G.center_host[2];
   }
   float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
-
   ItemParams P = load_item<VEC>(G, bl, b, item, ox, oy, oz);
-  if (!in_range) P.valid = false;
 
   size_t dim = gm.dim;
   size_t chan_off = ((size_t)b * G.T + P.chan) * dim * dim * dim;
@@ -502,55 +766,83 @@ __global__ void __launch_bounds__(BWD_THREADS) k_backward(BwdArgs G) {
   const float* dens = MODE == 2 ? G.density + chan_off : nullptr;
 
   float agx = 0.f, agy = 0.f, agz = 0.f, tg = 0.f;
-  // vector types skip the atom gradient of zero-weight channels (src/grid_maker.cpp:510-515) but
-  // still produce their type gradient
   bool want_ag = MODE == 0 || (MODE == 1 && P.w != 0.f);
   float Tcull = MODE == 0 ? P.Tcut : fmaxf(P.Tcut, BINARY ? P.Tbin : -1.f);
-  const float k4 = -4.f * P.inv_ar2, kD = gm.D * P.inv_ar2, kE = gm.E * P.inv_ar;
+  const float kexp = P.inv_ar2 * NEG2_LOG2E;
+  const float k4 = 4.f * P.inv_ar2, kD = -gm.D * P.inv_ar2, kE = -gm.E * P.inv_ar;  // sign of -(s*dv) folded in
 
   if (P.valid) {
-    for (unsigned x = P.lox; x < P.hix; x++) {
-      float dx = __fsub_rn(voxel_coord(ox, x, gm.res), P.x);
-      float dx2 = __fmul_rn(dx, dx);
-      for (unsigned y = P.loy; y < P.hiy; y++) {
+    unsigned nx = P.hix - P.lox, ny = P.hiy - P.loy;
+    unsigned ncols = nx * ny;
+    float inv_ny = 1.f / (float)ny;
+    int grp = lane >> 2, sub = lane & 3;
+    for (unsigned cbase = 0; cbase < ncols;) {
+      // ---- compact the in-circle columns of [cbase, ...) until the buffer is full ----
+      unsigned nkept = 0;
+      while (cbase < ncols && nkept + 32 <= BWD2_COLS) {
+        unsigned c = cbase + lane;
+        bool keep = false;
+        unsigned xy = 0;
+        if (c < ncols) {
+          // c / ny through a float reciprocal (exact for the footprint sizes that fit a grid)
+          unsigned xi = ncols < (1u << 20) ? (unsigned)(((float)c + 0.5f) * inv_ny) : c / ny;
+          unsigned yi = c - xi * ny;
+          unsigned x = P.lox + xi, y = P.loy + yi;
+          float dx = __fsub_rn(voxel_coord(ox, x, gm.res), P.x);
+          float dy = __fsub_rn(voxel_coord(oy, y, gm.res), P.y);
+          float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
+          keep = dxy2 <= Tcull;
+          xy = (x << 16) | y;
+        }
+        unsigned m = __ballot_sync(0xffffffffu, keep);
+        if (keep) cols[nkept + __popc(m & ((1u << lane) - 1u))] = xy;
+        nkept += __popc(m);
+        cbase += 32;
+      }
+      __syncwarp();
+      // ---- sweep: 8 columns per iteration, 4 lanes along z ----
+      for (unsigned i = grp; i < nkept; i += 8) {
+        unsigned xy = cols[i];
+        unsigned x = xy >> 16, y = xy & 0xffffu;
+        float dx = __fsub_rn(voxel_coord(ox, x, gm.res), P.x);
         float dy = __fsub_rn(voxel_coord(oy, y, gm.res), P.y);
-        float dxy2 = __fadd_rn(dx2, __fmul_rn(dy, dy));
-        if (!(dxy2 <= Tcull)) continue;
-        const float* row = diff + (x * dim + y) * dim;
-        for (unsigned z = P.loz + sub; z < P.hiz; z += 8) {
+        float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
+        size_t rowoff = ((size_t)x * dim + y) * dim;
+        const float* row = diff + rowoff;
+        for (unsigned z = P.loz + sub; z < P.hiz; z += 4) {
           float dz = __fsub_rn(voxel_coord(oz, z, gm.res), P.z);
           float rsq = __fadd_rn(dxy2, __fmul_rn(dz, dz));
+          if (!(rsq <= Tcull)) continue;
           float dv = __ldg(row + z);
           if (MODE != 2) {
-            if (want_ag && rsq <= P.Tcut && rsq > 0.f) {
-              // (d density / d dist) / dist, src/grid_maker.cu:881-896
-              float s = rsq <= P.Tg ? k4 * ex2_approx(rsq * P.inv_ar2 * NEG2_LOG2E)
-                                    : fmaf(kE, rsqrt_approx(rsq), kD);
-              float f = -(s * dv);
+            if (want_ag && rsq <= P.Tcut) {
+              // -(d density / d dist) / dist * dv, src/grid_maker.cu:881-919; rsq == 0 contributes
+              // nothing because dx = dy = dz = 0 there
+              float s = rsq <= P.Tg ? k4 * ex2_approx(rsq * kexp) : fmaf(kE, rsqrt_approx(rsq), kD);
+              float f = s * dv;
               agx = fmaf(f, dx, agx);
               agy = fmaf(f, dy, agy);
               agz = fmaf(f, dz, agz);
             }
           }
           if (MODE != 0) {
-            // relevance divides by the density grid, which amplifies any relative error of a
-            // near-zero tail value: it uses the reference's own operation order
             float v = BINARY ? (rsq < P.Tbin ? 1.f : 0.f)
                       : MODE == 2 ? density_precise(rsq, P.ar, P.Tg, P.Tcut, gm.A, gm.B, gm.C)
                                   : density_fast(rsq, P.inv_ar2, P.Tg, P.Tcut, gm.A, gm.B, gm.C);
             if (MODE == 1) {
               tg = fmaf(v, dv, tg);
             } else if (v > 0.f) {
-              float de = __ldg(dens + (x * dim + y) * dim + z);
+              float de = __ldg(dens + rowoff + z);
               if (de > 0.f) tg += __fdiv_rn(__fmul_rn(dv, v), de);
             }
           }
         }
       }
+      __syncwarp();
     }
   }
 #pragma unroll
-  for (int o = 4; o >= 1; o >>= 1) {
+  for (int o = 16; o >= 1; o >>= 1) {
     if (MODE != 2) {
       agx += __shfl_xor_sync(0xffffffffu, agx, o);
       agy += __shfl_xor_sync(0xffffffffu, agy, o);
@@ -558,7 +850,7 @@ __global__ void __launch_bounds__(BWD_THREADS) k_backward(BwdArgs G) {
     }
     if (MODE != 0) tg += __shfl_xor_sync(0xffffffffu, tg, o);
   }
-  if (in_range && sub == 0) {
+  if (lane == 0) {
     size_t ai = (size_t)b * G.N + (VEC ? item / G.T : item);
     if (MODE == 0) {
       G.atom_gradients[ai * 3] = agx;
@@ -623,10 +915,14 @@ cudaError_t launch_scan_fill(const EmitArgs& A, cudaStream_t st) {
 
 template <bool BINARY, bool PRECISE>
 static void launch_forward_t(const FwdArgs& F, dim3 grid, cudaStream_t st) {
-  if (F.vec)
+  if (F.vec) {
     k_forward<BINARY, PRECISE, true><<<grid, FWD_WARPS * 32, 0, st>>>(F);
-  else
-    k_forward<BINARY, PRECISE, false><<<grid, FWD_WARPS * 32, 0, st>>>(F);
+  } else {
+    dim3 gidx(F.nrx * F.nry * F.nrz, F.nb);
+    k_forward_index<BINARY, PRECISE><<<gidx, FWD_WARPS * 32, 0, st>>>(F);
+    dim3 gbig(min(F.N, 32), F.nb);
+    k_forward_big<BINARY, PRECISE><<<gbig, 128, 0, st>>>(F);
+  }
 }
 
 cudaError_t launch_forward(const FwdArgs& F, cudaStream_t st) {
@@ -642,21 +938,20 @@ cudaError_t launch_forward(const FwdArgs& F, cudaStream_t st) {
 }
 
 cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st) {
-  long items = (long)G.nb * G.N * (mode == 1 ? G.T : 1);
-  long threads = items * 8;
-  unsigned blocks = (unsigned)((threads + BWD_THREADS - 1) / BWD_THREADS);
-  if (blocks == 0) return cudaSuccess;
+  long items = (long)G.N * (mode == 1 ? G.T : 1);
+  if (items == 0 || G.nb == 0) return cudaSuccess;
+  dim3 grid((unsigned)((items + BWD2_WARPS - 1) / BWD2_WARPS), G.nb);
   bool bin = G.gm.binary != 0;
   if (mode == 0) {
-    k_backward<0, false><<<blocks, BWD_THREADS, 0, st>>>(G);
+    k_backward_warp<0, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
   } else if (mode == 1) {
-    if (bin) k_backward<1, true><<<blocks, BWD_THREADS, 0, st>>>(G);
-    else k_backward<1, false><<<blocks, BWD_THREADS, 0, st>>>(G);
+    if (bin) k_backward_warp<1, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    else k_backward_warp<1, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
     int n = G.nb * G.N;
     k_reduce_types<<<(n + 255) / 256, 256, 0, st>>>(G);
   } else {
-    if (bin) k_backward<2, true><<<blocks, BWD_THREADS, 0, st>>>(G);
-    else k_backward<2, false><<<blocks, BWD_THREADS, 0, st>>>(G);
+    if (bin) k_backward_warp<2, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    else k_backward_warp<2, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
   }
   return cudaGetLastError();
 }

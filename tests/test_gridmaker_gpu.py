@@ -282,3 +282,29 @@ def test_small_workspace_runs_in_passes(port):
         api._workspaces.clear()
     assert torch.equal(a != 0, b != 0)
     assert torch.allclose(a, b, rtol=1e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("binary", [False, True])
+def test_atoms_larger_than_the_radius_hint(port, binary):
+    """Atoms whose footprint exceeds the list capacity take the unbinned path; same grids."""
+    from libmolgrid_b200 import _cabi
+    g, og = gm_pair(port, resolution=0.5, dimension=11.5, binary=binary)
+    T = 5
+    coords, types, radii = cases.index_case(21, 120, T, 6.5)
+    want = port.forward_index(og, (0, 0, 0), coords, types, radii, T)
+    vc, tv, vr = cases.vector_case(22, 80, T, 6.5)
+    wantv = port.forward_vector(og, (0, 0, 0), vc, tv, vr)
+    _cabi.lib().lmg_set_max_radius_hint(0.4)
+    try:
+        out = torch.empty(g.grid_dimensions(T), device="cuda")
+        g.forward((0, 0, 0), dev(coords), dev(types), dev(radii), out)
+        outv = torch.empty(g.grid_dimensions(T), device="cuda")
+        g.forward((0, 0, 0), dev(vc), dev(tv), dev(vr), outv)
+    finally:
+        _cabi.lib().lmg_set_max_radius_hint(3.5)
+    got = out.cpu().numpy()
+    if binary:
+        assert np.array_equal(got, want)
+    else:
+        assert np.allclose(got, want, **DENS)
+    assert np.allclose(outv.cpu().numpy(), wantv, **DENS)

@@ -6,7 +6,8 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "liblmg_b200.so")
+# LMG_B200_LIB overrides the library path (for trying differently built variants)
+LIB_PATH = os.environ.get("LMG_B200_LIB") or os.path.join(HERE, "liblmg_b200.so")
 
 LMG_OK, LMG_ERR_OUT_OF_RANGE, LMG_ERR_INVALID_ARGUMENT, LMG_ERR_CUDA, LMG_ERR_WORKSPACE = range(5)
 OP_FORWARD, OP_BACKWARD, OP_BACKWARD_GRADIENTS, OP_BACKWARD_RELEVANCE = range(4)

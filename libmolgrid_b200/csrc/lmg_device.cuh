@@ -52,6 +52,7 @@ struct __align__(16) Rec {
 
 constexpr unsigned REC_VALID = 1u;     // contributes to some voxel
 constexpr unsigned REC_BIG = 2u;       // footprint spans more regions than the list capacity
+constexpr unsigned REC_ZFREE = 4u;     // no voxel outside [lo.z, hi.z) can pass the radial test
 
 // Per (example, channel) radius constants for type-indexed radii.
 struct __align__(16) ChanParam {

@@ -138,8 +138,19 @@ __global__ void __launch_bounds__(256) k_emit(EmitArgs A) {
     if (any) {
       r.a = make_float4(x, y, z, cp.q.w);
       r.b = make_float4(1.f, cp.p.x, cp.p.y, cp.p.z);
+      // If even the nearest voxel layers outside [lo.z, hi.z) are farther than the cut-off by
+      // their z distance alone, the z test of the footprint can never decide anything.
+      bool zfree = true;
+      if (loz > 0) {
+        float dzl = __fsub_rn(voxel_coord(oz, loz - 1, gm.res), z);
+        zfree = zfree && dzl <= 0.f && __fmul_rn(dzl, dzl) > cp.q.w;
+      }
+      if (hiz < gm.dim) {
+        float dzh = __fsub_rn(voxel_coord(oz, hiz, gm.res), z);
+        zfree = zfree && dzh >= 0.f && __fmul_rn(dzh, dzh) > cp.q.w;
+      }
       r.c = make_uint4(lox | (loy << 16), hix | (hiy << 16), loz | (hiz << 16),
-                       (unsigned)chan | (REC_VALID << 16));
+                       (unsigned)chan | ((REC_VALID | (zfree ? REC_ZFREE : 0u)) << 16));
       r.d = make_float4(cp.p.w, cp.q.x, cp.q.y, cp.q.z);
     }
     valid = any;
@@ -248,11 +259,23 @@ __global__ void __launch_bounds__(256) k_fill(EmitArgs A) {
   int ch = A.vec ? 0 : (int)(c.w & 0xffffu);
   for (int rx = rx0; rx <= rx1; rx++)
     for (int ry = ry0; ry <= ry1; ry++)
-      for (int rz = rz0; rz <= rz1; rz++) {
-        if (!region_in_reach(A.gm, ox, oy, oz, ra.x, ra.y, ra.z, ra.w, rx, ry, rz)) continue;
-        int reg = (rx * A.nry + ry) * A.nrz + rz;
-        unsigned p = atomicAdd(&cnt[(size_t)reg * tb + ch], 1u);
-        list[p] = (unsigned)a;
+      for (int rzb = rz0; rzb <= rz1; rzb += 4) {
+        // four regions per step: their atomics are issued before any result is consumed
+        bool in[4];
+        unsigned p[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          int rz = rzb + k;
+          in[k] = rz <= rz1 && region_in_reach(A.gm, ox, oy, oz, ra.x, ra.y, ra.z, ra.w, rx, ry, rz);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          int reg = (rx * A.nry + ry) * A.nrz + rzb + k;
+          p[k] = in[k] ? atomicAdd(&cnt[(size_t)reg * tb + ch], 1u) : 0u;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+          if (in[k]) list[p[k]] = (unsigned)a;
       }
 }
 
@@ -475,9 +498,38 @@ __device__ __forceinline__ unsigned warp_transpose32(unsigned x, int lane) {
 
 struct __align__(16) CandI {
   float4 a;  // x, y, z, Tcull
-  float4 b;  // kexp (ar when PRECISE), inv_ar2, Tg, Tcut (Tbin when BINARY)
-  uint4 c;   // lo.z|hi.z<<16, channel, unused, unused
+  float4 b;  // kexp (ar when PRECISE), 1/ar^2, Tg, Tcut (Tbin when BINARY)
+  uint4 c;   // lo.z|hi.z<<16, channel | zfree<<16, unused, unused
 };
+
+
+// Adds one atom's density at the REG_Z voxels of a lane's column.  CHECKZ applies the footprint's
+// z range [lo.z, hi.z) (zoff = first voxel - lo.z, nz = hi.z - lo.z) on top of the radial test.
+template <bool BINARY, bool PRECISE, bool CHECKZ>
+__device__ __forceinline__ void fwd_eval4(float (&acc)[REG_Z], const float (&gz)[REG_Z], float az,
+                                          float dxy2, float4 bq, float A_, float B_,
+                                          float C_, unsigned zoff, unsigned nz) {
+#pragma unroll
+  for (int k = 0; k < REG_Z; k++) {
+    float dz = __fsub_rn(gz[k], az);
+    float rsq = __fadd_rn(dxy2, __fmul_rn(dz, dz));
+    bool inz = !CHECKZ || (zoff + k) < nz;
+    if (BINARY) {
+      if (inz && rsq < bq.w) acc[k] = 1.f;
+    } else if (PRECISE) {
+      float v = density_precise(rsq, bq.x, bq.z, bq.w, A_, B_, C_);
+      if (inz) acc[k] = __fadd_rn(acc[k], v);
+    } else {
+      // the tail keeps the reference's polynomial and constants so that its rounding residue near
+      // the zero at final_radius_multiple cancels against the reference's instead of adding to it
+      float g = ex2_approx(rsq * bq.x);
+      float sq = sqrt_approx(rsq * bq.y);
+      float q = fmaxf(fmaf(fmaf(A_, sq, B_), sq, C_), 0.f);
+      float v = rsq <= bq.z ? g : q;
+      acc[k] += (inz && rsq <= bq.w) ? v : 0.f;
+    }
+  }
+}
 
 template <bool BINARY, bool PRECISE>
 __global__ void __launch_bounds__(FWD_WARPS * 32) k_forward_index(FwdArgs F) {
@@ -489,6 +541,9 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) k_forward_index(FwdArgs F) {
   int reg = blockIdx.x;
   int bl = blockIdx.y;
   int b = F.b0 + bl;
+  // (Letting one warp take all channels of a sparsely populated region was tried and is slower:
+  // the warps that leave early keep the block's registers allocated until the last one is done.)
+  const unsigned* cnt = F.cnt + (size_t)bl * F.M;
   int chans_per_warp = (F.T + FWD_WARPS - 1) / FWD_WARPS;
   int cbeg = wid * chans_per_warp, cend = min(F.T, cbeg + chans_per_warp);
   if (cbeg >= cend) return;
@@ -517,7 +572,6 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) k_forward_index(FwdArgs F) {
   for (int k = 0; k < REG_X; k++) gxr[k] = voxel_coord(ox, x0 + k, gm.res);
 
   const Rec* recs = F.recs + (size_t)bl * F.N;
-  const unsigned* cnt = F.cnt + (size_t)bl * F.M;
   const unsigned* list = F.list + (size_t)bl * F.listcap;
   size_t dim = gm.dim;
   float* outb = F.out + (size_t)b * F.T * dim * dim * dim;
@@ -571,7 +625,7 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) k_forward_index(FwdArgs F) {
         CandI cd;
         cd.a = ra;
         cd.b = make_float4(PRECISE ? rd.z : rb.y * NEG2_LOG2E, rb.y, rb.z, BINARY ? rd.y : rd.x);
-        cd.c = make_uint4(rc.z, rc.w & 0xffffu, 0u, 0u);
+        cd.c = make_uint4(rc.z, (rc.w & 0xffffu) | ((rc.w >> 16) & REC_ZFREE) << 16, 0u, 0u);
         cs[lane] = cd;
         // columns of this region inside the atom's integer footprint, minus x-rows that are
         // farther than the cut-off by their x distance alone
@@ -592,8 +646,8 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) k_forward_index(FwdArgs F) {
         mask &= mask - 1;
         float4 a = cs[i].a;
         float4 bq = cs[i].b;
-        uint2 cc = *reinterpret_cast<const uint2*>(&cs[i].c);
-        int ch = (int)cc.y;
+        uint4 cc = cs[i].c;
+        int ch = (int)(cc.y & 0xffffu);
         if (ch != cur) {
           flush();
           cur = ch;
@@ -603,24 +657,13 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) k_forward_index(FwdArgs F) {
         float dx = __fsub_rn(gx, a.x), dy = __fsub_rn(gy, a.y);
         float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
         if (!(dxy2 <= a.w)) continue;
-        unsigned loz = lo16(cc.x), nz = hi16(cc.x) - loz;
-#pragma unroll
-        for (int k = 0; k < REG_Z; k++) {
-          float dz = __fsub_rn(gz[k], a.z);
-          float rsq = __fadd_rn(dxy2, __fmul_rn(dz, dz));
-          bool inz = (vz0 + k - loz) < nz;
-          if (BINARY) {
-            if (inz && rsq < bq.w) acc[k] = 1.f;
-          } else if (PRECISE) {
-            float v = density_precise(rsq, bq.x, bq.z, bq.w, A_, B_, C_);
-            if (inz) acc[k] = __fadd_rn(acc[k], v);
-          } else {
-            float g = ex2_approx(rsq * bq.x);
-            float sq = sqrt_approx(rsq * bq.y);
-            float q = fmaxf(fmaf(fmaf(A_, sq, B_), sq, C_), 0.f);
-            float v = rsq <= bq.z ? g : q;
-            acc[k] += (inz && rsq <= bq.w) ? v : 0.f;
-          }
+        // the footprint's z range only matters for atoms flagged as needing it (exact ties at the
+        // cut-off, truncated Gaussians); everywhere else the radial test already implies it
+        if (cc.y >> 16) {
+          fwd_eval4<BINARY, PRECISE, false>(acc, gz, a.z, dxy2, bq, A_, B_, C_, 0u, 0u);
+        } else {
+          unsigned loz = lo16(cc.x);
+          fwd_eval4<BINARY, PRECISE, true>(acc, gz, a.z, dxy2, bq, A_, B_, C_, vz0 - loz, hi16(cc.x) - loz);
         }
       }
       __syncwarp();

@@ -457,12 +457,84 @@ int lmg_backward_gradients(const lmg_gridmaker* g, const lmg_atoms* a, const flo
                            const float* atom_gradients, const float* type_gradients, float* diffdiff,
                            float* atom_diffdiff, float* type_diffdiff, void* workspace,
                            size_t workspace_bytes, void* stream) {
-  (void)diff; (void)atom_gradients; (void)type_gradients; (void)diffdiff; (void)atom_diffdiff;
-  (void)type_diffdiff; (void)workspace_bytes; (void)stream;
   int rc = check_common(g, a, workspace);
   if (rc) return rc;
+  // src/grid_maker.cpp:559 and the vector-types-only overload set (include/libmolgrid/grid_maker.h:463-547)
   if (g->binary) return fail(LMG_ERR_INVALID_ARGUMENT, "Binary densities not supported");
-  return fail(LMG_ERR_INVALID_ARGUMENT, "backward_gradients is not built yet");
+  if (a->batch == 0) return LMG_OK;
+  if (a->type_vector == nullptr)
+    return fail(LMG_ERR_INVALID_ARGUMENT, "backward_gradients needs vector types");
+  if (diff == nullptr || atom_gradients == nullptr || type_gradients == nullptr || diffdiff == nullptr ||
+      atom_diffdiff == nullptr || type_diffdiff == nullptr)
+    return fail(LMG_ERR_INVALID_ARGUMENT, "backward_gradients argument missing memory");
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = (char*)workspace;
+  size_t grid_elems = (size_t)a->ntypes * g->dim * g->dim * g->dim;
+  cudaError_t e = cudaMemsetAsync(ws, 0, STATUS_BYTES, st);
+  if (e != cudaSuccess) return cuda_fail(e, "clearing status");
+  // type_diffdiff is identically zero: the density is linear in the type weights
+  e = cudaMemsetAsync(type_diffdiff, 0, (size_t)a->batch * a->max_atoms * a->ntypes * sizeof(float), st);
+  if (e != cudaSuccess) return cuda_fail(e, "zeroing type_diffdiff");
+  if (a->max_atoms == 0 || g->dim == 0) {
+    e = cudaMemsetAsync(diffdiff, 0, grid_elems * a->batch * sizeof(float), st);
+    return e == cudaSuccess ? LMG_OK : cuda_fail(e, "zeroing output");
+  }
+  Layout one = layout(g, LMG_OP_BACKWARD_GRADIENTS, 1, a->max_atoms, a->ntypes, 1);
+  int per_pass = examples_per_pass(one, workspace_bytes, a->batch);
+  if (per_pass == 0)
+    return fail(LMG_ERR_WORKSPACE, "workspace too small for one example: need " +
+                                       std::to_string(STATUS_BYTES + one.per_example) + " bytes");
+  Geometry G = geometry(g);
+  for (int b0 = 0; b0 < a->batch; b0 += per_pass) {
+    int nb = std::min(per_pass, a->batch - b0);
+    Layout L = layout(g, LMG_OP_BACKWARD_GRADIENTS, nb, a->max_atoms, a->ntypes, 1);
+    lmg::EmitArgs E;
+    fill_emit(E, g, a);
+    carve(E, L, ws, nb);
+    E.b0 = b0; E.nb = nb;
+    E.round_types = 0;
+    E.nrx = G.nrx; E.nry = G.nry; E.nrz = G.nrz; E.cap = G.cap;
+    e = cudaMemsetAsync(ws + L.cnt, 0, L.biglist - L.cnt, st);
+    if (e != cudaSuccess) return cuda_fail(e, "clearing counters");
+    e = lmg::launch_emit(E, st);
+    if (e != cudaSuccess) return cuda_fail(e, "emit");
+    e = lmg::launch_scan_fill(E, st);
+    if (e != cudaSuccess) return cuda_fail(e, "scan/fill");
+    g_launches += 3 + (g->radii_type_indexed ? 1 : 0);
+    // grid part: diffdiff
+    lmg::FwdArgs F;
+    std::memset(&F, 0, sizeof F);
+    F.gm = E.gm; F.b0 = b0; F.nb = nb; F.N = E.N; F.T = E.T;
+    F.vec = 1; F.gradgrad = 1;
+    F.vec4_ok = (g->dim % 4 == 0) && ((uintptr_t)diffdiff % 16 == 0);
+    F.atom_gradients = atom_gradients; F.type_gradients = type_gradients;
+    F.type_vector = a->type_vector;
+    F.centers = a->centers;
+    for (int i = 0; i < 3; i++) F.center_host[i] = a->center_host[i];
+    F.recs = E.recs; F.chanp = E.chanp; F.cnt = E.cnt; F.list = E.list;
+    F.bigcount = E.bigcount; F.biglist = E.biglist;
+    F.nrx = G.nrx; F.nry = G.nry; F.nrz = G.nrz; F.M = E.M; F.listcap = E.listcap;
+    F.out = diffdiff;
+    e = lmg::launch_forward(F, st);
+    if (e != cudaSuccess) return cuda_fail(e, "backward_gradients grid");
+    // atom part: atom_diffdiff
+    lmg::BwdArgs B;
+    std::memset(&B, 0, sizeof B);
+    B.gm = E.gm; B.b0 = b0; B.nb = nb; B.N = E.N; B.T = E.T;
+    B.type_vector = a->type_vector;
+    B.centers = a->centers;
+    for (int i = 0; i < 3; i++) B.center_host[i] = a->center_host[i];
+    B.recs = E.recs; B.chanp = E.chanp;
+    B.diff = diff;
+    B.atom_gradients = atom_diffdiff;
+    B.ag_in = atom_gradients; B.tg_in = type_gradients;
+    B.plain_reduce = 1;
+    B.partial = reinterpret_cast<float*>(ws + L.partial);
+    e = lmg::launch_backward(B, 3, st);
+    if (e != cudaSuccess) return cuda_fail(e, "backward_gradients atoms");
+    g_launches += 3;
+  }
+  return LMG_OK;
 }
 
 static int transform_common(const lmg_transform* t, int n, const float* in, float* out, int dotranslate,

@@ -285,15 +285,25 @@ __global__ void __launch_bounds__(256) k_fill(EmitArgs A) {
 
 constexpr int FWD_WARPS = 4;
 
-// staged candidate in shared memory (48 bytes): what the column test and the voxel loop read
+// ---------------------------------------------------------------------------------------------
+// forward, vector types (and the grid part of backward_gradients)
+//
+// One warp per region; the region's atom list is shared by all channels, so the warp loops over
+// the channels and, for each, stages the atoms that carry weight in that channel.  With
+// type-indexed radii the footprint and thresholds of an (atom, channel) pair are built here.
+// GRADGRAD evaluates, instead of the density, the derivative of the backward pass with respect
+// to the grid gradient (src/grid_maker.cpp:618-634).
+// ---------------------------------------------------------------------------------------------
+
 struct __align__(16) Cand {
   float4 a;  // x, y, z, Tcull
-  float4 b;  // w, inv_ar2 (or ar when PRECISE), Tg, Tcut
-  uint4 c;   // lo.x|lo.y<<16, hi.x|hi.y<<16, lo.z|hi.z<<16, unused
+  float4 b;  // w, inv_ar2 (or ar when PRECISE), Tg, Tcut (Tbin when BINARY)
+  uint4 c;   // lo.x|lo.y<<16, hi.x|hi.y<<16, lo.z|hi.z<<16, bits of 1/ar
+  float4 g;  // GRADGRAD: incoming atom gradient x, y, z and type gradient of this channel
 };
 
-template <bool BINARY, bool PRECISE, bool VEC>
-__global__ void __launch_bounds__(FWD_WARPS * 32) k_forward(FwdArgs F) {
+template <bool BINARY, bool PRECISE, bool GRADGRAD>
+__global__ void __launch_bounds__(FWD_WARPS * 32) k_forward_vector(FwdArgs F) {
   __shared__ Cand cand_s[FWD_WARPS][32];
   const GMParams& gm = F.gm;
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -330,149 +340,134 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) k_forward(FwdArgs F) {
   size_t dim = gm.dim;
   float* outb = F.out + (size_t)b * F.T * dim * dim * dim;
   bool vec4_ok = F.vec4_ok;
+  unsigned beg = reg == 0 ? 0u : cnt[reg - 1];
+  unsigned nlist = cnt[reg] - beg;
+  unsigned total = nlist + nbig;  // atoms too large for the lists are visited by every region
 
-  // VEC: one list per region shared by all channels; otherwise one list per (region, channel)
-  unsigned vbeg = 0, vend = 0;
-  if (VEC) {
-    vbeg = reg == 0 ? 0u : cnt[reg - 1];
-    vend = cnt[reg];
-  }
-
-  for (int c0 = 0; c0 < F.T; c0 += 32) {
-    unsigned my_end = 0, my_beg = 0;
-    if (!VEC) {
-      int c = c0 + lane;
-      if (c < F.T) {
-        size_t bin = (size_t)reg * F.T + c;
-        my_end = cnt[bin];
-        my_beg = bin == 0 ? 0u : cnt[bin - 1];
-      }
-    }
-    int cn = min(32, F.T - c0);
-    for (int cc = 0; cc < cn; cc++) {
-      int chan = c0 + cc;
-      unsigned beg, end;
-      if (VEC) {
-        beg = vbeg; end = vend;
-      } else {
-        beg = __shfl_sync(0xffffffffu, my_beg, cc);
-        end = __shfl_sync(0xffffffffu, my_end, cc);
-      }
-      float acc[REG_Z];
+  for (int chan = 0; chan < F.T; chan++) {
+    float acc[REG_Z];
 #pragma unroll
-      for (int k = 0; k < REG_Z; k++) acc[k] = 0.f;
+    for (int k = 0; k < REG_Z; k++) acc[k] = 0.f;
+    ChanParam cp;
+    if (gm.rti) cp = F.chanp[(size_t)bl * F.T + chan];
 
-      ChanParam cp;
-      if (VEC && gm.rti) cp = F.chanp[(size_t)bl * F.T + chan];
-
-      unsigned total = (end - beg) + nbig;
-      for (unsigned base = 0; base < total; base += 32) {
-        unsigned n = min(32u, total - base);
-        // ---- stage up to 32 candidates ----
-        bool have = false;
-        if (lane < n) {
-          unsigned e = base + lane;
-          unsigned ai = e < (end - beg) ? list[beg + e] : biglist[e - (end - beg)];
-          const Rec* rp = recs + ai;
-          float4 ra = rp->a, rb = rp->b;
-          uint4 rc = rp->c;
-          Cand cd;
-          bool use = true;
-          if (!VEC) {
-            // entries from the big list are not sorted by channel
-            if (e >= (end - beg)) use = (int)(rc.w & 0xffffu) == chan;
-            float Tcut = rp->d.x;
-            cd.a = ra;
-            cd.b = make_float4(1.f, PRECISE ? rp->d.z : rb.y, rb.z, Tcut);
-            if (BINARY) cd.b.w = rp->d.y;  // Tbin
-            cd.c = rc;
-          } else {
-            float w = F.type_vector[((size_t)b * F.N + ai) * F.T + chan];
-            use = w != 0.f;
-            if (!gm.rti) {
-              float Tcut = rp->d.x;
-              cd.a = ra;
-              cd.b = make_float4(w, PRECISE ? rp->d.z : rb.y, rb.z, BINARY ? rp->d.y : Tcut);
-              cd.c = rc;
-            } else {
-              // per-channel radius: footprint and thresholds of this (atom, channel)
-              unsigned lox, hix, loy, hiy, loz, hiz;
-              bounds_1d(ox, ra.x, cp.q.z, gm.res, gm.dim, lox, hix);
-              bounds_1d(oy, ra.y, cp.q.z, gm.res, gm.dim, loy, hiy);
-              bounds_1d(oz, ra.z, cp.q.z, gm.res, gm.dim, loz, hiz);
-              cd.a = make_float4(ra.x, ra.y, ra.z, cp.q.w);
-              cd.b = make_float4(w, PRECISE ? cp.q.y : cp.p.x, cp.p.y, BINARY ? cp.q.x : cp.p.w);
-              cd.c = make_uint4(lox | (loy << 16), hix | (hiy << 16), loz | (hiz << 16), 0u);
-              use = use && cp.q.y > 0.f;
-            }
-          }
-          if (!use) cd.a.w = -1.f;  // nothing passes a negative threshold
-          cs[lane] = cd;
-          have = use;
+    for (unsigned base = 0; base < total; base += 32) {
+      unsigned n = min(32u, total - base);
+      // ---- stage up to 32 candidates ----
+      bool have = false;
+      if (lane < n) {
+        unsigned e = base + lane;
+        unsigned ai = e < nlist ? list[beg + e] : biglist[e - nlist];
+        const Rec* rp = recs + ai;
+        float4 ra = rp->a, rb = rp->b;
+        uint4 rc = rp->c;
+        Cand cd;
+        size_t gi = (size_t)b * F.N + ai;
+        float w = F.type_vector[gi * F.T + chan];
+        bool use = w != 0.f;
+        if (!gm.rti) {
+          cd.a = ra;
+          cd.b = make_float4(w, PRECISE ? rp->d.z : rb.y, rb.z, BINARY ? rp->d.y : rp->d.x);
+          cd.c = make_uint4(rc.x, rc.y, rc.z, __float_as_uint(rb.w));
+        } else {
+          // per-channel radius: footprint and thresholds of this (atom, channel)
+          unsigned lox, hix, loy, hiy, loz, hiz;
+          bounds_1d(ox, ra.x, cp.q.z, gm.res, gm.dim, lox, hix);
+          bounds_1d(oy, ra.y, cp.q.z, gm.res, gm.dim, loy, hiy);
+          bounds_1d(oz, ra.z, cp.q.z, gm.res, gm.dim, loz, hiz);
+          cd.a = make_float4(ra.x, ra.y, ra.z, cp.q.w);
+          cd.b = make_float4(w, PRECISE ? cp.q.y : cp.p.x, cp.p.y, BINARY ? cp.q.x : cp.p.w);
+          cd.c = make_uint4(lox | (loy << 16), hix | (hiy << 16), loz | (hiz << 16),
+                            __float_as_uint(cp.p.z));
+          use = use && cp.q.y > 0.f;
         }
-        __syncwarp();
-        // ---- column test: bit i set when candidate i can touch this lane's z-column ----
-        unsigned mask = 0;
-        if (__any_sync(0xffffffffu, have)) {
-          for (unsigned i = 0; i < n; i++) {
-            float4 a = cs[i].a;
-            uint2 bb = *reinterpret_cast<const uint2*>(&cs[i].c);
-            float dx = __fsub_rn(gx, a.x), dy = __fsub_rn(gy, a.y);
-            float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
-            bool p = dxy2 <= a.w;
-            p = p && (vx - lo16(bb.x)) < (lo16(bb.y) - lo16(bb.x));
-            p = p && (vy - hi16(bb.x)) < (hi16(bb.y) - hi16(bb.x));
-            mask |= (p ? 1u : 0u) << i;
-          }
+        if (GRADGRAD) {
+          cd.g = make_float4(F.atom_gradients[gi * 3], F.atom_gradients[gi * 3 + 1],
+                             F.atom_gradients[gi * 3 + 2], F.type_gradients[gi * F.T + chan]);
+        } else {
+          cd.g = make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        if (!col_ok) mask = 0;
-        // ---- each lane walks its own candidates ----
-        while (mask) {
-          int i = __ffs(mask) - 1;
-          mask &= mask - 1;
-          float4 a = cs[i].a, bq = cs[i].b;
-          unsigned bz = cs[i].c.z;
+        if (!use) cd.a.w = -1.f;  // nothing passes a negative threshold
+        cs[lane] = cd;
+        have = use;
+      }
+      __syncwarp();
+      // ---- column test: bit i set when candidate i can touch this lane's z-column ----
+      unsigned mask = 0;
+      if (__any_sync(0xffffffffu, have)) {
+        for (unsigned i = 0; i < n; i++) {
+          float4 a = cs[i].a;
+          uint2 bb = *reinterpret_cast<const uint2*>(&cs[i].c);
           float dx = __fsub_rn(gx, a.x), dy = __fsub_rn(gy, a.y);
           float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
-          unsigned loz = lo16(bz), nz = hi16(bz) - loz;
+          bool p = dxy2 <= a.w;
+          p = p && (vx - lo16(bb.x)) < (lo16(bb.y) - lo16(bb.x));
+          p = p && (vy - hi16(bb.x)) < (hi16(bb.y) - hi16(bb.x));
+          mask |= (p ? 1u : 0u) << i;
+        }
+      }
+      if (!col_ok) mask = 0;
+      // ---- each lane walks its own candidates ----
+      while (mask) {
+        int i = __ffs(mask) - 1;
+        mask &= mask - 1;
+        float4 a = cs[i].a, bq = cs[i].b;
+        uint4 cc = cs[i].c;
+        float dx = __fsub_rn(gx, a.x), dy = __fsub_rn(gy, a.y);
+        float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
+        unsigned loz = lo16(cc.z), nz = hi16(cc.z) - loz;
+        float4 gg = make_float4(0.f, 0.f, 0.f, 0.f);
+        float kD = 0.f, kE = 0.f, k4 = 0.f, dotxy = 0.f;
+        if (GRADGRAD) {
+          gg = cs[i].g;
+          float inv_ar = __uint_as_float(cc.w);
+          k4 = -4.f * bq.y; kD = gm.D * bq.y; kE = gm.E * inv_ar;
+          dotxy = fmaf(dx, gg.x, dy * gg.y);
+        }
 #pragma unroll
-          for (int k = 0; k < REG_Z; k++) {
-            float dz = __fsub_rn(gz[k], a.z);
-            float rsq = __fadd_rn(dxy2, __fmul_rn(dz, dz));
-            bool inz = (vz0 + k - loz) < nz;
-            if (BINARY) {
-              bool hit = inz && rsq < bq.w;
-              if (VEC) {
-                if (hit) acc[k] = __fadd_rn(acc[k], bq.x);
-              } else {
-                if (hit) acc[k] = 1.f;
-              }
+        for (int k = 0; k < REG_Z; k++) {
+          float dz = __fsub_rn(gz[k], a.z);
+          float rsq = __fadd_rn(dxy2, __fmul_rn(dz, dz));
+          bool inz = (vz0 + k - loz) < nz;
+          if (GRADGRAD) {
+            // -(w * (d density/d dist)/dist) * (delta . atom gradient) + density * type gradient,
+            // only where the voxel is within the cut-off (the reference's isfinite test)
+            float e = ex2_approx(rsq * bq.y * NEG2_LOG2E);
+            float sq = sqrt_approx(rsq * bq.y);
+            float q = fmaxf(fmaf(fmaf(gm.A, sq, gm.B), sq, gm.C), 0.f);
+            bool gauss = rsq <= bq.z;
+            float val = gauss ? e : q;
+            float s = gauss ? k4 * e : fmaf(kE, rsqrt_approx(rsq), kD);
+            float dot = fmaf(dz, gg.z, dotxy);
+            float gval = fmaf(val, gg.w, -(bq.x * s) * (rsq > 0.f ? dot : 0.f));
+            if (inz && rsq <= bq.w) acc[k] += gval;
+          } else if (BINARY) {
+            if (inz && rsq < bq.w) acc[k] = __fadd_rn(acc[k], bq.x);
+          } else {
+            float v = PRECISE ? density_precise(rsq, bq.y, bq.z, bq.w, gm.A, gm.B, gm.C)
+                              : density_fast(rsq, bq.y, bq.z, bq.w, gm.A, gm.B, gm.C);
+            if (PRECISE) {
+              if (inz) acc[k] = __fadd_rn(acc[k], __fmul_rn(v, bq.x));
             } else {
-              float v = PRECISE ? density_precise(rsq, bq.y, bq.z, bq.w, gm.A, gm.B, gm.C)
-                                : density_fast(rsq, bq.y, bq.z, bq.w, gm.A, gm.B, gm.C);
-              if (PRECISE) {
-                if (inz) acc[k] = __fadd_rn(acc[k], __fmul_rn(v, bq.x));
-              } else {
-                acc[k] = fmaf(inz ? v : 0.f, bq.x, acc[k]);
-              }
+              acc[k] = fmaf(inz ? v : 0.f, bq.x, acc[k]);
             }
           }
         }
-        __syncwarp();
       }
+      __syncwarp();
+    }
 
-      // ---- write this channel's 4 voxels ----
-      if (col_ok) {
-        float* o = outb + (((size_t)chan * dim + vx) * dim + vy) * dim + vz0;
-        if (vec4_ok) {
-          if (vz0 + REG_Z <= gm.dim) {
-            __stcs(reinterpret_cast<float4*>(o), make_float4(acc[0], acc[1], acc[2], acc[3]));
-          }
-        } else {
-#pragma unroll
-          for (int k = 0; k < REG_Z; k++)
-            if (vz0 + k < gm.dim) o[k] = acc[k];
+    // ---- write this channel's 4 voxels ----
+    if (col_ok) {
+      float* o = outb + (((size_t)chan * dim + vx) * dim + vy) * dim + vz0;
+      if (vec4_ok) {
+        if (vz0 + REG_Z <= gm.dim) {
+          __stcs(reinterpret_cast<float4*>(o), make_float4(acc[0], acc[1], acc[2], acc[3]));
         }
+      } else {
+#pragma unroll
+        for (int k = 0; k < REG_Z; k++)
+          if (vz0 + k < gm.dim) o[k] = acc[k];
       }
     }
   }
@@ -781,9 +776,13 @@ __device__ __forceinline__ ItemParams load_item(const BwdArgs& G, int bl, int b,
 constexpr int BWD2_WARPS = 4;
 constexpr int BWD2_COLS = 256;  // compacted columns held per warp at a time
 
+// MODE 0: atom gradient (index types)          -> atom_gradients[b][a][3]
+// MODE 1: atom + type gradient (vector types)  -> partial[b][a][t][3], type_gradients[b][a][t]
+// MODE 2: relevance (index types)              -> relevance[b][a]
+// MODE 3: backward_gradients' atom term        -> partial[b][a][t][3]  (src/grid_maker.cpp:636-662)
 template <int MODE, bool BINARY>
 __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_warp(BwdArgs G) {
-  constexpr bool VEC = MODE == 1;
+  constexpr bool VEC = MODE == 1 || MODE == 3;
   __shared__ unsigned cols_s[BWD2_WARPS][BWD2_COLS];
   const GMParams& gm = G.gm;
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -809,8 +808,15 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_warp(BwdArgs G) {
   const float* dens = MODE == 2 ? G.density + chan_off : nullptr;
 
   float agx = 0.f, agy = 0.f, agz = 0.f, tg = 0.f;
-  bool want_ag = MODE == 0 || (MODE == 1 && P.w != 0.f);
-  float Tcull = MODE == 0 ? P.Tcut : fmaxf(P.Tcut, BINARY ? P.Tbin : -1.f);
+  bool want_ag = MODE == 0 || ((MODE == 1 || MODE == 3) && P.w != 0.f);
+  float Tcull = (MODE == 0 || MODE == 3) ? P.Tcut : fmaxf(P.Tcut, BINARY ? P.Tbin : -1.f);
+  float inx = 0.f, iny = 0.f, inz = 0.f, intg = 0.f;  // MODE 3: incoming gradients of this item
+  if (MODE == 3) {
+    size_t gi = (size_t)b * G.N + item / G.T;
+    inx = G.ag_in[gi * 3]; iny = G.ag_in[gi * 3 + 1]; inz = G.ag_in[gi * 3 + 2];
+    intg = G.tg_in[gi * G.T + P.chan];
+    if (!want_ag) P.valid = false;  // zero-weight channels contribute nothing (src/grid_maker.cpp:573)
+  }
   const float kexp = P.inv_ar2 * NEG2_LOG2E;
   const float k4 = 4.f * P.inv_ar2, kD = -gm.D * P.inv_ar2, kE = -gm.E * P.inv_ar;  // sign of -(s*dv) folded in
 
@@ -857,7 +863,29 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_warp(BwdArgs G) {
           float rsq = __fadd_rn(dxy2, __fmul_rn(dz, dz));
           if (!(rsq <= Tcull)) continue;
           float dv = __ldg(row + z);
-          if (MODE != 2) {
+          if (MODE == 3) {
+            // second derivatives H_ab = alpha*delta_a*delta_b + [a==b]*beta of the density
+            // (src/grid_maker.cu:812-878); delta = atom - grid point
+            float alpha, beta;
+            if (rsq <= P.Tg) {
+              float e = ex2_approx(rsq * kexp);
+              alpha = 16.f * e * P.inv_ar2 * P.inv_ar2;
+              beta = -4.f * e * P.inv_ar2;
+            } else {
+              float id = rsqrt_approx(rsq);
+              float S = fmaf(gm.D * P.inv_ar, rsq * id, gm.E);
+              beta = S * id * P.inv_ar;
+              alpha = fmaf(gm.D * P.inv_ar2, id * id, -beta * id * id);
+            }
+            float dot = fmaf(dx, inx, fmaf(dy, iny, dz * inz));
+            float wa = P.w * alpha * dot;
+            float wb = P.w * beta;
+            float tt = alpha * intg;
+            float bt = beta * intg;
+            agx = fmaf(dv, fmaf(wa, dx, fmaf(wb, inx, fmaf(tt, dx * dx, bt))), agx);
+            agy = fmaf(dv, fmaf(wa, dy, fmaf(wb, iny, fmaf(tt, dy * dy, bt))), agy);
+            agz = fmaf(dv, fmaf(wa, dz, fmaf(wb, inz, fmaf(tt, dz * dz, bt))), agz);
+          } else if (MODE != 2) {
             if (want_ag && rsq <= P.Tcut) {
               // -(d density / d dist) / dist * dv, src/grid_maker.cu:881-919; rsq == 0 contributes
               // nothing because dx = dy = dz = 0 there
@@ -868,7 +896,7 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_warp(BwdArgs G) {
               agz = fmaf(f, dz, agz);
             }
           }
-          if (MODE != 0) {
+          if (MODE == 1 || MODE == 2) {
             float v = BINARY ? (rsq < P.Tbin ? 1.f : 0.f)
                       : MODE == 2 ? density_precise(rsq, P.ar, P.Tg, P.Tcut, gm.A, gm.B, gm.C)
                                   : density_fast(rsq, P.inv_ar2, P.Tg, P.Tcut, gm.A, gm.B, gm.C);
@@ -891,7 +919,7 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_warp(BwdArgs G) {
       agy += __shfl_xor_sync(0xffffffffu, agy, o);
       agz += __shfl_xor_sync(0xffffffffu, agz, o);
     }
-    if (MODE != 0) tg += __shfl_xor_sync(0xffffffffu, tg, o);
+    if (MODE == 1 || MODE == 2) tg += __shfl_xor_sync(0xffffffffu, tg, o);
   }
   if (lane == 0) {
     size_t ai = (size_t)b * G.N + (VEC ? item / G.T : item);
@@ -899,12 +927,12 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_warp(BwdArgs G) {
       G.atom_gradients[ai * 3] = agx;
       G.atom_gradients[ai * 3 + 1] = agy;
       G.atom_gradients[ai * 3 + 2] = agz;
-    } else if (MODE == 1) {
+    } else if (MODE == 1 || MODE == 3) {
       size_t pi = (size_t)bl * G.N * G.T + item;
       G.partial[pi * 3] = agx;
       G.partial[pi * 3 + 1] = agy;
       G.partial[pi * 3 + 2] = agz;
-      G.type_gradients[ai * G.T + P.chan] = tg;
+      if (MODE == 1) G.type_gradients[ai * G.T + P.chan] = tg;
     } else {
       G.relevance[ai] = tg;
     }
@@ -924,6 +952,7 @@ __global__ void __launch_bounds__(256) k_reduce_types(BwdArgs G) {
   for (int t = 0; t < G.T; t++) {
     float wt = w[t];
     if (wt != 0.f) {
+      if (G.plain_reduce) wt = 1.f;  // backward_gradients: the weight is already inside the partial
       gx = __fadd_rn(gx, __fmul_rn(p[t * 3], wt));
       gy = __fadd_rn(gy, __fmul_rn(p[t * 3 + 1], wt));
       gz = __fadd_rn(gz, __fmul_rn(p[t * 3 + 2], wt));
@@ -959,7 +988,7 @@ cudaError_t launch_scan_fill(const EmitArgs& A, cudaStream_t st) {
 template <bool BINARY, bool PRECISE>
 static void launch_forward_t(const FwdArgs& F, dim3 grid, cudaStream_t st) {
   if (F.vec) {
-    k_forward<BINARY, PRECISE, true><<<grid, FWD_WARPS * 32, 0, st>>>(F);
+    k_forward_vector<BINARY, PRECISE, false><<<grid, FWD_WARPS * 32, 0, st>>>(F);
   } else {
     dim3 gidx(F.nrx * F.nry * F.nrz, F.nb);
     k_forward_index<BINARY, PRECISE><<<gidx, FWD_WARPS * 32, 0, st>>>(F);
@@ -971,6 +1000,10 @@ static void launch_forward_t(const FwdArgs& F, dim3 grid, cudaStream_t st) {
 cudaError_t launch_forward(const FwdArgs& F, cudaStream_t st) {
   int nreg = F.nrx * F.nry * F.nrz;
   dim3 grid((nreg + FWD_WARPS - 1) / FWD_WARPS, F.nb);
+  if (F.gradgrad) {
+    k_forward_vector<false, false, true><<<grid, FWD_WARPS * 32, 0, st>>>(F);
+    return cudaGetLastError();
+  }
   if (F.gm.binary)
     launch_forward_t<true, false>(F, grid, st);
   else if (F.precise)
@@ -981,7 +1014,7 @@ cudaError_t launch_forward(const FwdArgs& F, cudaStream_t st) {
 }
 
 cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st) {
-  long items = (long)G.N * (mode == 1 ? G.T : 1);
+  long items = (long)G.N * ((mode == 1 || mode == 3) ? G.T : 1);
   if (items == 0 || G.nb == 0) return cudaSuccess;
   dim3 grid((unsigned)((items + BWD2_WARPS - 1) / BWD2_WARPS), G.nb);
   bool bin = G.gm.binary != 0;
@@ -990,6 +1023,10 @@ cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st) {
   } else if (mode == 1) {
     if (bin) k_backward_warp<1, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
     else k_backward_warp<1, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    int n = G.nb * G.N;
+    k_reduce_types<<<(n + 255) / 256, 256, 0, st>>>(G);
+  } else if (mode == 3) {
+    k_backward_warp<3, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
     int n = G.nb * G.N;
     k_reduce_types<<<(n + 255) / 256, 256, 0, st>>>(G);
   } else {

@@ -40,6 +40,9 @@ struct FwdArgs {
   GMParams gm;
   int b0, nb, N, T;
   int vec, precise, vec4_ok;
+  int gradgrad;                  // evaluate backward_gradients' grid output instead of the density
+  const float* atom_gradients;   // [B][N][3], gradgrad only
+  const float* type_gradients;   // [B][N][T], gradgrad only
   const float* type_vector;
   const float* centers;
   float center_host[3];
@@ -68,6 +71,10 @@ struct BwdArgs {
   float* type_gradients;
   float* relevance;
   float* partial;  // [nb][N][T][3] scratch, vector types
+  // backward_gradients (mode 3): incoming gradients, and a reduction without the weight factor
+  const float* ag_in;  // [B][N][3]
+  const float* tg_in;  // [B][N][T]
+  int plain_reduce;
 };
 
 cudaError_t launch_emit(const EmitArgs& A, cudaStream_t st);

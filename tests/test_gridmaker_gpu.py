@@ -308,3 +308,36 @@ def test_atoms_larger_than_the_radius_hint(port, binary):
     else:
         assert np.allclose(got, want, **DENS)
     assert np.allclose(outv.cpu().numpy(), wantv, **DENS)
+
+
+@pytest.mark.parametrize("rti", [False, True])
+@pytest.mark.parametrize("kw", [dict(resolution=0.5, dimension=11.5),
+                                dict(resolution=0.25, dimension=5.75, gaussian_radius_multiple=-2.0)])
+def test_backward_gradients(port, kw, rti):
+    """Second-order pass against the oracle; also batched with per-example transforms."""
+    kw = dict(kw, radius_type_indexed=rti)
+    g, og = gm_pair(port, **kw)
+    T, N, B = 4, 40, 2
+    rng = np.random.default_rng(17)
+    coords = np.stack([cases.vector_case(30 + b, N, T, kw["dimension"] / 2 + 0.5, rti=rti)[0] for b in range(B)])
+    tv = np.stack([cases.vector_case(30 + b, N, T, 5, rti=rti)[1] for b in range(B)])
+    radii = np.stack([cases.vector_case(30 + b, N, T, 5, rti=rti)[2] for b in range(B)])
+    shape = (B,) + g.grid_dimensions(T)
+    diff = rng.normal(size=shape).astype(np.float32)
+    ag = rng.normal(size=(B, N, 3)).astype(np.float32)
+    tg = rng.normal(size=(B, N, T)).astype(np.float32)
+    q = cases.random_quaternion(rng, B)
+    tr = np.zeros((B, 10), np.float32)
+    tr[:, :4] = q
+    tr[:, 7:] = rng.uniform(-1, 1, (B, 3))
+    dd = torch.empty(shape, device="cuda")
+    add = torch.empty((B, N, 3), device="cuda")
+    tdd = torch.full((B, N, T), 3.0, device="cuda")
+    g.backward_gradients(dev(np.zeros((B, 3), np.float32)), dev(coords), dev(tv), dev(radii), dev(diff), dev(ag),
+                         dev(tg), dd, add, tdd, transforms=dev(tr))
+    for b in range(B):
+        moved = port.transform_forward(tr[b], coords[b])
+        wdd, wadd, wtdd = port.backward_gradients(og, (0, 0, 0), moved, tv[b], radii[b], diff[b], ag[b], tg[b])
+        grad_close(dd[b].cpu().numpy(), wdd, "diffdiff")
+        grad_close(add[b].cpu().numpy(), wadd, "atom_diffdiff")
+    assert not tdd.any()

@@ -139,6 +139,25 @@ int lmg_backward_relevance(const lmg_gridmaker* g, const lmg_atoms* atoms, const
                            const float* diff, float* relevance, void* workspace,
                            size_t workspace_bytes, void* stream);
 
+/* lmg_backward for index types without a workspace and without any allocation.
+ * No counterpart in the reference.  It exists for hosts that cannot allocate device memory for
+ * a plug-in: applications that hand the whole GPU to their own memory manager at start-up (a later
+ * cudaMalloc fails there), or that ban allocation calls from their steady-state loop because
+ * cudaMalloc may synchronise the device.  The atom records live in a fixed array inside the
+ * library image instead (about 1 MB, held by every GPU that loads the library until exit).
+ *  - batch * max_atoms must not exceed lmg_static_max_atoms() (16384); beyond that the call fails
+ *    with LMG_ERR_WORKSPACE and launches nothing.  Index types only.
+ *  - All calls on one device share that array, which keeps the previous call's contents; each
+ *    call clears the status word and rewrites every record slot first, so consecutive calls on one
+ *    stream are independent, while calls that can overlap on the GPU race and must be serialised by
+ *    the caller.
+ *  - The first call on each device resolves the array's device address; make it outside any stream
+ *    capture.
+ * Results are those of lmg_backward. */
+int lmg_backward_static(const lmg_gridmaker* g, const lmg_atoms* atoms, const float* diff,
+                        float* atom_gradients, void* stream);
+size_t lmg_static_max_atoms(void);
+
 /* out[n][3] = transform applied to in[n][3]; in-place is allowed; `t` is a host struct.
  * dotranslate == 0 rotates about the centre only.
  * Replaces Transform::forward / Transform::backward on Grid2fCUDA

@@ -200,6 +200,8 @@ bool use_precise(const lmg_gridmaker* g) {
 extern "C" {
 
 const char* lmg_last_error(void) { return g_err.c_str(); }
+// lets the library's other translation units report through lmg_last_error()
+void lmg_internal_set_error(const char* msg) { g_err = msg ? msg : ""; }
 int lmg_version(void) { return 100; }
 
 void lmg_set_random_seed(unsigned seed) { g_engine.seed(seed); }

@@ -373,7 +373,7 @@ int lmg_forward(const lmg_gridmaker* g, const lmg_atoms* a, float* out, void* wo
     ProfRec* pr = prof_begin(0, st);
     e = lmg::launch_forward(F, st);
     prof_end(pr, st);
-    g_launches += 1;
+    g_launches += vec ? 1 : 2;
     if (e != cudaSuccess) return cuda_fail(e, "forward");
   }
   return LMG_OK;

@@ -6,6 +6,9 @@ hand-written CUDA kernels reached through the C ABI of ``include/lmg_b200.h``.
 """
 from .api import (GridMaker, GridInterpolater, Transform, Quaternion, float3,  # noqa: F401
                   set_random_seed)
+from .torch_bindings import (Coords2Grid, Coords2GridFunction, BatchedCoords2GridFunction,  # noqa: F401
+                             Grid2CoordsGradientFunction)
 from . import _cabi  # noqa: F401
 
-__all__ = ["GridMaker", "GridInterpolater", "Transform", "Quaternion", "float3", "set_random_seed"]
+__all__ = ["GridMaker", "GridInterpolater", "Transform", "Quaternion", "float3", "set_random_seed",
+           "Coords2Grid", "Coords2GridFunction", "BatchedCoords2GridFunction", "Grid2CoordsGradientFunction"]

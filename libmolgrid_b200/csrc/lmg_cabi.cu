@@ -17,6 +17,7 @@ thread_local std::string g_err;
 std::default_random_engine g_engine;  // same engine type as libmolgrid::random_engine
 float g_radius_hint = 3.5f;           // largest radius*radius_scale*final_radius_multiple expected
 int g_precise = -1;                   // -1 auto, 0 fast density, 1 reference-order density
+int g_forward_mode = 1;               // 0: gather through region lists, 1: zero-fill + scatter
 
 // ---- optional per-kernel timing (bench support; off by default) --------------------------------
 // When enabled, the forward and backward kernels of each pass are bracketed by CUDA events on the
@@ -243,6 +244,7 @@ long lmg_launch_count(void) { return g_launches; }
 // Tuning knobs (not part of the reference interface).
 void lmg_set_max_radius_hint(float angstroms) { g_radius_hint = angstroms > 0 ? angstroms : 3.5f; }
 void lmg_set_precise(int mode) { g_precise = mode; }
+void lmg_set_forward_mode(int mode) { g_forward_mode = mode; }
 
 int lmg_gridmaker_init(lmg_gridmaker* g, float res, float d, int bin, int rti, float rscale, float grm) {
   if (g == nullptr) return fail(LMG_ERR_INVALID_ARGUMENT, "null settings");
@@ -342,6 +344,10 @@ int lmg_forward(const lmg_gridmaker* g, const lmg_atoms* a, float* out, void* wo
     return fail(LMG_ERR_WORKSPACE, "workspace too small for one example: need " +
                                        std::to_string(STATUS_BYTES + one.per_example) + " bytes");
   Geometry G = geometry(g);
+  if (g_forward_mode == 1) {
+    e = cudaMemsetAsync(out, 0, grid_elems * a->batch * sizeof(float), st);
+    if (e != cudaSuccess) return cuda_fail(e, "zeroing output");
+  }
   for (int b0 = 0; b0 < a->batch; b0 += per_pass) {
     int nb = std::min(per_pass, a->batch - b0);
     Layout L = layout(g, LMG_OP_FORWARD, nb, a->max_atoms, a->ntypes, vec);
@@ -350,6 +356,26 @@ int lmg_forward(const lmg_gridmaker* g, const lmg_atoms* a, float* out, void* wo
     carve(E, L, ws, nb);
     E.b0 = b0; E.nb = nb;
     E.round_types = 0;
+    if (g_forward_mode == 1) {
+      E.cnt = nullptr;  // no lists
+      e = lmg::launch_emit(E, st);
+      if (e != cudaSuccess) return cuda_fail(e, "emit");
+      lmg::BwdArgs S;
+      std::memset(&S, 0, sizeof S);
+      S.gm = E.gm; S.b0 = b0; S.nb = nb; S.N = E.N; S.T = E.T;
+      S.type_vector = a->type_vector;
+      S.centers = a->centers;
+      for (int i = 0; i < 3; i++) S.center_host[i] = a->center_host[i];
+      S.recs = E.recs; S.chanp = E.chanp;
+      S.out_grid = out;
+      S.precise = use_precise(g);
+      ProfRec* pr = prof_begin(0, st);
+      e = lmg::launch_forward_scatter(S, vec != 0, st);
+      prof_end(pr, st);
+      g_launches += 2 + ((vec && g->radii_type_indexed) ? 1 : 0);
+      if (e != cudaSuccess) return cuda_fail(e, "forward scatter");
+      continue;
+    }
     E.nrx = G.nrx; E.nry = G.nry; E.nrz = G.nrz; E.cap = G.cap;
     e = cudaMemsetAsync(ws + L.cnt, 0, L.biglist - L.cnt, st);
     if (e != cudaSuccess) return cuda_fail(e, "clearing counters");

@@ -878,7 +878,9 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_warp(BwdArgs G) {
         float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
         size_t rowoff = ((size_t)x * dim + y) * dim;
         const float* row = diff + rowoff;
-        // four z steps at a time: their loads are issued together before any is used
+        // four z steps at a time: their loads are issued together before any is used.
+        // (Restricting z to the chord of the cut-off sphere in this column was measured slower: the
+        // per-column square root and conversions cost more than the skipped steps.)
         for (unsigned zb = P.loz + sub; zb < P.hiz; zb += 16) {
           float dzv[4], rsqv[4], dvv[4];
           bool okv[4];
@@ -969,6 +971,101 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_warp(BwdArgs G) {
     } else {
       G.relevance[ai] = tg;
     }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// forward by scatter: the grid is zero-filled first, then one warp per atom (or per (atom, channel)
+// pair with vector types) sweeps the atom's footprint exactly as the backward kernel does and adds
+// its density into the grid with fire-and-forget reductions (red.global.add.f32), which resolve in
+// L2.  No lists, no per-region work: the cost is proportional to the atoms' footprints.  Binary
+// occupancy with index types needs no reduction at all (every writer stores the same 1.0).
+// ---------------------------------------------------------------------------------------------
+template <bool BINARY, bool PRECISE, bool VEC>
+__global__ void __launch_bounds__(BWD2_WARPS * 32) k_forward_scatter(BwdArgs G) {
+  __shared__ unsigned cols_s[BWD2_WARPS][BWD2_COLS];
+  const GMParams& gm = G.gm;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int items_per_ex = VEC ? G.N * G.T : G.N;
+  int item = blockIdx.x * BWD2_WARPS + wid;
+  int bl = blockIdx.y;
+  int b = G.b0 + bl;
+  if (item >= items_per_ex) return;
+  unsigned* cols = cols_s[wid];
+
+  float cx, cy, cz;
+  if (G.centers != nullptr) {
+    cx = G.centers[b * 3]; cy = G.centers[b * 3 + 1]; cz = G.centers[b * 3 + 2];
+  } else {
+    cx = G.center_host[0]; cy = G.center_host[1]; cz = G.center_host[2];
+  }
+  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
+  ItemParams P = load_item<VEC>(G, bl, b, item, ox, oy, oz);
+  if (!P.valid || (VEC && P.w == 0.f)) return;  // zero weights add nothing (src/grid_maker.cpp:229)
+
+  size_t dim = gm.dim;
+  float* out = G.out_grid + ((size_t)b * G.T + P.chan) * dim * dim * dim;
+  const float Tcull = BINARY ? P.Tbin : P.Tcut;
+  const float kexp = P.inv_ar2 * NEG2_LOG2E;
+
+  unsigned nx = P.hix - P.lox, ny = P.hiy - P.loy;
+  unsigned ncols = nx * ny;
+  float inv_ny = 1.f / (float)ny;
+  int grp = lane >> 2, sub = lane & 3;
+  for (unsigned cbase = 0; cbase < ncols;) {
+    unsigned nkept = 0;
+    while (cbase < ncols && nkept + 32 <= BWD2_COLS) {
+      unsigned c = cbase + lane;
+      bool keep = false;
+      unsigned xy = 0;
+      if (c < ncols) {
+        unsigned xi = ncols < (1u << 20) ? (unsigned)(((float)c + 0.5f) * inv_ny) : c / ny;
+        unsigned yi = c - xi * ny;
+        unsigned x = P.lox + xi, y = P.loy + yi;
+        float dx = __fsub_rn(voxel_coord(ox, x, gm.res), P.x);
+        float dy = __fsub_rn(voxel_coord(oy, y, gm.res), P.y);
+        float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
+        keep = dxy2 <= Tcull;
+        xy = (x << 16) | y;
+      }
+      unsigned m = __ballot_sync(0xffffffffu, keep);
+      if (keep) cols[nkept + __popc(m & ((1u << lane) - 1u))] = xy;
+      nkept += __popc(m);
+      cbase += 32;
+    }
+    __syncwarp();
+    for (unsigned i = grp; i < nkept; i += 8) {
+      unsigned xy = cols[i];
+      unsigned x = xy >> 16, y = xy & 0xffffu;
+      float dx = __fsub_rn(voxel_coord(ox, x, gm.res), P.x);
+      float dy = __fsub_rn(voxel_coord(oy, y, gm.res), P.y);
+      float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
+      float* row = out + ((size_t)x * dim + y) * dim;
+      for (unsigned z = P.loz + sub; z < P.hiz; z += 4) {
+        float dz = __fsub_rn(voxel_coord(oz, z, gm.res), P.z);
+        float rsq = __fadd_rn(dxy2, __fmul_rn(dz, dz));
+        if (BINARY) {
+          if (rsq < P.Tbin) {
+            if (VEC) atomicAdd(row + z, P.w);
+            else row[z] = 1.f;
+          }
+        } else {
+          if (!(rsq <= P.Tcut)) continue;
+          float v;
+          if (PRECISE) {
+            v = density_precise(rsq, P.ar, P.Tg, P.Tcut, gm.A, gm.B, gm.C);
+          } else {
+            float g = ex2_approx(rsq * kexp);
+            float sq = sqrt_approx(rsq * P.inv_ar2);
+            float q = fmaxf(fmaf(fmaf(gm.A, sq, gm.B), sq, gm.C), 0.f);
+            v = rsq <= P.Tg ? g : q;
+          }
+          if (VEC) v *= P.w;
+          if (v != 0.f) atomicAdd(row + z, v);
+        }
+      }
+    }
+    __syncwarp();
   }
 }
 
@@ -1065,6 +1162,23 @@ cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st) {
   } else {
     if (bin) k_backward_warp<2, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
     else k_backward_warp<2, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_forward_scatter(const BwdArgs& G, bool vec, cudaStream_t st) {
+  long items = (long)G.N * (vec ? G.T : 1);
+  if (items == 0 || G.nb == 0) return cudaSuccess;
+  dim3 grid((unsigned)((items + BWD2_WARPS - 1) / BWD2_WARPS), G.nb);
+  bool bin = G.gm.binary != 0;
+  if (vec) {
+    if (bin) k_forward_scatter<true, false, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    else if (G.precise) k_forward_scatter<false, true, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    else k_forward_scatter<false, false, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+  } else {
+    if (bin) k_forward_scatter<true, false, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    else if (G.precise) k_forward_scatter<false, true, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    else k_forward_scatter<false, false, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
   }
   return cudaGetLastError();
 }

@@ -75,11 +75,14 @@ struct BwdArgs {
   const float* ag_in;  // [B][N][3]
   const float* tg_in;  // [B][N][T]
   int plain_reduce;
+  float* out_grid;     // forward by scatter: [B][T][D][D][D], zero-filled before the launch
+  int precise;
 };
 
 cudaError_t launch_emit(const EmitArgs& A, cudaStream_t st);
 cudaError_t launch_scan_fill(const EmitArgs& A, cudaStream_t st);
 cudaError_t launch_forward(const FwdArgs& F, cudaStream_t st);
 cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st);
+cudaError_t launch_forward_scatter(const BwdArgs& G, bool vec, cudaStream_t st);
 
 }  // namespace lmg

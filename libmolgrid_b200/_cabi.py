@@ -80,6 +80,7 @@ EXTRA_SYMBOLS = [
     ("lmg_set_max_radius_hint", None, [ctypes.c_float]),
     ("lmg_set_precise", None, [ctypes.c_int]),
     ("lmg_set_forward_mode", None, [ctypes.c_int]),
+    ("lmg_set_quads", None, [ctypes.c_int]),
     # bench support
     ("lmg_profile_enable", ctypes.c_int, [ctypes.c_int]),
     ("lmg_profile_collect", ctypes.c_int, [ctypes.POINTER(ctypes.c_double), c_int_p]),

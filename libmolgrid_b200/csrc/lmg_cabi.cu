@@ -17,6 +17,7 @@ thread_local std::string g_err;
 std::default_random_engine g_engine;  // same engine type as libmolgrid::random_engine
 float g_radius_hint = 3.5f;           // largest radius*radius_scale*final_radius_multiple expected
 int g_precise = -1;                   // -1 auto, 0 fast density, 1 reference-order density
+int g_quads = 1;                      // aligned-quad kernels where the grid allows them
 int g_forward_mode = 1;               // 0: gather through region lists, 1: zero-fill + scatter
 
 // ---- optional per-kernel timing (bench support; off by default) --------------------------------
@@ -187,7 +188,8 @@ void carve(lmg::EmitArgs& E, const Layout& L, char* ws, int nb) {
 int examples_per_pass(const Layout& one, size_t ws_bytes, int batch) {
   if (ws_bytes < STATUS_BYTES + one.per_example) return 0;
   size_t fit = (ws_bytes - STATUS_BYTES) / one.per_example;
-  return (int)std::min<size_t>(fit, (size_t)batch);
+  // the example index is the y coordinate of every launch grid
+  return (int)std::min<size_t>(std::min<size_t>(fit, (size_t)batch), 65535);
 }
 
 bool use_precise(const lmg_gridmaker* g) {
@@ -245,6 +247,7 @@ long lmg_launch_count(void) { return g_launches; }
 void lmg_set_max_radius_hint(float angstroms) { g_radius_hint = angstroms > 0 ? angstroms : 3.5f; }
 void lmg_set_precise(int mode) { g_precise = mode; }
 void lmg_set_forward_mode(int mode) { g_forward_mode = mode; }
+void lmg_set_quads(int on) { g_quads = on; }
 
 int lmg_gridmaker_init(lmg_gridmaker* g, float res, float d, int bin, int rti, float rscale, float grm) {
   if (g == nullptr) return fail(LMG_ERR_INVALID_ARGUMENT, "null settings");
@@ -377,6 +380,7 @@ int lmg_forward(const lmg_gridmaker* g, const lmg_atoms* a, float* out, void* wo
       S.recs = E.recs; S.chanp = E.chanp;
       S.out_grid = out;
       S.precise = use_precise(g);
+      S.quads = g_quads;
       ProfRec* pr = prof_begin(0, st);
       e = lmg::launch_forward_scatter(S, vec != 0, st);
       prof_end(pr, st);
@@ -449,6 +453,7 @@ static int backward_common(const lmg_gridmaker* g, const lmg_atoms* a, int op, i
     B.diff = diff; B.density = density;
     B.atom_gradients = atom_gradients; B.type_gradients = type_gradients; B.relevance = relevance;
     B.partial = reinterpret_cast<float*>(ws + L.partial);
+    B.quads = g_quads;
     g_launches += 1 + ((vec && g->radii_type_indexed) ? 1 : 0);
     ProfRec* pr = prof_begin(1, st);
     e = lmg::launch_backward(B, mode, st);
@@ -521,6 +526,10 @@ int lmg_backward_gradients(const lmg_gridmaker* g, const lmg_atoms* a, const flo
     return fail(LMG_ERR_WORKSPACE, "workspace too small for one example: need " +
                                        std::to_string(STATUS_BYTES + one.per_example) + " bytes");
   Geometry G = geometry(g);
+  if (g_forward_mode == 1) {
+    e = cudaMemsetAsync(diffdiff, 0, grid_elems * a->batch * sizeof(float), st);
+    if (e != cudaSuccess) return cuda_fail(e, "zeroing output");
+  }
   for (int b0 = 0; b0 < a->batch; b0 += per_pass) {
     int nb = std::min(per_pass, a->batch - b0);
     Layout L = layout(g, LMG_OP_BACKWARD_GRADIENTS, nb, a->max_atoms, a->ntypes, 1);
@@ -529,6 +538,31 @@ int lmg_backward_gradients(const lmg_gridmaker* g, const lmg_atoms* a, const flo
     carve(E, L, ws, nb);
     E.b0 = b0; E.nb = nb;
     E.round_types = 0;
+    // atom part (atom_diffdiff) and, by scatter, the grid part (diffdiff)
+    lmg::BwdArgs B;
+    std::memset(&B, 0, sizeof B);
+    B.gm = E.gm; B.b0 = b0; B.nb = nb; B.N = E.N; B.T = E.T;
+    B.type_vector = a->type_vector;
+    B.centers = a->centers;
+    for (int i = 0; i < 3; i++) B.center_host[i] = a->center_host[i];
+    B.recs = E.recs; B.chanp = E.chanp;
+    B.diff = diff;
+    B.atom_gradients = atom_diffdiff;
+    B.ag_in = atom_gradients; B.tg_in = type_gradients;
+    B.plain_reduce = 1;
+    B.partial = reinterpret_cast<float*>(ws + L.partial);
+    B.out_grid = diffdiff;
+    if (g_forward_mode == 1) {
+      E.cnt = nullptr;  // no lists
+      e = lmg::launch_emit(E, st);
+      if (e != cudaSuccess) return cuda_fail(e, "emit");
+      e = lmg::launch_gradgrad_scatter(B, st);
+      if (e != cudaSuccess) return cuda_fail(e, "backward_gradients grid");
+      e = lmg::launch_backward(B, 3, st);
+      if (e != cudaSuccess) return cuda_fail(e, "backward_gradients atoms");
+      g_launches += 4 + (g->radii_type_indexed ? 1 : 0);
+      continue;
+    }
     E.nrx = G.nrx; E.nry = G.nry; E.nrz = G.nrz; E.cap = G.cap;
     e = cudaMemsetAsync(ws + L.cnt, 0, L.biglist - L.cnt, st);
     if (e != cudaSuccess) return cuda_fail(e, "clearing counters");
@@ -553,19 +587,6 @@ int lmg_backward_gradients(const lmg_gridmaker* g, const lmg_atoms* a, const flo
     F.out = diffdiff;
     e = lmg::launch_forward(F, st);
     if (e != cudaSuccess) return cuda_fail(e, "backward_gradients grid");
-    // atom part: atom_diffdiff
-    lmg::BwdArgs B;
-    std::memset(&B, 0, sizeof B);
-    B.gm = E.gm; B.b0 = b0; B.nb = nb; B.N = E.N; B.T = E.T;
-    B.type_vector = a->type_vector;
-    B.centers = a->centers;
-    for (int i = 0; i < 3; i++) B.center_host[i] = a->center_host[i];
-    B.recs = E.recs; B.chanp = E.chanp;
-    B.diff = diff;
-    B.atom_gradients = atom_diffdiff;
-    B.ag_in = atom_gradients; B.tg_in = type_gradients;
-    B.plain_reduce = 1;
-    B.partial = reinterpret_cast<float*>(ws + L.partial);
     e = lmg::launch_backward(B, 3, st);
     if (e != cudaSuccess) return cuda_fail(e, "backward_gradients atoms");
     g_launches += 3;

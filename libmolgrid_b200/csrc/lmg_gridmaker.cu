@@ -789,12 +789,79 @@ __device__ __forceinline__ ItemParams load_item(const BwdArgs& G, int bl, int b,
   return P;
 }
 
-// Backward kernels: one warp per work item.  The warp first compacts the
+// Backward and scatter-forward kernels: one warp per work item.  The warp first compacts the
 // columns (x,y) of the item's footprint that lie within the cut-off circle, then sweeps eight
 // columns at a time with four lanes along z each, and finally reduces with shuffles.  All lanes
 // work on the same atom, so footprints of different size do not idle each other.
-constexpr int BWD2_WARPS = 4;
+//
+// Everything that depends on z alone (dz, dz^2, the z factor of the Gaussian) is the same for every
+// column, so each lane keeps it in registers for its (up to) four z positions of the current chunk
+// of 16 voxels; everything that depends on (x,y) alone is computed once per column at compaction
+// time and parked in shared memory.  The inner step is then  rsq = dxy2 + dz2[k]  (the reference's
+// own association, src/grid_maker.cu:82-92), one compare, and the density arithmetic.  The Gaussian
+// is evaluated as exp(-2 dxy2/ar^2) * exp(-2 dz2/ar^2): one ex2 per column instead of one per voxel.
+// One warp per block in the backward kernels: the kernel waits on its loads of the grid gradient,
+// and a block of several warps keeps its registers until its slowest atom is done.
+#ifndef LMG_BWD_WARPS
+#define LMG_BWD_WARPS 1
+#endif
+#ifndef LMG_SCAT_WARPS
+#define LMG_SCAT_WARPS 4
+#endif
+constexpr int BWD2_WARPS = LMG_BWD_WARPS;    // warps (work items) per block, backward kernels
+constexpr int SCAT_WARPS = LMG_SCAT_WARPS;   // the same for the scatter kernels
 constexpr int BWD2_COLS = 256;  // compacted columns held per warp at a time
+constexpr int ZSTEPS = 4;       // z positions per lane and chunk; a chunk covers 4*ZSTEPS voxels
+
+struct ColBuf {
+  unsigned row[BWD2_COLS];  // x*dim + y
+  float dxy2[BWD2_COLS];    // (gx-ax)^2 + (gy-ay)^2
+};
+struct ColBufD {
+  unsigned row[BWD2_COLS];
+  float dxy2[BWD2_COLS];
+  float dx[BWD2_COLS];  // gx-ax
+  float dy[BWD2_COLS];
+};
+
+// Appends the columns of [cbase, ncols) whose squared distance in the xy plane is <= Tcull to the
+// buffer until it is (nearly) full; returns how many it holds and advances cbase.
+template <class BUF, bool WITH_D>
+__device__ __forceinline__ unsigned compact_columns(BUF& buf, const ItemParams& P, unsigned& cbase,
+                                                    unsigned ncols, unsigned ny, float inv_ny, float Tcull,
+                                                    float ox, float oy, float res, unsigned dim, int lane) {
+  unsigned nkept = 0;
+  while (cbase < ncols && nkept + 32 <= BWD2_COLS) {
+    unsigned c = cbase + lane;
+    bool keep = false;
+    unsigned x = 0, y = 0;
+    float dx = 0.f, dy = 0.f, dxy2 = 0.f;
+    if (c < ncols) {
+      // c / ny through a float reciprocal (exact for the footprint sizes that fit a grid)
+      unsigned xi = ncols < (1u << 20) ? (unsigned)(((float)c + 0.5f) * inv_ny) : c / ny;
+      unsigned yi = c - xi * ny;
+      x = P.lox + xi;
+      y = P.loy + yi;
+      dx = __fsub_rn(voxel_coord(ox, x, res), P.x);
+      dy = __fsub_rn(voxel_coord(oy, y, res), P.y);
+      dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
+      keep = dxy2 <= Tcull;
+    }
+    unsigned m = __ballot_sync(0xffffffffu, keep);
+    if (keep) {
+      unsigned slot = nkept + __popc(m & ((1u << lane) - 1u));
+      buf.row[slot] = x * dim + y;
+      buf.dxy2[slot] = dxy2;
+      if constexpr (WITH_D) {
+        buf.dx[slot] = dx;
+        buf.dy[slot] = dy;
+      }
+    }
+    nkept += __popc(m);
+    cbase += 32;
+  }
+  return nkept;
+}
 
 // MODE 0: atom gradient (index types)          -> atom_gradients[b][a][3]
 // MODE 1: atom + type gradient (vector types)  -> partial[b][a][t][3], type_gradients[b][a][t]
@@ -803,7 +870,7 @@ constexpr int BWD2_COLS = 256;  // compacted columns held per warp at a time
 template <int MODE, bool BINARY>
 __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_warp(BwdArgs G) {
   constexpr bool VEC = MODE == 1 || MODE == 3;
-  __shared__ unsigned cols_s[BWD2_WARPS][BWD2_COLS];
+  __shared__ ColBufD bufs[BWD2_WARPS];
   const GMParams& gm = G.gm;
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   int items_per_ex = VEC ? G.N * G.T : G.N;
@@ -811,7 +878,7 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_warp(BwdArgs G) {
   int bl = blockIdx.y;
   int b = G.b0 + bl;
   if (item >= items_per_ex) return;
-  unsigned* cols = cols_s[wid];
+  ColBufD& buf = bufs[wid];
 
   float cx, cy, cz;
   if (G.centers != nullptr) {
@@ -846,102 +913,99 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_warp(BwdArgs G) {
     float inv_ny = 1.f / (float)ny;
     int grp = lane >> 2, sub = lane & 3;
     for (unsigned cbase = 0; cbase < ncols;) {
-      // ---- compact the in-circle columns of [cbase, ...) until the buffer is full ----
-      unsigned nkept = 0;
-      while (cbase < ncols && nkept + 32 <= BWD2_COLS) {
-        unsigned c = cbase + lane;
-        bool keep = false;
-        unsigned xy = 0;
-        if (c < ncols) {
-          // c / ny through a float reciprocal (exact for the footprint sizes that fit a grid)
-          unsigned xi = ncols < (1u << 20) ? (unsigned)(((float)c + 0.5f) * inv_ny) : c / ny;
-          unsigned yi = c - xi * ny;
-          unsigned x = P.lox + xi, y = P.loy + yi;
-          float dx = __fsub_rn(voxel_coord(ox, x, gm.res), P.x);
-          float dy = __fsub_rn(voxel_coord(oy, y, gm.res), P.y);
-          float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
-          keep = dxy2 <= Tcull;
-          xy = (x << 16) | y;
-        }
-        unsigned m = __ballot_sync(0xffffffffu, keep);
-        if (keep) cols[nkept + __popc(m & ((1u << lane) - 1u))] = xy;
-        nkept += __popc(m);
-        cbase += 32;
-      }
+      unsigned nkept = compact_columns<ColBufD, true>(buf, P, cbase, ncols, ny, inv_ny, Tcull, ox, oy,
+                                                      gm.res, gm.dim, lane);
       __syncwarp();
-      // ---- sweep: 8 columns per iteration, 4 lanes along z ----
-      for (unsigned i = grp; i < nkept; i += 8) {
-        unsigned xy = cols[i];
-        unsigned x = xy >> 16, y = xy & 0xffffu;
-        float dx = __fsub_rn(voxel_coord(ox, x, gm.res), P.x);
-        float dy = __fsub_rn(voxel_coord(oy, y, gm.res), P.y);
-        float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
-        size_t rowoff = ((size_t)x * dim + y) * dim;
-        const float* row = diff + rowoff;
-        // four z steps at a time: their loads are issued together before any is used.
-        // (Restricting z to the chord of the cut-off sphere in this column was measured slower: the
-        // per-column square root and conversions cost more than the skipped steps.)
-        for (unsigned zb = P.loz + sub; zb < P.hiz; zb += 16) {
-          float dzv[4], rsqv[4], dvv[4];
-          bool okv[4];
+      for (unsigned zc = P.loz; zc < P.hiz; zc += 4 * ZSTEPS) {
+        // this lane's z positions of the chunk; positions past the footprint get NaN, which fails
+        // every comparison below
+        unsigned z0 = zc + sub;
+        float dzt[ZSTEPS], dz2t[ZSTEPS], ezt[ZSTEPS];
 #pragma unroll
-          for (int p = 0; p < 4; p++) {
-            unsigned zz = zb + 4 * p;
-            dzv[p] = __fsub_rn(voxel_coord(oz, zz, gm.res), P.z);
-            rsqv[p] = __fadd_rn(dxy2, __fmul_rn(dzv[p], dzv[p]));
-            okv[p] = zz < P.hiz && rsqv[p] <= Tcull;
-            dvv[p] = okv[p] ? __ldg(row + zz) : 0.f;
-          }
+        for (int k = 0; k < ZSTEPS; k++) {
+          unsigned zz = z0 + 4 * k;
+          float dz = __fsub_rn(voxel_coord(oz, zz, gm.res), P.z);
+          dzt[k] = dz;
+          dz2t[k] = zz < P.hiz ? __fmul_rn(dz, dz) : CUDART_NAN_F;
+          ezt[k] = ex2_approx(dz2t[k] * kexp);
+        }
+        for (unsigned i = grp; i < nkept; i += 8) {
+          float dxy2 = buf.dxy2[i], dx = buf.dx[i], dy = buf.dy[i];
+          size_t rowoff = (size_t)buf.row[i] * dim + z0;
+          const float* row = diff + rowoff;
+          float exy = ex2_approx(dxy2 * kexp);
+          // the loads of the four z steps are issued together before any is used.  (Fetching one
+          // column ahead was measured slower: the extra registers cost more occupancy than the
+          // deeper queue of loads gains.)
+          float rsqv[ZSTEPS], dvv[ZSTEPS];
+          bool okv[ZSTEPS];
 #pragma unroll
-          for (int p = 0; p < 4; p++) {
-          if (!okv[p]) continue;
-          unsigned z = zb + 4 * p;
-          float dz = dzv[p], rsq = rsqv[p], dv = dvv[p];
-          if (MODE == 3) {
-            // second derivatives H_ab = alpha*delta_a*delta_b + [a==b]*beta of the density
-            // (src/grid_maker.cu:812-878); delta = atom - grid point
-            float alpha, beta;
-            if (rsq <= P.Tg) {
-              float e = ex2_approx(rsq * kexp);
-              alpha = 16.f * e * P.inv_ar2 * P.inv_ar2;
-              beta = -4.f * e * P.inv_ar2;
-            } else {
-              float id = rsqrt_approx(rsq);
-              float S = fmaf(gm.D * P.inv_ar, rsq * id, gm.E);
-              beta = S * id * P.inv_ar;
-              alpha = fmaf(gm.D * P.inv_ar2, id * id, -beta * id * id);
-            }
-            float dot = fmaf(dx, inx, fmaf(dy, iny, dz * inz));
-            float wa = P.w * alpha * dot;
-            float wb = P.w * beta;
-            float tt = alpha * intg;
-            float bt = beta * intg;
-            agx = fmaf(dv, fmaf(wa, dx, fmaf(wb, inx, fmaf(tt, dx * dx, bt))), agx);
-            agy = fmaf(dv, fmaf(wa, dy, fmaf(wb, iny, fmaf(tt, dy * dy, bt))), agy);
-            agz = fmaf(dv, fmaf(wa, dz, fmaf(wb, inz, fmaf(tt, dz * dz, bt))), agz);
-          } else if (MODE != 2) {
-            if (want_ag && rsq <= P.Tcut) {
-              // -(d density / d dist) / dist * dv, src/grid_maker.cu:881-919; rsq == 0 contributes
-              // nothing because dx = dy = dz = 0 there
-              float s = rsq <= P.Tg ? k4 * ex2_approx(rsq * kexp) : fmaf(kE, rsqrt_approx(rsq), kD);
-              float f = s * dv;
-              agx = fmaf(f, dx, agx);
-              agy = fmaf(f, dy, agy);
-              agz = fmaf(f, dz, agz);
-            }
+          for (int k = 0; k < ZSTEPS; k++) {
+            rsqv[k] = __fadd_rn(dxy2, dz2t[k]);
+            okv[k] = rsqv[k] <= Tcull;
+            dvv[k] = okv[k] ? __ldg(row + 4 * k) : 0.f;
           }
-          if (MODE == 1 || MODE == 2) {
-            float v = BINARY ? (rsq < P.Tbin ? 1.f : 0.f)
-                      : MODE == 2 ? density_precise(rsq, P.ar, P.Tg, P.Tcut, gm.A, gm.B, gm.C)
-                                  : density_fast(rsq, P.inv_ar2, P.Tg, P.Tcut, gm.A, gm.B, gm.C);
-            if (MODE == 1) {
-              tg = fmaf(v, dv, tg);
-            } else if (v > 0.f) {
-              float de = __ldg(dens + rowoff + z);
-              if (de > 0.f) tg += __fdiv_rn(__fmul_rn(dv, v), de);
+          float fsum = 0.f;  // sum over the column of -(d density / d dist) / dist * dv
+#pragma unroll
+          for (int k = 0; k < ZSTEPS; k++) {
+            if (!okv[k]) continue;
+            float dz = dzt[k], rsq = rsqv[k], dv = dvv[k];
+            float g = exy * ezt[k];  // exp(-2 rsq / ar^2)
+            if (MODE == 3) {
+              // second derivatives H_ab = alpha*delta_a*delta_b + [a==b]*beta of the density
+              // (src/grid_maker.cu:812-878); delta = atom - grid point
+              float alpha, beta;
+              if (rsq <= P.Tg) {
+                alpha = 16.f * g * P.inv_ar2 * P.inv_ar2;
+                beta = -4.f * g * P.inv_ar2;
+              } else {
+                float id = rsqrt_approx(rsq);
+                float S = fmaf(gm.D * P.inv_ar, rsq * id, gm.E);
+                beta = S * id * P.inv_ar;
+                alpha = fmaf(gm.D * P.inv_ar2, id * id, -beta * id * id);
+              }
+              float dot = fmaf(dx, inx, fmaf(dy, iny, dz * inz));
+              float wa = P.w * alpha * dot;
+              float wb = P.w * beta;
+              float tt = alpha * intg;
+              float bt = beta * intg;
+              agx = fmaf(dv, fmaf(wa, dx, fmaf(wb, inx, fmaf(tt, dx * dx, bt))), agx);
+              agy = fmaf(dv, fmaf(wa, dy, fmaf(wb, iny, fmaf(tt, dy * dy, bt))), agy);
+              agz = fmaf(dv, fmaf(wa, dz, fmaf(wb, inz, fmaf(tt, dz * dz, bt))), agz);
+            } else if (MODE != 2) {
+              if (want_ag && rsq <= P.Tcut) {
+                // -(d density / d dist) / dist * dv, src/grid_maker.cu:881-919; rsq == 0 contributes
+                // nothing because dx = dy = dz = 0 there
+                float s = rsq <= P.Tg ? k4 * g : fmaf(kE, rsqrt_approx(rsq), kD);
+                float f = s * dv;
+                fsum += f;
+                agz = fmaf(f, dz, agz);
+              }
             }
+            if (MODE == 1 || MODE == 2) {
+              float v;
+              if (BINARY) {
+                v = rsq < P.Tbin ? 1.f : 0.f;
+              } else if (MODE == 2) {
+                v = density_precise(rsq, P.ar, P.Tg, P.Tcut, gm.A, gm.B, gm.C);
+              } else {
+                float sq = sqrt_approx(rsq * P.inv_ar2);
+                float q = fmaxf(fmaf(fmaf(gm.A, sq, gm.B), sq, gm.C), 0.f);
+                v = rsq <= P.Tg ? g : q;
+                v = rsq <= P.Tcut ? v : 0.f;
+              }
+              if (MODE == 1) {
+                tg = fmaf(v, dv, tg);
+              } else if (v > 0.f) {
+                float de = __ldg(dens + rowoff + 4 * k);
+                if (de > 0.f) tg += __fdiv_rn(__fmul_rn(dv, v), de);
+              }
+            }
+          }  // k
+          if (MODE == 0 || MODE == 1) {
+            agx = fmaf(fsum, dx, agx);
+            agy = fmaf(fsum, dy, agy);
           }
-          }  // p
         }
       }
       __syncwarp();
@@ -982,16 +1046,16 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_warp(BwdArgs G) {
 // occupancy with index types needs no reduction at all (every writer stores the same 1.0).
 // ---------------------------------------------------------------------------------------------
 template <bool BINARY, bool PRECISE, bool VEC>
-__global__ void __launch_bounds__(BWD2_WARPS * 32) k_forward_scatter(BwdArgs G) {
-  __shared__ unsigned cols_s[BWD2_WARPS][BWD2_COLS];
+__global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_scatter(BwdArgs G) {
+  __shared__ ColBuf bufs[SCAT_WARPS];
   const GMParams& gm = G.gm;
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   int items_per_ex = VEC ? G.N * G.T : G.N;
-  int item = blockIdx.x * BWD2_WARPS + wid;
+  int item = blockIdx.x * SCAT_WARPS + wid;
   int bl = blockIdx.y;
   int b = G.b0 + bl;
   if (item >= items_per_ex) return;
-  unsigned* cols = cols_s[wid];
+  ColBuf& buf = bufs[wid];
 
   float cx, cy, cz;
   if (G.centers != nullptr) {
@@ -1013,59 +1077,325 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_forward_scatter(BwdArgs G) 
   float inv_ny = 1.f / (float)ny;
   int grp = lane >> 2, sub = lane & 3;
   for (unsigned cbase = 0; cbase < ncols;) {
-    unsigned nkept = 0;
-    while (cbase < ncols && nkept + 32 <= BWD2_COLS) {
-      unsigned c = cbase + lane;
-      bool keep = false;
-      unsigned xy = 0;
-      if (c < ncols) {
-        unsigned xi = ncols < (1u << 20) ? (unsigned)(((float)c + 0.5f) * inv_ny) : c / ny;
-        unsigned yi = c - xi * ny;
-        unsigned x = P.lox + xi, y = P.loy + yi;
-        float dx = __fsub_rn(voxel_coord(ox, x, gm.res), P.x);
-        float dy = __fsub_rn(voxel_coord(oy, y, gm.res), P.y);
-        float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
-        keep = dxy2 <= Tcull;
-        xy = (x << 16) | y;
-      }
-      unsigned m = __ballot_sync(0xffffffffu, keep);
-      if (keep) cols[nkept + __popc(m & ((1u << lane) - 1u))] = xy;
-      nkept += __popc(m);
-      cbase += 32;
-    }
+    unsigned nkept = compact_columns<ColBuf, false>(buf, P, cbase, ncols, ny, inv_ny, Tcull, ox, oy,
+                                                    gm.res, gm.dim, lane);
     __syncwarp();
-    for (unsigned i = grp; i < nkept; i += 8) {
-      unsigned xy = cols[i];
-      unsigned x = xy >> 16, y = xy & 0xffffu;
-      float dx = __fsub_rn(voxel_coord(ox, x, gm.res), P.x);
-      float dy = __fsub_rn(voxel_coord(oy, y, gm.res), P.y);
-      float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
-      float* row = out + ((size_t)x * dim + y) * dim;
-      for (unsigned z = P.loz + sub; z < P.hiz; z += 4) {
-        float dz = __fsub_rn(voxel_coord(oz, z, gm.res), P.z);
-        float rsq = __fadd_rn(dxy2, __fmul_rn(dz, dz));
-        if (BINARY) {
-          if (rsq < P.Tbin) {
-            if (VEC) atomicAdd(row + z, P.w);
-            else row[z] = 1.f;
-          }
-        } else {
-          if (!(rsq <= P.Tcut)) continue;
-          float v;
-          if (PRECISE) {
-            v = density_precise(rsq, P.ar, P.Tg, P.Tcut, gm.A, gm.B, gm.C);
+    for (unsigned zc = P.loz; zc < P.hiz; zc += 4 * ZSTEPS) {
+      unsigned z0 = zc + sub;
+      float dz2t[ZSTEPS], ezt[ZSTEPS];
+#pragma unroll
+      for (int k = 0; k < ZSTEPS; k++) {
+        unsigned zz = z0 + 4 * k;
+        float dz = __fsub_rn(voxel_coord(oz, zz, gm.res), P.z);
+        dz2t[k] = zz < P.hiz ? __fmul_rn(dz, dz) : CUDART_NAN_F;
+        ezt[k] = (BINARY || PRECISE) ? 0.f : ex2_approx(dz2t[k] * kexp);
+      }
+      for (unsigned i = grp; i < nkept; i += 8) {
+        float dxy2 = buf.dxy2[i];
+        float* row = out + (size_t)buf.row[i] * dim + z0;
+        float exy = (BINARY || PRECISE) ? 0.f : ex2_approx(dxy2 * kexp);
+#pragma unroll
+        for (int k = 0; k < ZSTEPS; k++) {
+          float rsq = __fadd_rn(dxy2, dz2t[k]);
+          if (BINARY) {
+            if (rsq < P.Tbin) {
+              if (VEC) atomicAdd(row + 4 * k, P.w);
+              else row[4 * k] = 1.f;
+            }
           } else {
-            float g = ex2_approx(rsq * kexp);
-            float sq = sqrt_approx(rsq * P.inv_ar2);
-            float q = fmaxf(fmaf(fmaf(gm.A, sq, gm.B), sq, gm.C), 0.f);
-            v = rsq <= P.Tg ? g : q;
+            if (!(rsq <= P.Tcut)) continue;
+            float v;
+            if (PRECISE) {
+              v = density_precise(rsq, P.ar, P.Tg, P.Tcut, gm.A, gm.B, gm.C);
+            } else {
+              float sq = sqrt_approx(rsq * P.inv_ar2);
+              float q = fmaxf(fmaf(fmaf(gm.A, sq, gm.B), sq, gm.C), 0.f);
+              v = rsq <= P.Tg ? exy * ezt[k] : q;
+            }
+            if (VEC) v *= P.w;
+            if (v != 0.f) atomicAdd(row + 4 * k, v);
           }
-          if (VEC) v *= P.w;
-          if (v != 0.f) atomicAdd(row + z, v);
         }
       }
     }
     __syncwarp();
+  }
+}
+
+// Grid term of backward_gradients by scatter (src/grid_maker.cpp:618-634): per (atom, channel) with
+// non-zero weight, every voxel within the cut-off receives
+//   density * type_gradient  -  w * ((d density/d dist)/dist) * (delta . atom_gradient),
+// delta = grid point - atom.  The output is zero-filled before the launch.
+__global__ void __launch_bounds__(SCAT_WARPS * 32) k_gradgrad_scatter(BwdArgs G) {
+  __shared__ ColBufD bufs[SCAT_WARPS];
+  const GMParams& gm = G.gm;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int item = blockIdx.x * SCAT_WARPS + wid;
+  int bl = blockIdx.y;
+  int b = G.b0 + bl;
+  if (item >= G.N * G.T) return;
+  ColBufD& buf = bufs[wid];
+
+  float cx, cy, cz;
+  if (G.centers != nullptr) {
+    cx = G.centers[b * 3]; cy = G.centers[b * 3 + 1]; cz = G.centers[b * 3 + 2];
+  } else {
+    cx = G.center_host[0]; cy = G.center_host[1]; cz = G.center_host[2];
+  }
+  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
+  ItemParams P = load_item<true>(G, bl, b, item, ox, oy, oz);
+  if (!P.valid || P.w == 0.f) return;
+
+  size_t dim = gm.dim;
+  float* out = G.out_grid + ((size_t)b * G.T + P.chan) * dim * dim * dim;
+  size_t gi = (size_t)b * G.N + item / G.T;
+  const float inx = G.ag_in[gi * 3], iny = G.ag_in[gi * 3 + 1], inz = G.ag_in[gi * 3 + 2];
+  const float intg = G.tg_in[gi * G.T + P.chan];
+  const float kexp = P.inv_ar2 * NEG2_LOG2E;
+  // -w * (d density/d dist)/dist: Gaussian 4 w g / ar^2; tail -w (D/ar^2 + E/(ar dist))
+  const float k4 = 4.f * P.inv_ar2 * P.w, kD = -gm.D * P.inv_ar2 * P.w, kE = -gm.E * P.inv_ar * P.w;
+
+  unsigned nx = P.hix - P.lox, ny = P.hiy - P.loy;
+  unsigned ncols = nx * ny;
+  float inv_ny = 1.f / (float)ny;
+  int grp = lane >> 2, sub = lane & 3;
+  for (unsigned cbase = 0; cbase < ncols;) {
+    unsigned nkept = compact_columns<ColBufD, true>(buf, P, cbase, ncols, ny, inv_ny, P.Tcut, ox, oy,
+                                                    gm.res, gm.dim, lane);
+    __syncwarp();
+    for (unsigned zc = P.loz; zc < P.hiz; zc += 4 * ZSTEPS) {
+      unsigned z0 = zc + sub;
+      float dzt[ZSTEPS], dz2t[ZSTEPS], ezt[ZSTEPS];
+#pragma unroll
+      for (int k = 0; k < ZSTEPS; k++) {
+        unsigned zz = z0 + 4 * k;
+        float dz = __fsub_rn(voxel_coord(oz, zz, gm.res), P.z);
+        dzt[k] = dz * inz;
+        dz2t[k] = zz < P.hiz ? __fmul_rn(dz, dz) : CUDART_NAN_F;
+        ezt[k] = ex2_approx(dz2t[k] * kexp);
+      }
+      for (unsigned i = grp; i < nkept; i += 8) {
+        float dxy2 = buf.dxy2[i];
+        float dotxy = fmaf(buf.dx[i], inx, buf.dy[i] * iny);
+        float* row = out + (size_t)buf.row[i] * dim + z0;
+        float exy = ex2_approx(dxy2 * kexp);
+#pragma unroll
+        for (int k = 0; k < ZSTEPS; k++) {
+          float rsq = __fadd_rn(dxy2, dz2t[k]);
+          if (!(rsq <= P.Tcut)) continue;
+          float g = exy * ezt[k];
+          float sq = sqrt_approx(rsq * P.inv_ar2);
+          float q = fmaxf(fmaf(fmaf(gm.A, sq, gm.B), sq, gm.C), 0.f);
+          bool gauss = rsq <= P.Tg;
+          float val = gauss ? g : q;
+          float s = gauss ? k4 * g : fmaf(kE, rsqrt_approx(rsq), kD);
+          float dot = rsq > 0.f ? dotxy + dzt[k] : 0.f;
+          float gval = fmaf(val, intg, s * dot);
+          if (gval != 0.f) atomicAdd(row + 4 * k, gval);
+        }
+      }
+    }
+    __syncwarp();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Quad kernels: the same work items, for grids whose rows are 16-byte aligned (dim % 4 == 0 and an
+// aligned base).  Here a lane owns a whole column (x,y) and walks it in aligned quads of four z
+// voxels: the forward adds a quad with one red.global.add.v4.f32, the backward reads it with one
+// 16-byte load, so a warp has 32 columns x 4 quads in flight per round trip to memory instead of
+// 8 columns x 4 voxels.  What depends on z alone sits in a small shared table per warp (one pass
+// covers 32 z positions from the aligned start of the footprint).
+// ---------------------------------------------------------------------------------------------
+constexpr int QPASS = 8;  // quads per pass
+
+struct __align__(16) ZTabs {
+  float4 dz2[QPASS];  // (gz-az)^2, NaN outside [loz, hiz)
+  float4 ez[QPASS];   // exp(-2 dz2 / ar^2)
+  float4 dz[QPASS];   // gz-az
+};
+
+__device__ __forceinline__ void fill_ztabs(ZTabs& zt, unsigned zc, const ItemParams& P, float oz, float res,
+                                           float kexp, int lane) {
+  unsigned zz = zc + lane;
+  float dz = __fsub_rn(voxel_coord(oz, zz, res), P.z);
+  bool in = zz >= P.loz && zz < P.hiz;
+  float d2 = in ? __fmul_rn(dz, dz) : CUDART_NAN_F;
+  reinterpret_cast<float*>(zt.dz2)[lane] = d2;
+  reinterpret_cast<float*>(zt.ez)[lane] = ex2_approx(d2 * kexp);
+  reinterpret_cast<float*>(zt.dz)[lane] = dz;
+}
+
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads(BwdArgs G) {
+  __shared__ ColBuf bufs[SCAT_WARPS];
+  __shared__ ZTabs ztabs[SCAT_WARPS];
+  const GMParams& gm = G.gm;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int items_per_ex = VEC ? G.N * G.T : G.N;
+  int item = blockIdx.x * SCAT_WARPS + wid;
+  int bl = blockIdx.y;
+  int b = G.b0 + bl;
+  if (item >= items_per_ex) return;
+  ColBuf& buf = bufs[wid];
+  ZTabs& zt = ztabs[wid];
+
+  float cx, cy, cz;
+  if (G.centers != nullptr) {
+    cx = G.centers[b * 3]; cy = G.centers[b * 3 + 1]; cz = G.centers[b * 3 + 2];
+  } else {
+    cx = G.center_host[0]; cy = G.center_host[1]; cz = G.center_host[2];
+  }
+  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
+  ItemParams P = load_item<VEC>(G, bl, b, item, ox, oy, oz);
+  if (!P.valid || (VEC && P.w == 0.f)) return;  // zero weights add nothing (src/grid_maker.cpp:229)
+
+  size_t dim = gm.dim;
+  float* out = G.out_grid + ((size_t)b * G.T + P.chan) * dim * dim * dim;
+  const float kexp = P.inv_ar2 * NEG2_LOG2E;
+  const float A = gm.A, B = gm.B, C = gm.C;
+
+  unsigned nx = P.hix - P.lox, ny = P.hiy - P.loy;
+  unsigned ncols = nx * ny;
+  float inv_ny = 1.f / (float)ny;
+  for (unsigned cbase = 0; cbase < ncols;) {
+    unsigned nkept = compact_columns<ColBuf, false>(buf, P, cbase, ncols, ny, inv_ny, P.Tcut, ox, oy,
+                                                    gm.res, gm.dim, lane);
+    for (unsigned zc = P.loz & ~3u; zc < P.hiz; zc += 4 * QPASS) {
+      __syncwarp();
+      fill_ztabs(zt, zc, P, oz, gm.res, kexp, lane);
+      __syncwarp();
+      unsigned nq = min((unsigned)QPASS, (P.hiz - zc + 3) >> 2);
+      for (unsigned c0 = 0; c0 < nkept; c0 += 32) {
+        unsigned i = c0 + lane;
+        bool have = i < nkept;
+        float dxy2 = have ? buf.dxy2[i] : CUDART_NAN_F;  // NaN fails every test below
+        float* row = out + (size_t)(have ? buf.row[i] : 0u) * dim + zc;
+        float exy = ex2_approx(dxy2 * kexp);
+        for (unsigned q = 0; q < nq; q++) {
+          float4 d2 = zt.dz2[q], e = zt.ez[q];
+          float d2v[4] = {d2.x, d2.y, d2.z, d2.w}, ev[4] = {e.x, e.y, e.z, e.w}, v[4];
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            float rsq = __fadd_rn(dxy2, d2v[j]);
+            float sq = sqrt_approx(rsq * P.inv_ar2);
+            float qd = fmaxf(fmaf(fmaf(A, sq, B), sq, C), 0.f);
+            float val = rsq <= P.Tg ? exy * ev[j] : qd;
+            val = rsq <= P.Tcut ? val : 0.f;
+            v[j] = VEC ? val * P.w : val;
+          }
+          unsigned any = __float_as_uint(v[0]) | __float_as_uint(v[1]) | __float_as_uint(v[2]) |
+                         __float_as_uint(v[3]);
+          if (any != 0u) red_add_v4(row + 4 * q, v[0], v[1], v[2], v[3]);
+        }
+      }
+    }
+    __syncwarp();
+  }
+}
+
+// backward, index types (MODE 0 of k_backward_warp) on aligned quads
+__global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads(BwdArgs G) {
+  __shared__ ColBufD bufs[BWD2_WARPS];
+  __shared__ ZTabs ztabs[BWD2_WARPS];
+  const GMParams& gm = G.gm;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int item = blockIdx.x * BWD2_WARPS + wid;
+  int bl = blockIdx.y;
+  int b = G.b0 + bl;
+  if (item >= G.N) return;
+  ColBufD& buf = bufs[wid];
+  ZTabs& zt = ztabs[wid];
+
+  float cx, cy, cz;
+  if (G.centers != nullptr) {
+    cx = G.centers[b * 3]; cy = G.centers[b * 3 + 1]; cz = G.centers[b * 3 + 2];
+  } else {
+    cx = G.center_host[0]; cy = G.center_host[1]; cz = G.center_host[2];
+  }
+  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
+  ItemParams P = load_item<false>(G, bl, b, item, ox, oy, oz);
+
+  size_t dim = gm.dim;
+  const float* diff = G.diff + ((size_t)b * G.T + P.chan) * dim * dim * dim;
+  float agx = 0.f, agy = 0.f, agz = 0.f;
+  const float kexp = P.inv_ar2 * NEG2_LOG2E;
+  const float k4 = 4.f * P.inv_ar2, kD = -gm.D * P.inv_ar2, kE = -gm.E * P.inv_ar;
+
+  if (P.valid) {
+    unsigned nx = P.hix - P.lox, ny = P.hiy - P.loy;
+    unsigned ncols = nx * ny;
+    float inv_ny = 1.f / (float)ny;
+    for (unsigned cbase = 0; cbase < ncols;) {
+      unsigned nkept = compact_columns<ColBufD, true>(buf, P, cbase, ncols, ny, inv_ny, P.Tcut, ox, oy,
+                                                      gm.res, gm.dim, lane);
+      for (unsigned zc = P.loz & ~3u; zc < P.hiz; zc += 4 * QPASS) {
+        __syncwarp();
+        fill_ztabs(zt, zc, P, oz, gm.res, kexp, lane);
+        __syncwarp();
+        unsigned nq = min((unsigned)QPASS, (P.hiz - zc + 3) >> 2);
+        for (unsigned c0 = 0; c0 < nkept; c0 += 32) {
+          unsigned i = c0 + lane;
+          bool have = i < nkept;
+          float dxy2 = have ? buf.dxy2[i] : CUDART_NAN_F;
+          float dx = have ? buf.dx[i] : 0.f, dy = have ? buf.dy[i] : 0.f;
+          const float4* row = reinterpret_cast<const float4*>(diff + (size_t)(have ? buf.row[i] : 0u) * dim + zc);
+          float exy = ex2_approx(dxy2 * kexp);
+          float fsum = 0.f;
+          for (unsigned q0 = 0; q0 < nq; q0 += 4) {
+            // up to four quads of the column are requested together, then used
+            float4 dv[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+              dv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (q0 + u < nq) {
+                float4 d2 = zt.dz2[q0 + u];
+                float lo = fminf(fminf(d2.x, d2.y), fminf(d2.z, d2.w));  // fminf skips the NaN entries
+                if (__fadd_rn(dxy2, lo) <= P.Tcut) dv[u] = __ldg(row + q0 + u);
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+              if (q0 + u < nq) {
+                float4 d2 = zt.dz2[q0 + u], e = zt.ez[q0 + u], dz = zt.dz[q0 + u];
+                float d2v[4] = {d2.x, d2.y, d2.z, d2.w}, ev[4] = {e.x, e.y, e.z, e.w};
+                float dzv[4] = {dz.x, dz.y, dz.z, dz.w}, dvv[4] = {dv[u].x, dv[u].y, dv[u].z, dv[u].w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                  float rsq = __fadd_rn(dxy2, d2v[j]);
+                  // -(d density / d dist) / dist * dv, src/grid_maker.cu:881-919; rsq == 0 contributes
+                  // nothing because dx = dy = dz = 0 there
+                  float sg = rsq <= P.Tg ? k4 * (exy * ev[j]) : fmaf(kE, rsqrt_approx(rsq), kD);
+                  float f = rsq <= P.Tcut ? sg * dvv[j] : 0.f;
+                  fsum += f;
+                  agz = fmaf(f, dzv[j], agz);
+                }
+              }
+            }
+          }
+          agx = fmaf(fsum, dx, agx);
+          agy = fmaf(fsum, dy, agy);
+        }
+      }
+      __syncwarp();
+    }
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) {
+    agx += __shfl_xor_sync(0xffffffffu, agx, o);
+    agy += __shfl_xor_sync(0xffffffffu, agy, o);
+    agz += __shfl_xor_sync(0xffffffffu, agz, o);
+  }
+  if (lane == 0) {
+    size_t ai = (size_t)b * G.N + item;
+    G.atom_gradients[ai * 3] = agx;
+    G.atom_gradients[ai * 3 + 1] = agy;
+    G.atom_gradients[ai * 3 + 2] = agz;
   }
 }
 
@@ -1149,7 +1479,10 @@ cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st) {
   dim3 grid((unsigned)((items + BWD2_WARPS - 1) / BWD2_WARPS), G.nb);
   bool bin = G.gm.binary != 0;
   if (mode == 0) {
-    k_backward_warp<0, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    if (G.quads && G.gm.dim % 4 == 0 && (uintptr_t)G.diff % 16 == 0)
+      k_backward_quads<<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    else
+      k_backward_warp<0, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
   } else if (mode == 1) {
     if (bin) k_backward_warp<1, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
     else k_backward_warp<1, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
@@ -1166,19 +1499,32 @@ cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st) {
   return cudaGetLastError();
 }
 
+cudaError_t launch_gradgrad_scatter(const BwdArgs& G, cudaStream_t st) {
+  long items = (long)G.N * G.T;
+  if (items == 0 || G.nb == 0) return cudaSuccess;
+  dim3 grid((unsigned)((items + SCAT_WARPS - 1) / SCAT_WARPS), G.nb);
+  k_gradgrad_scatter<<<grid, SCAT_WARPS * 32, 0, st>>>(G);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_forward_scatter(const BwdArgs& G, bool vec, cudaStream_t st) {
   long items = (long)G.N * (vec ? G.T : 1);
   if (items == 0 || G.nb == 0) return cudaSuccess;
-  dim3 grid((unsigned)((items + BWD2_WARPS - 1) / BWD2_WARPS), G.nb);
+  dim3 grid((unsigned)((items + SCAT_WARPS - 1) / SCAT_WARPS), G.nb);
   bool bin = G.gm.binary != 0;
+  if (G.quads && !bin && !G.precise && G.gm.dim % 4 == 0 && (uintptr_t)G.out_grid % 16 == 0) {
+    if (vec) k_forward_quads<true><<<grid, SCAT_WARPS * 32, 0, st>>>(G);
+    else k_forward_quads<false><<<grid, SCAT_WARPS * 32, 0, st>>>(G);
+    return cudaGetLastError();
+  }
   if (vec) {
-    if (bin) k_forward_scatter<true, false, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
-    else if (G.precise) k_forward_scatter<false, true, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
-    else k_forward_scatter<false, false, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    if (bin) k_forward_scatter<true, false, true><<<grid, SCAT_WARPS * 32, 0, st>>>(G);
+    else if (G.precise) k_forward_scatter<false, true, true><<<grid, SCAT_WARPS * 32, 0, st>>>(G);
+    else k_forward_scatter<false, false, true><<<grid, SCAT_WARPS * 32, 0, st>>>(G);
   } else {
-    if (bin) k_forward_scatter<true, false, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
-    else if (G.precise) k_forward_scatter<false, true, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
-    else k_forward_scatter<false, false, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    if (bin) k_forward_scatter<true, false, false><<<grid, SCAT_WARPS * 32, 0, st>>>(G);
+    else if (G.precise) k_forward_scatter<false, true, false><<<grid, SCAT_WARPS * 32, 0, st>>>(G);
+    else k_forward_scatter<false, false, false><<<grid, SCAT_WARPS * 32, 0, st>>>(G);
   }
   return cudaGetLastError();
 }

@@ -77,6 +77,7 @@ struct BwdArgs {
   int plain_reduce;
   float* out_grid;     // forward by scatter: [B][T][D][D][D], zero-filled before the launch
   int precise;
+  int quads;           // rows are walked in aligned quads of four voxels when the grid allows it
 };
 
 cudaError_t launch_emit(const EmitArgs& A, cudaStream_t st);
@@ -84,5 +85,6 @@ cudaError_t launch_scan_fill(const EmitArgs& A, cudaStream_t st);
 cudaError_t launch_forward(const FwdArgs& F, cudaStream_t st);
 cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st);
 cudaError_t launch_forward_scatter(const BwdArgs& G, bool vec, cudaStream_t st);
+cudaError_t launch_gradgrad_scatter(const BwdArgs& G, cudaStream_t st);
 
 }  // namespace lmg

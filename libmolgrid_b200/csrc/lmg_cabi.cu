@@ -59,6 +59,12 @@ lmg::GMParams to_params(const lmg_gridmaker* g) {
   p.G = g->gaussian_radius_multiple;
   p.finalm = g->final_radius_multiple;
   p.A = g->A; p.B = g->B; p.C = g->C; p.D = g->D; p.E = g->E;
+  {
+    double G = g->gaussian_radius_multiple, eg = std::exp(-G * G);
+    bool truncated = g->final_radius_multiple == g->gaussian_radius_multiple;
+    p.ta = truncated ? 0.f : (float)(2.0 * G * eg);
+    p.tb = truncated ? 0.f : (float)((1.0 + 2.0 * G * G) * eg);
+  }
   p.dim = g->dim;
   p.binary = g->binary;
   p.rti = g->radii_type_indexed;

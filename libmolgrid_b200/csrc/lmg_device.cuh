@@ -26,6 +26,10 @@ constexpr int REG_Z = 4;
 struct GMParams {
   float res, half, rscale, G, finalm;
   float A, B, C, D, E;
+  // The tail polynomial A dr^2 + B dr + C has a double root at dr = final_radius_multiple, so it
+  // equals (ta*dr - tb)^2 with ta = 2G e^{-G^2}, tb = (1+2G^2) e^{-G^2}; min(ta*dr - tb, 0)^2 is
+  // then also zero beyond the cut-off.  Both are 0 for a truncated Gaussian (no tail).
+  float ta, tb;
   unsigned dim;
   int binary, rti;
 };

@@ -1258,7 +1258,7 @@ __global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads(BwdArgs G) {
   size_t dim = gm.dim;
   float* out = G.out_grid + ((size_t)b * G.T + P.chan) * dim * dim * dim;
   const float kexp = P.inv_ar2 * NEG2_LOG2E;
-  const float A = gm.A, B = gm.B, C = gm.C;
+  const float ta = gm.ta, ntb = -gm.tb;
 
   unsigned nx = P.hix - P.lox, ny = P.hiy - P.loy;
   unsigned ncols = nx * ny;
@@ -1283,10 +1283,9 @@ __global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads(BwdArgs G) {
 #pragma unroll
           for (int j = 0; j < 4; j++) {
             float rsq = __fadd_rn(dxy2, d2v[j]);
-            float sq = sqrt_approx(rsq * P.inv_ar2);
-            float qd = fmaxf(fmaf(fmaf(A, sq, B), sq, C), 0.f);
-            float val = rsq <= P.Tg ? exy * ev[j] : qd;
-            val = rsq <= P.Tcut ? val : 0.f;
+            // tail (ta*dr - tb)^2 clamped to zero beyond the cut-off; a NaN rsq gives zero too
+            float tq = fminf(fmaf(ta, sqrt_approx(rsq * P.inv_ar2), ntb), 0.f);
+            float val = rsq <= P.Tg ? exy * ev[j] : tq * tq;
             v[j] = VEC ? val * P.w : val;
           }
           unsigned any = __float_as_uint(v[0]) | __float_as_uint(v[1]) | __float_as_uint(v[2]) |
@@ -1345,7 +1344,7 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads(BwdArgs G) {
           float dxy2 = have ? buf.dxy2[i] : CUDART_NAN_F;
           float dx = have ? buf.dx[i] : 0.f, dy = have ? buf.dy[i] : 0.f;
           const float4* row = reinterpret_cast<const float4*>(diff + (size_t)(have ? buf.row[i] : 0u) * dim + zc);
-          float exy = ex2_approx(dxy2 * kexp);
+          float exy4 = k4 * ex2_approx(dxy2 * kexp);
           float fsum = 0.f;
           for (unsigned q0 = 0; q0 < nq; q0 += 4) {
             // up to four quads of the column are requested together, then used
@@ -1370,7 +1369,7 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads(BwdArgs G) {
                   float rsq = __fadd_rn(dxy2, d2v[j]);
                   // -(d density / d dist) / dist * dv, src/grid_maker.cu:881-919; rsq == 0 contributes
                   // nothing because dx = dy = dz = 0 there
-                  float sg = rsq <= P.Tg ? k4 * (exy * ev[j]) : fmaf(kE, rsqrt_approx(rsq), kD);
+                  float sg = rsq <= P.Tg ? exy4 * ev[j] : fmaf(kE, rsqrt_approx(rsq), kD);
                   float f = rsq <= P.Tcut ? sg * dvv[j] : 0.f;
                   fsum += f;
                   agz = fmaf(f, dzv[j], agz);

@@ -40,8 +40,11 @@ SEED = 1001
 METRIC = "examples/s gridded (28x48^3 fp32) fwd+bwd"
 WORKLOAD = ("batch 50 x [2000,4000] index-typed atoms (70% in a 4A blob), 28x48^3 @0.5A, "
             "forward with fused per-example rotation+translation, then backward with N(0,1) grid gradient")
-# dram bytes per example of the dominant kernel from an ncu capture (profiles/), or None
-NCU_TRAFFIC_PER_EXAMPLE = {}
+# dram bytes per example from the ncu captures summarised under profiles/ (batch 12, scaled per
+# example: every example's grids are separate and larger than what L2 keeps, so traffic grows in
+# proportion).  forward = the fill's own 12,386,304 B + the scatter kernel's 6.46 MB of read-modify-
+# write on the sectors atoms touch; backward = the touched part of the grid gradient.
+NCU_TRAFFIC_PER_EXAMPLE = {"forward": 12386304 + 6.46e6, "backward": 6.85e6}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -278,8 +281,8 @@ def run_gpu_arm(args, rank, world, local_rank):
     # the forward pass is a zero fill of the grids plus the scatter kernel that adds the densities
     # into them; its algorithmic bytes (one write of every grid) are charged to the pair
     fill_ms = kms[2] / kcount[2] if kcount[2] else 0.0
-    for k, name, nbytes in ((0, "forward (zero fill + k_forward_scatter)", fwd_bytes),
-                            (1, "backward (k_backward_warp)", bwd_bytes)):
+    for k, name, nbytes in ((0, "forward (zero fill + k_forward_quads)", fwd_bytes),
+                            (1, "backward (k_backward_quads)", bwd_bytes)):
         if kcount[k]:
             avg_ms = kms[k] / kcount[k] + (fill_ms if k == 0 else 0.0)
             kern.append({"kernel": name, "launches": int(kcount[k]), "avg_ms": avg_ms,

@@ -12,6 +12,7 @@ import numpy as np
 import torch
 
 from . import _cabi
+from . import grids as _grids
 from ._cabi import check
 
 
@@ -120,6 +121,7 @@ class _Arg(object):
 
     def __init__(self, obj, device, ndim, name, output=False):
         self.host = None
+        obj = _grids.operand_tensor(obj)
         if isinstance(obj, np.ndarray):
             if obj.dtype != np.float32 or not obj.flags["C_CONTIGUOUS"]:
                 raise ValueError("%s: numpy arrays must be C-contiguous float32" % name)
@@ -138,7 +140,7 @@ class _Arg(object):
                 self.host = obj
                 t = self._stage(obj, device, output)
         else:
-            raise TypeError("%s: expected a torch tensor or numpy array" % name)
+            raise TypeError("%s: expected a Grid, MGrid, torch tensor or numpy array" % name)
         if t.dim() != ndim:
             raise TypeError("%s: expected %d dimensions, got %d" % (name, ndim, t.dim()))
         self.t = t
@@ -243,11 +245,40 @@ class Transform(object):
         check(fn(ctypes.byref(s), int(i.t.shape[0]), i.ptr, o.ptr, int(bool(dotranslate)), _stream_ptr(dev)))
         o.finish()
 
+    def _apply_sets(self, fn, inp, out, dotranslate):
+        """CoordinateSet and Example overloads (src/transform.cpp:35-55): only coordinates change;
+        types and radii are copied when ``out`` is another object."""
+        from .coordinates import CoordinateSet, Example
+        if isinstance(inp, Example):
+            if not isinstance(out, Example):
+                raise TypeError("Example input needs an Example output")
+            if out is not inp:
+                out.coord_sets = [s.clone() for s in inp.coord_sets]
+                out.labels, out.group, out.seqcont = list(inp.labels), inp.group, inp.seqcont
+            for s in out.coord_sets:
+                self._apply_sets(fn, s, s, dotranslate)
+            return True
+        if isinstance(inp, CoordinateSet):
+            if not isinstance(out, CoordinateSet):
+                raise TypeError("CoordinateSet input needs a CoordinateSet output")
+            if out is not inp:
+                c = inp.clone()
+                out.coords, out.type_index, out.type_vector = c.coords, c.type_index, c.type_vector
+                out.radii, out.max_type, out.src = c.radii, c.max_type, c.src
+            if out.coords.size() > 0:
+                g = out.coords.gpu()
+                out.coords.togpu()
+                self._apply(fn, g, g, dotranslate)
+            return True
+        return False
+
     def forward(self, inp, out, dotranslate=True):
-        self._apply(_cabi.lib().lmg_transform_forward, inp, out, dotranslate)
+        if not self._apply_sets(_cabi.lib().lmg_transform_forward, inp, out, dotranslate):
+            self._apply(_cabi.lib().lmg_transform_forward, inp, out, dotranslate)
 
     def backward(self, inp, out, dotranslate=True):
-        self._apply(_cabi.lib().lmg_transform_backward, inp, out, dotranslate)
+        if not self._apply_sets(_cabi.lib().lmg_transform_backward, inp, out, dotranslate):
+            self._apply(_cabi.lib().lmg_transform_backward, inp, out, dotranslate)
 
 
 def _transforms_tensor(transforms, batch, device):
@@ -308,9 +339,16 @@ class GridMaker(object):
             shape = (batch,) + shape
         return torch.zeros(shape, dtype=torch.float32, device=device or _current_device())
 
+    def make_ndarray(self, center, c):
+        """New numpy array holding the grid of CoordinateSet ``c`` (python/__init__.py:29-35)."""
+        t = np.zeros(self.grid_dimensions(c.max_type), dtype=np.float32)
+        self.forward(center, c, t)
+        return t
+
     # --- argument handling -------------------------------------------------------------------
     def _atoms(self, center, coords, types, radii, transforms=None, n_atoms=None):
         dev = _current_device()
+        coords, types, radii = (_grids.operand_tensor(x) for x in (coords, types, radii))
         batched = (coords.ndim if isinstance(coords, np.ndarray) else coords.dim()) == 3
         keep = []
         A = _cabi.AtomsStruct()
@@ -380,7 +418,100 @@ class GridMaker(object):
         return ws
 
     # --- forward -----------------------------------------------------------------------------
-    def forward(self, center, coords, types, radii, out, transforms=None, n_atoms=None):
+    def forward(self, *args, **kw):
+        """The reference's forward overload set (python/bindings.in.cpp:829-868):
+
+        * ``forward(example, grid, random_translation=0.0, random_rotation=False)``
+        * ``forward(examples, grid5, random_translation=0.0, random_rotation=False)``
+        * ``forward(center, coordinate_set, grid)``
+        * ``forward(example, transform, grid)``
+        * ``forward(center, coords, types, radii, grid)`` - index or vector types, single or batched
+          (plus the ``transforms=`` / ``n_atoms=`` extensions of :meth:`forward_arrays`).
+        """
+        from .coordinates import CoordinateSet, Example
+        a0 = args[0] if args else kw.get("example", kw.get("examples", kw.get("examplevec")))
+        if isinstance(a0, Example):
+            rest = list(args[1:])
+            if rest and isinstance(rest[0], Transform):
+                return self._forward_example(a0, rest[0], rest[1] if len(rest) > 1 else kw["grid"])
+            grid = rest[0] if rest else kw["grid"]
+            rt = rest[1] if len(rest) > 1 else kw.get("random_translation", 0.0)
+            rr = rest[2] if len(rest) > 2 else kw.get("random_rotation", False)
+            return self._forward_example(a0, Transform(self._default_center(a0), rt, rr), grid)
+        if isinstance(a0, (list, tuple)) and (len(a0) == 0 or isinstance(a0[0], Example)):
+            rest = list(args[1:])
+            grid = rest[0] if rest else kw["grid"]
+            rt = rest[1] if len(rest) > 1 else kw.get("random_translation", 0.0)
+            rr = rest[2] if len(rest) > 2 else kw.get("random_rotation", False)
+            return self._forward_examples(list(a0), grid, rt, rr)
+        if len(args) >= 2 and isinstance(args[1], CoordinateSet):
+            center, cs, grid = args[0], args[1], args[2] if len(args) > 2 else kw["grid"]
+            # vector types win when the set has both (include/libmolgrid/grid_maker.h:132-153)
+            if cs.has_vector_types() and cs.size() > 0:
+                return self.forward_arrays(center, cs.coords, cs.type_vector, cs.radii, grid)
+            return self.forward_arrays(center, cs.coords, cs.type_index, cs.radii, grid)
+        return self.forward_arrays(*args, **kw)
+
+    @staticmethod
+    def _default_center(ex):
+        """Grid centre of forward(example, grid, ...): the centre of the LAST set, taken as soon as
+        any set from the back is non-empty (src/grid_maker.cpp:126-137)."""
+        for s in reversed(ex.coord_sets):
+            if s.size():
+                return ex.coord_sets[-1].center()
+        return float3(0, 0, 0)
+
+    def _forward_example(self, ex, transform, grid):
+        """forward(Example, Transform, grid), src/grid_maker.cpp:109-116: sets merged, the transform
+        applied (here inside the gridding kernel), the rotation centre used as grid centre."""
+        c = ex.merge_coordinates()
+        T = int(_grids.operand_tensor(grid).shape[0])
+        if c.max_type != T:
+            raise IndexError("Incorrect number of channels in output grid: %d vs %d" % (c.max_type, T))
+        types = c.type_vector if (c.has_vector_types() and c.size() > 0) else c.type_index
+        return self.forward_arrays(transform.get_rotation_center(), c.coords, types, c.radii, grid,
+                                   transforms=transform)
+
+    def _forward_examples(self, examples, grid, random_translation, random_rotation):
+        """forward(vector<Example>, grid5, ...), include/libmolgrid/grid_maker.h:194-201, as ONE
+        batched call: examples are merged, padded to the longest and gridded together, each with its
+        own random Transform drawn in example order (the reference's sequence of draws)."""
+        gt = _grids.operand_tensor(grid)
+        if gt.shape[0] != len(examples):
+            raise ValueError("output grid dimension doesn't match examples vector size")
+        if not examples:
+            return
+        T = int(gt.shape[1])
+        merged, trs = [], []
+        for ex in examples:
+            c = ex.merge_coordinates()
+            if c.max_type != T:
+                raise IndexError("Incorrect number of channels in output grid: %d vs %d" % (c.max_type, T))
+            merged.append(c)
+            trs.append(Transform(self._default_center(ex), random_translation, random_rotation))
+        vec = any(c.has_vector_types() and c.size() > 0 for c in merged)
+        B = len(merged)
+        nmax = max(1, max(c.size() for c in merged))
+        dev = _current_device()
+        coords = torch.zeros((B, nmax, 3), dtype=torch.float32, device=dev)
+        nr = T if (vec and self.s.radii_type_indexed) else nmax
+        radii = torch.zeros((B, nr), dtype=torch.float32, device=dev)
+        types = torch.zeros((B, nmax, T) if vec else (B, nmax), dtype=torch.float32, device=dev)
+        ns = torch.zeros(B, dtype=torch.int32)
+        for b, c in enumerate(merged):
+            n = c.size()
+            ns[b] = n
+            if n == 0:
+                continue
+            coords[b, :n] = c.coords._current().t
+            src_t = c.type_vector if vec else c.type_index
+            types[b, :n] = src_t._current().t
+            r = c.radii._current().t
+            radii[b, :r.shape[0]] = r
+        centers = torch.tensor([list(t.get_rotation_center()) for t in trs], dtype=torch.float32, device=dev)
+        return self.forward_arrays(centers, coords, types, radii, grid, transforms=trs, n_atoms=ns)
+
+    def forward_arrays(self, center, coords, types, radii, out, transforms=None, n_atoms=None):
         """out[T,D,D,D] (or out[B,T,D,D,D] for batched inputs) from atoms.
 
         ``center`` is a float3/tuple, or a (B,3) array for batched input.  ``transforms`` (a
@@ -418,8 +549,25 @@ class GridMaker(object):
             check(_cabi.lib().lmg_check_status(ctypes.c_void_p(ws.data_ptr()), _stream_ptr(ws.device)))
 
     # --- backward ----------------------------------------------------------------------------
-    def backward(self, center, coords, types, radii, diff, atom_gradients, type_gradients=None,
-                 transforms=None, n_atoms=None):
+    def backward(self, *args, **kw):
+        """The reference's backward overload set (python/bindings.in.cpp:869-896):
+        ``backward(center, coordinate_set, diff, atom_gradients[, type_gradients])`` or
+        ``backward(center, coords, types, radii, diff, atom_gradients[, type_gradients])``."""
+        from .coordinates import CoordinateSet
+        if len(args) >= 2 and isinstance(args[1], CoordinateSet):
+            center, cs, diff, ag = args[:4]
+            tg = args[4] if len(args) > 4 else kw.get("type_gradients")
+            if tg is not None:
+                if not cs.has_vector_types():
+                    raise ValueError("Vector types missing from coordinate set")
+                return self.backward_arrays(center, cs.coords, cs.type_vector, cs.radii, diff, ag, tg)
+            if not cs.has_indexed_types():
+                raise ValueError("Index types missing from coordinate set")
+            return self.backward_arrays(center, cs.coords, cs.type_index, cs.radii, diff, ag)
+        return self.backward_arrays(*args, **kw)
+
+    def backward_arrays(self, center, coords, types, radii, diff, atom_gradients, type_gradients=None,
+                        transforms=None, n_atoms=None):
         """Atom (and, for vector types, type) gradients from grid gradients ``diff``."""
         dev, A, keep, batched, vec, B, N, nr = self._atoms(center, coords, types, radii, transforms, n_atoms)
         df = _Arg(diff, dev, 5 if batched else 4, "diff")
@@ -456,8 +604,19 @@ class GridMaker(object):
         if tg is not None:
             tg.finish()
 
-    def backward_relevance(self, center, coords, types, radii, density, diff, relevance,
-                           transforms=None, n_atoms=None):
+    def backward_relevance(self, *args, **kw):
+        """``backward_relevance(center, coordinate_set, density, diff, relevance)`` or the array form
+        of :meth:`backward_relevance_arrays` (include/libmolgrid/grid_maker.h:558-618)."""
+        from .coordinates import CoordinateSet
+        if len(args) >= 2 and isinstance(args[1], CoordinateSet):
+            center, cs, density, diff, rel = args[:5]
+            if not cs.has_indexed_types():
+                raise ValueError("Index types missing from coordinate set in backward relevance")
+            return self.backward_relevance_arrays(center, cs.coords, cs.type_index, cs.radii, density, diff, rel)
+        return self.backward_relevance_arrays(*args, **kw)
+
+    def backward_relevance_arrays(self, center, coords, types, radii, density, diff, relevance,
+                                  transforms=None, n_atoms=None):
         """Per-atom relevance; C++-only in the reference (include/libmolgrid/grid_maker.h:558-618)."""
         dev, A, keep, batched, vec, B, N, nr = self._atoms(center, coords, types, radii, transforms, n_atoms)
         if vec:
@@ -480,8 +639,19 @@ class GridMaker(object):
         self._last_ws = ws
         rel.finish()
 
-    def backward_gradients(self, center, coords, types, radii, diff, atom_gradients, type_gradients,
-                           diffdiff, atom_diffdiff, type_diffdiff, transforms=None, n_atoms=None):
+    def backward_gradients(self, *args, **kw):
+        """``backward_gradients(center, coordinate_set, diff, atom_gradients, type_gradients, diffdiff,
+        atom_diffdiff, type_diffdiff)`` or the array form (python/bindings.in.cpp:897-918)."""
+        from .coordinates import CoordinateSet
+        if len(args) >= 2 and isinstance(args[1], CoordinateSet):
+            cs = args[1]
+            if not cs.has_vector_types():
+                raise ValueError("Vector types missing from coordinate set")
+            return self.backward_gradients_arrays(args[0], cs.coords, cs.type_vector, cs.radii, *args[2:], **kw)
+        return self.backward_gradients_arrays(*args, **kw)
+
+    def backward_gradients_arrays(self, center, coords, types, radii, diff, atom_gradients, type_gradients,
+                                  diffdiff, atom_diffdiff, type_diffdiff, transforms=None, n_atoms=None):
         """Second-order pass (vector types only), src/grid_maker.cpp:529-672."""
         dev, A, keep, batched, vec, B, N, nr = self._atoms(center, coords, types, radii, transforms, n_atoms)
         if not vec:
@@ -558,6 +728,7 @@ class GridInterpolater(object):
         else:
             raise TypeError("forward takes 3 or 5 arguments")
         dev = _current_device()
+        inp, out = _grids.operand_tensor(inp), _grids.operand_tensor(out)
         nd = inp.ndim if isinstance(inp, np.ndarray) else inp.dim()
         batched = nd == 5
         i = _Arg(inp, dev, nd, "in")

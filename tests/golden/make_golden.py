@@ -92,6 +92,47 @@ def main():
     out["random/norot"] = R.random_transform(99, (0, 0, 0), 1.0, False, 2)
     np.savez_compressed(OUT, **out)
     print("wrote", OUT, os.path.getsize(OUT), "bytes,", len(out), "arrays")
+    molecule(R)
+
+
+MOL_OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "molecule.npz")
+REF_DATA = "/root/reference/test/data"
+
+
+def molecule_diff(shape):
+    """Grid gradient of the molecule case, regenerated identically by the tests."""
+    return np.random.default_rng(4242).normal(size=shape).astype(np.float32)
+
+
+def molecule(R):
+    """The first example of the reference's test/data/small.types (receptor 4kqp_rec_0 and ligand
+    4kqp_min_0, pre-typed records), decoded with this package's reader and gridded by the reference
+    with its default GridMaker.  test/test_gridmaker.py:72-103 expects maxima 1.438691 (ligand about
+    its centre) and 2.094017 (whole example); both are asserted here before anything is written."""
+    from libmolgrid_b200 import coord_cache
+    prov = coord_cache.ExampleProvider(data_root=os.path.join(REF_DATA, "structs"))
+    prov.populate(os.path.join(REF_DATA, "small.types"))
+    ex = prov.next()
+    lig = ex.coord_sets[1]
+    center = np.array(tuple(lig.center()), dtype=np.float32)
+    gm = R.gm(resolution=0.5, dimension=23.5)
+    m = ex.merge_coordinates()
+    arr = lambda g: g.tonumpy()
+    lig_grid = R.forward_index(gm, center, arr(lig.coords), arr(lig.type_index), arr(lig.radii), lig.max_type)
+    ex_grid = R.forward_index(gm, center, arr(m.coords), arr(m.type_index), arr(m.radii), m.max_type)
+    assert abs(float(lig_grid.max()) - 1.438691) < 1e-5 and abs(float(ex_grid.max()) - 2.094017) < 1e-5
+    diff = molecule_diff(ex_grid.shape)
+    grad = R.backward_index(gm, center, arr(m.coords), arr(m.type_index), arr(m.radii), diff)
+    sample = np.random.default_rng(4243).choice(ex_grid.size, 8192, replace=False)
+    out = dict(center=center, labels=np.array(ex.labels, dtype=np.float32),
+               rec_coords=arr(ex.coord_sets[0].coords), rec_types=arr(ex.coord_sets[0].type_index),
+               rec_radii=arr(ex.coord_sets[0].radii), lig_coords=arr(lig.coords), lig_types=arr(lig.type_index),
+               lig_radii=arr(lig.radii), lig_max=lig_grid.max(), ex_max=ex_grid.max(),
+               lig_channel_sums=lig_grid.reshape(lig.max_type, -1).sum(1),
+               ex_channel_sums=ex_grid.reshape(m.max_type, -1).sum(1, dtype=np.float64),
+               sample=sample, ex_sample=ex_grid.reshape(-1)[sample], backward=grad)
+    np.savez_compressed(MOL_OUT, **out)
+    print("wrote", MOL_OUT, os.path.getsize(MOL_OUT), "bytes")
 
 
 if __name__ == "__main__":

@@ -1,0 +1,160 @@
+"""Per-operation timings of the gridding path beside its headline benchmark (bench.py).
+
+    python bench_ops.py [--reps 20] [--ops forward,backward,...]
+
+One JSON line per operation: device time per call (CUDA events on the launching stream, inputs
+resident on the device, 3 warm-up calls, every call's grids larger than L2), examples/s, and the
+operation's algorithmic bytes against the measured HBM bandwidth.  Workloads are seeded synthetic
+inputs with the shapes of the benchmark configurations:
+
+* index types, 28x48^3 @0.5 A, batch 50 x [2000,4000] atoms in a blob (forward, binary forward,
+  backward, relevance);
+* vector types, 28x96^3 @0.25 A, batch 4 x 3000 atoms, Dirichlet(0.3) type vectors, type-indexed radii
+  1.7 A x U[0.8,1.2] (forward, backward, backward_gradients) - compute bound: pair evaluations/s are
+  reported next to the byte figure;
+* interpolation 28x48^3 -> 28x48^3, batch 48, random rotation + translation.
+"""
+import argparse
+import json
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+from tests import cases  # noqa: E402
+
+T = 28
+
+
+def peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--ops", default="forward,forward_binary,backward,relevance,forward_vector,"
+                                      "backward_vector,backward_gradients,interpolate")
+    args = ap.parse_args()
+    import torch
+    import libmolgrid_b200 as lmg
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    pk, pk_kind = peak()
+    ops = args.ops.split(",")
+
+    def d(a):
+        return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+    def timeit(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.reps
+
+    def report(op, workload, ms, batch, nbytes, extra=None):
+        line = {"op": op, "workload": workload, "ms_per_call": ms, "examples_per_s": batch / (ms * 1e-3),
+                "algorithmic_bytes_per_call": nbytes, "achieved_gbs": nbytes / (ms * 1e-3) / 1e9,
+                "peak_gbs": pk, "peak_kind": pk_kind, "frac": nbytes / (ms * 1e-3) / 1e9 / pk}
+        if extra:
+            line.update(extra)
+        print(json.dumps(line), flush=True)
+
+    # ---- index types, 48^3 ----------------------------------------------------------------------
+    if set(ops) & {"forward", "forward_binary", "backward", "relevance"}:
+        B = 50
+        coords, types, radii, ns, tr = cases.blob_batch(1001, B, 2000, 4000, T)
+        g = lmg.GridMaker(0.5, 23.5)
+        dc, dt, dr, dtr, dn = d(coords), d(types), d(radii), d(tr), d(ns)
+        cen = torch.zeros((B, 3), device=dev)
+        grid = torch.empty((B,) + g.grid_dimensions(T), device=dev)
+        diff = torch.randn(grid.shape, device=dev)
+        ag = torch.empty((B, coords.shape[1], 3), device=dev)
+        rel = torch.empty((B, coords.shape[1]), device=dev)
+        natoms = float(ns.sum())
+        gb = grid.numel() * 4
+        wl = "index types, 28x48^3, batch 50 x [2000,4000] atoms"
+        if "forward" in ops:
+            report("forward", wl, timeit(lambda: g.forward(cen, dc, dt, dr, grid, transforms=dtr, n_atoms=dn)),
+                   B, gb + 20 * natoms)
+        if "forward_binary" in ops:
+            g.set_binary(True)
+            report("forward_binary", wl,
+                   timeit(lambda: g.forward(cen, dc, dt, dr, grid, transforms=dtr, n_atoms=dn)), B, gb + 20 * natoms)
+            g.set_binary(False)
+        g.forward(cen, dc, dt, dr, grid, transforms=dtr, n_atoms=dn)
+        if "backward" in ops:
+            report("backward", wl,
+                   timeit(lambda: g.backward(cen, dc, dt, dr, diff, ag, transforms=dtr, n_atoms=dn)),
+                   B, gb + 32 * natoms)
+        if "relevance" in ops:
+            report("relevance", wl,
+                   timeit(lambda: g.backward_relevance(cen, dc, dt, dr, grid, diff, rel, transforms=dtr, n_atoms=dn)),
+                   B, 2 * gb + 24 * natoms)
+        del grid, diff
+
+    # ---- vector types, 96^3 ---------------------------------------------------------------------
+    if set(ops) & {"forward_vector", "backward_vector", "backward_gradients"}:
+        B, N = 4, 3000
+        rng = np.random.default_rng(1003)
+        coords = np.stack([cases.blob_batch(1003 + b, 1, N, N, T)[0][0] for b in range(B)])
+        tv = rng.dirichlet(np.ones(T) * 0.3, (B, N)).astype(np.float32)
+        rad = (1.7 * rng.uniform(0.8, 1.2, (B, T))).astype(np.float32)
+        g = lmg.GridMaker(0.25, 23.75, False, True)
+        dc, dtv, dr = d(coords), d(tv), d(rad)
+        cen = torch.zeros((B, 3), device=dev)
+        grid = torch.empty((B,) + g.grid_dimensions(T), device=dev)
+        diff = torch.randn(grid.shape, device=dev)
+        ag, tg = torch.empty((B, N, 3), device=dev), torch.empty((B, N, T), device=dev)
+        dd, add, tdd = torch.empty_like(grid), torch.empty_like(ag), torch.empty_like(tg)
+        gb = grid.numel() * 4
+        # pair evaluations: per (atom, channel with weight != 0) the voxels of a sphere of 1.5 r_t
+        vol = 4.0 / 3.0 * np.pi * (1.5 * rad / 0.25) ** 3              # [B][T]
+        pairs_fwd = float(((tv != 0) * vol[:, None, :]).sum())
+        pairs_all = float(N * vol.sum())
+        wl = "vector types, 28x96^3, batch %d x %d atoms, type-indexed radii" % (B, N)
+        if "forward_vector" in ops:
+            ms = timeit(lambda: g.forward(cen, dc, dtv, dr, grid))
+            report("forward_vector", wl, ms, B, gb + B * N * (12 + 4 * T),
+                   {"pair_evaluations_per_s": pairs_fwd / (ms * 1e-3)})
+        g.forward(cen, dc, dtv, dr, grid)
+        if "backward_vector" in ops:
+            ms = timeit(lambda: g.backward(cen, dc, dtv, dr, diff, ag, tg))
+            report("backward_vector", wl, ms, B, gb + B * N * (12 + 4 * T) * 2,
+                   {"pair_evaluations_per_s": pairs_all / (ms * 1e-3)})
+        g.backward(cen, dc, dtv, dr, diff, ag, tg)
+        if "backward_gradients" in ops:
+            ms = timeit(lambda: g.backward_gradients(cen, dc, dtv, dr, diff, ag, tg, dd, add, tdd))
+            report("backward_gradients", wl, ms, B, 2 * gb + B * N * (12 + 4 * T) * 3,
+                   {"pair_evaluations_per_s": 2 * pairs_fwd / (ms * 1e-3)})
+        del grid, diff, dd
+
+    # ---- interpolation --------------------------------------------------------------------------
+    if "interpolate" in ops:
+        B = 48
+        rng = np.random.default_rng(1005)
+        gi = lmg.GridInterpolater(0.5, 23.5, 0.5, 23.5)
+        src = torch.rand((B, T, 48, 48, 48), device=dev)
+        dst = torch.empty_like(src)
+        q = cases.random_quaternion(rng, B)
+        trs = [lmg.Transform(lmg.Quaternion(*[float(v) for v in q[b]]), (0, 0, 0),
+                             tuple(float(v) for v in rng.uniform(-2, 2, 3))) for b in range(B)]
+        ms = timeit(lambda: gi.forward(src, trs, dst))
+        report("interpolate", "28x48^3 -> 28x48^3, batch 48, random rotation and translation", ms, B,
+               2 * src.numel() * 4)
+
+
+if __name__ == "__main__":
+    main()

@@ -81,6 +81,8 @@ EXTRA_SYMBOLS = [
     ("lmg_set_precise", None, [ctypes.c_int]),
     ("lmg_set_forward_mode", None, [ctypes.c_int]),
     ("lmg_set_quads", None, [ctypes.c_int]),
+    ("lmg_set_interp_tiled", None, [ctypes.c_int]),
+    ("lmg_tma_timeouts", ctypes.c_uint, []),
     # bench support
     ("lmg_profile_enable", ctypes.c_int, [ctypes.c_int]),
     ("lmg_profile_collect", ctypes.c_int, [ctypes.POINTER(ctypes.c_double), c_int_p]),

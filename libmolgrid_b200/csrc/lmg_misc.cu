@@ -1,5 +1,8 @@
 // sm_100a kernels for Transform forward/backward on coordinate arrays and for the
 // GridInterpolater trilinear resample.
+#include <cuda.h>
+#include <stdint.h>
+
 #include "lmg_device.cuh"
 #include "lmg_misc.h"
 
@@ -57,9 +60,83 @@ __device__ __forceinline__ float get_pt(const float* in, int dim, int x, int y, 
   return __ldg(in + ((size_t)x * dim + y) * dim + z);
 }
 
+// What is the same for every output voxel of an example: grid origins and the inverse rotation.
+struct InterpFrame {
+  float iox, ioy, ioz, oox, ooy, ooz;
+  float inv[4], cn[4];
+  float ux, uy, uz, cx, cy, cz;
+};
+
+__device__ __forceinline__ InterpFrame interp_frame(const InterpArgs& I, const InterpExample& E) {
+  InterpFrame F;
+  F.iox = __fsub_rn(E.in_center[0], I.in_half);
+  F.ioy = __fsub_rn(E.in_center[1], I.in_half);
+  F.ioz = __fsub_rn(E.in_center[2], I.in_half);
+  F.oox = __fsub_rn(E.out_center[0], I.out_half);
+  F.ooy = __fsub_rn(E.out_center[1], I.out_half);
+  F.ooz = __fsub_rn(E.out_center[2], I.out_half);
+  quat_inverse(E.X.q, F.inv);
+  quat_conj_over_norm(F.inv, F.cn);
+  F.ux = __fsub_rn(-E.X.t[0], E.X.c[0]);
+  F.uy = __fsub_rn(-E.X.t[1], E.X.c[1]);
+  F.uz = __fsub_rn(-E.X.t[2], E.X.c[2]);
+  F.cx = E.X.c[0]; F.cy = E.X.c[1]; F.cz = E.X.c[2];
+  return F;
+}
+
+// Position of output voxel (i,j,k) in input-grid index units (src/grid_interpolater.cpp:31-45).
+__device__ __forceinline__ void interp_point(const InterpArgs& I, const InterpFrame& F, unsigned i, unsigned j,
+                                             unsigned k, float& gx, float& gy, float& gz) {
+  float px = voxel_coord(F.oox, i, I.out_res), py = voxel_coord(F.ooy, j, I.out_res),
+        pz = voxel_coord(F.ooz, k, I.out_res);
+  float r[3];
+  quat_rotate(F.inv, F.cn, __fadd_rn(px, F.ux), __fadd_rn(py, F.uy), __fadd_rn(pz, F.uz), r);
+  gx = __fdiv_rn(__fsub_rn(__fadd_rn(r[0], F.cx), F.iox), I.in_res);
+  gy = __fdiv_rn(__fsub_rn(__fadd_rn(r[1], F.cy), F.ioy), I.in_res);
+  gz = __fdiv_rn(__fsub_rn(__fadd_rn(r[2], F.cz), F.ioz), I.in_res);
+}
+
+// Corner indices and weights of the trilinear blend (src/grid_interpolater.cu:26-58).
+struct InterpCell {
+  int xl, xh, yl, yh, zl, zh;
+  float xd, yd, zd, xm, ym, zm;
+};
+
+__device__ __forceinline__ InterpCell interp_cell(float gx, float gy, float gz) {
+  InterpCell C;
+  C.xl = (int)floorf(gx); C.xh = (int)ceilf(gx);
+  C.yl = (int)floorf(gy); C.yh = (int)ceilf(gy);
+  C.zl = (int)floorf(gz); C.zh = (int)ceilf(gz);
+  C.xd = C.xh > C.xl ? __fdiv_rn(__fsub_rn(gx, (float)C.xl), (float)(C.xh - C.xl)) : 0.f;
+  C.yd = C.yh > C.yl ? __fdiv_rn(__fsub_rn(gy, (float)C.yl), (float)(C.yh - C.yl)) : 0.f;
+  C.zd = C.zh > C.zl ? __fdiv_rn(__fsub_rn(gz, (float)C.zl), (float)(C.zh - C.zl)) : 0.f;
+  C.xm = __fsub_rn(1.f, C.xd); C.ym = __fsub_rn(1.f, C.yd); C.zm = __fsub_rn(1.f, C.zd);
+  return C;
+}
+
+__device__ __forceinline__ float interp_blend(const InterpCell& C, float p000, float p001, float p010,
+                                              float p011, float p100, float p101, float p110, float p111) {
+  float c00 = __fadd_rn(__fmul_rn(p000, C.xm), __fmul_rn(p100, C.xd));
+  float c01 = __fadd_rn(__fmul_rn(p001, C.xm), __fmul_rn(p101, C.xd));
+  float c10 = __fadd_rn(__fmul_rn(p010, C.xm), __fmul_rn(p110, C.xd));
+  float c11 = __fadd_rn(__fmul_rn(p011, C.xm), __fmul_rn(p111, C.xd));
+  float c0 = __fadd_rn(__fmul_rn(c00, C.ym), __fmul_rn(c10, C.yd));
+  float c1 = __fadd_rn(__fmul_rn(c01, C.ym), __fmul_rn(c11, C.yd));
+  return __fadd_rn(__fmul_rn(c0, C.zm), __fmul_rn(c1, C.zd));
+}
+
+// One channel of one output voxel read straight from the input grid.
+__device__ __forceinline__ float interp_direct(const InterpCell& C, const float* g, int id) {
+  if (C.xh < 0 || C.xl >= id || C.yh < 0 || C.yl >= id || C.zh < 0 || C.zl >= id) return 0.f;
+  return interp_blend(C, get_pt(g, id, C.xl, C.yl, C.zl), get_pt(g, id, C.xl, C.yl, C.zh),
+                      get_pt(g, id, C.xl, C.yh, C.zl), get_pt(g, id, C.xl, C.yh, C.zh),
+                      get_pt(g, id, C.xh, C.yl, C.zl), get_pt(g, id, C.xh, C.yl, C.zh),
+                      get_pt(g, id, C.xh, C.yh, C.zl), get_pt(g, id, C.xh, C.yh, C.zh));
+}
+
 // One thread per output voxel; the inverse transform is computed once and reused for every
-// channel (GridInterpolater::forward, src/grid_interpolater.cpp:31-45; interpolate,
-// src/grid_interpolater.cu:26-58).
+// channel (GridInterpolater::forward, src/grid_interpolater.cpp:31-45).  Used when the input grid
+// does not meet the alignment rules of the tiled kernel below.
 __global__ void __launch_bounds__(256) k_interpolate(InterpArgs I) {
   int bl = blockIdx.y;
   const InterpExample& E = I.ex[bl];
@@ -67,57 +144,209 @@ __global__ void __launch_bounds__(256) k_interpolate(InterpArgs I) {
   unsigned v = blockIdx.x * blockDim.x + threadIdx.x;
   if (v >= od * od * od) return;
   unsigned k = v % od, j = (v / od) % od, i = v / (od * od);
-
-  float in_radius = I.in_half, out_radius = I.out_half;
-  float iox = __fsub_rn(E.in_center[0], in_radius), ioy = __fsub_rn(E.in_center[1], in_radius),
-        ioz = __fsub_rn(E.in_center[2], in_radius);
-  float oox = __fsub_rn(E.out_center[0], out_radius), ooy = __fsub_rn(E.out_center[1], out_radius),
-        ooz = __fsub_rn(E.out_center[2], out_radius);
-  float inv[4], cn[4];
-  quat_inverse(E.X.q, inv);
-  quat_conj_over_norm(inv, cn);
-  float ux = __fsub_rn(-E.X.t[0], E.X.c[0]), uy = __fsub_rn(-E.X.t[1], E.X.c[1]),
-        uz = __fsub_rn(-E.X.t[2], E.X.c[2]);
-  float px = voxel_coord(oox, i, I.out_res), py = voxel_coord(ooy, j, I.out_res),
-        pz = voxel_coord(ooz, k, I.out_res);
-  float r[3];
-  quat_rotate(inv, cn, __fadd_rn(px, ux), __fadd_rn(py, uy), __fadd_rn(pz, uz), r);
-  float gx = __fdiv_rn(__fsub_rn(__fadd_rn(r[0], E.X.c[0]), iox), I.in_res);
-  float gy = __fdiv_rn(__fsub_rn(__fadd_rn(r[1], E.X.c[1]), ioy), I.in_res);
-  float gz = __fdiv_rn(__fsub_rn(__fadd_rn(r[2], E.X.c[2]), ioz), I.in_res);
-
-  int xl = (int)floorf(gx), xh = (int)ceilf(gx);
-  int yl = (int)floorf(gy), yh = (int)ceilf(gy);
-  int zl = (int)floorf(gz), zh = (int)ceilf(gz);
-  float xd = xh > xl ? __fdiv_rn(__fsub_rn(gx, (float)xl), (float)(xh - xl)) : 0.f;
-  float yd = yh > yl ? __fdiv_rn(__fsub_rn(gy, (float)yl), (float)(yh - yl)) : 0.f;
-  float zd = zh > zl ? __fdiv_rn(__fsub_rn(gz, (float)zl), (float)(zh - zl)) : 0.f;
-  float xm = __fsub_rn(1.f, xd), ym = __fsub_rn(1.f, yd), zm = __fsub_rn(1.f, zd);
-
+  InterpFrame F = interp_frame(I, E);
+  float gx, gy, gz;
+  interp_point(I, F, i, j, k, gx, gy, gz);
+  InterpCell C = interp_cell(gx, gy, gz);
   int id = (int)I.in_dim;
   size_t ichan = (size_t)id * id * id, ochan = (size_t)od * od * od;
   size_t b = (size_t)I.b0 + bl;
   const float* in = I.in + b * I.K * ichan;
   float* out = I.out + b * I.K * ochan + v;
-  bool any = !(xh < 0 || xl >= id || yh < 0 || yl >= id || zh < 0 || zl >= id);
-  for (int c = 0; c < I.K; c++) {
-    float res = 0.f;
-    if (any) {
-      const float* g = in + c * ichan;
-      float p000 = get_pt(g, id, xl, yl, zl), p001 = get_pt(g, id, xl, yl, zh);
-      float p010 = get_pt(g, id, xl, yh, zl), p011 = get_pt(g, id, xl, yh, zh);
-      float p100 = get_pt(g, id, xh, yl, zl), p101 = get_pt(g, id, xh, yl, zh);
-      float p110 = get_pt(g, id, xh, yh, zl), p111 = get_pt(g, id, xh, yh, zh);
-      float c00 = __fadd_rn(__fmul_rn(p000, xm), __fmul_rn(p100, xd));
-      float c01 = __fadd_rn(__fmul_rn(p001, xm), __fmul_rn(p101, xd));
-      float c10 = __fadd_rn(__fmul_rn(p010, xm), __fmul_rn(p110, xd));
-      float c11 = __fadd_rn(__fmul_rn(p011, xm), __fmul_rn(p111, xd));
-      float c0 = __fadd_rn(__fmul_rn(c00, ym), __fmul_rn(c10, yd));
-      float c1 = __fadd_rn(__fmul_rn(c01, ym), __fmul_rn(c11, yd));
-      res = __fadd_rn(__fmul_rn(c0, zm), __fmul_rn(c1, zd));
+  for (int c = 0; c < I.K; c++) __stcs(out + c * ochan, interp_direct(C, in + c * ichan, id));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tiled interpolation: a block owns an 8x8x8 tile of output voxels.  The input voxels that tile can
+// touch form a box of at most 16x16x20 (the rotated tile's bounding box, z rounded down to a
+// 16-byte boundary); one elected thread brings that box of channel c into shared memory with a
+// single tensor copy (cp.async.bulk.tensor, zero fill outside the grid = the reference's zero
+// padding), two channels in flight, and the 256 threads blend their two voxels each from shared
+// memory.  The blend arithmetic is that of the direct kernel.  Every wait on a copy is bounded; a
+// wait that runs out makes the block finish its tile through the direct reads.
+// ---------------------------------------------------------------------------------------------
+__device__ unsigned g_tma_timeouts = 0;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+  return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// false when the phase did not complete within the limit
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity) {
+  for (int it = 0; it < (1 << 20); it++)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void tma_load_box(float* dst, const CUtensorMap* map, uint64_t* bar, int z, int y,
+                                             int x, int chan) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(smem_u32(dst)),
+      "l"(map), "r"(z), "r"(y), "r"(x), "r"(chan), "r"(smem_u32(bar))
+      : "memory");
+}
+
+#ifndef LMG_INTERP_MINBLOCKS
+#define LMG_INTERP_MINBLOCKS 4
+#endif
+__global__ void __launch_bounds__(256, LMG_INTERP_MINBLOCKS) k_interpolate_tiled(const __grid_constant__ CUtensorMap map, InterpArgs I) {
+  __shared__ __align__(128) float box[2][ITILE_BOX];
+  __shared__ __align__(8) uint64_t bar[2];
+  const int tid = threadIdx.x, bl = blockIdx.y;
+  const InterpExample& E = I.ex[bl];
+  const unsigned od = I.out_dim;
+  const unsigned nt = (od + ITILE - 1) / ITILE;
+  const unsigned tk = blockIdx.x % nt, tj = (blockIdx.x / nt) % nt, ti = blockIdx.x / (nt * nt);
+  const InterpFrame F = interp_frame(I, E);
+
+  // bounding box of the tile in input index units, from its eight corner voxels
+  float lo[3] = {3e38f, 3e38f, 3e38f}, hi[3] = {-3e38f, -3e38f, -3e38f};
+#pragma unroll
+  for (int cnr = 0; cnr < 8; cnr++) {
+    unsigned ci = min(ti * ITILE + ((cnr & 4) ? ITILE - 1 : 0), od - 1);
+    unsigned cj = min(tj * ITILE + ((cnr & 2) ? ITILE - 1 : 0), od - 1);
+    unsigned ck = min(tk * ITILE + ((cnr & 1) ? ITILE - 1 : 0), od - 1);
+    float g[3];
+    interp_point(I, F, ci, cj, ck, g[0], g[1], g[2]);
+#pragma unroll
+    for (int a = 0; a < 3; a++) {
+      lo[a] = fminf(lo[a], g[a]);
+      hi[a] = fmaxf(hi[a], g[a]);
     }
-    __stcs(out + c * ochan, res);
   }
+  // every voxel of the tile lies in the hull of the corners up to rounding: a margin of 0.01 cells
+  bool sane = true;
+#pragma unroll
+  for (int a = 0; a < 3; a++) sane = sane && lo[a] > -1e6f && hi[a] < 1e6f;  // also false for NaN
+  int bx0 = 0, by0 = 0, bz0 = 0;
+  bool tiled = sane;
+  if (sane) {
+    bx0 = (int)floorf(lo[0] - 0.01f);
+    by0 = (int)floorf(lo[1] - 0.01f);
+    int z0 = (int)floorf(lo[2] - 0.01f);
+    bz0 = z0 & ~3;  // rounds down for negative values too (two's complement): 16-byte boundary
+    int nx = (int)ceilf(hi[0] + 0.01f) - bx0 + 1, ny = (int)ceilf(hi[1] + 0.01f) - by0 + 1,
+        nz = (int)ceilf(hi[2] + 0.01f) - bz0 + 1;
+    tiled = nx <= ITILE_BX && ny <= ITILE_BY && nz <= ITILE_BZ;
+  }
+
+  // this thread's two voxels
+  const int id = (int)I.in_dim;
+  const size_t ichan = (size_t)id * id * id, ochan = (size_t)od * od * od;
+  const size_t b = (size_t)I.b0 + bl;
+  const float* in = I.in + b * I.K * ichan;
+  float* outb = I.out + b * I.K * ochan;
+  InterpCell C[2];
+  size_t ov[2];
+  bool live[2];
+  int base[2], sx[2], sy[2], sz[2];
+#pragma unroll
+  for (int u = 0; u < 2; u++) {
+    int o = tid + 256 * u;
+    unsigned i = ti * ITILE + (o >> 6), j = tj * ITILE + ((o >> 3) & 7), k = tk * ITILE + (o & 7);
+    live[u] = i < od && j < od && k < od;
+    float gx, gy, gz;
+    interp_point(I, F, min(i, od - 1), min(j, od - 1), min(k, od - 1), gx, gy, gz);
+    C[u] = interp_cell(gx, gy, gz);
+    ov[u] = ((size_t)i * od + j) * od + k;
+    base[u] = ((C[u].xl - bx0) * ITILE_BY + (C[u].yl - by0)) * ITILE_BZ + (C[u].zl - bz0);
+    sx[u] = (C[u].xh - C[u].xl) * ITILE_BY * ITILE_BZ;
+    sy[u] = (C[u].yh - C[u].yl) * ITILE_BZ;
+    sz[u] = C[u].zh - C[u].zl;
+    // belt and braces: a corner outside the staged box sends the whole block down the direct path
+    bool inside = C[u].xl >= bx0 && C[u].xh < bx0 + ITILE_BX && C[u].yl >= by0 && C[u].yh < by0 + ITILE_BY &&
+                  C[u].zl >= bz0 && C[u].zh < bz0 + ITILE_BZ;
+    if (live[u] && !inside) tiled = false;
+  }
+  tiled = __syncthreads_and(tiled) != 0;
+
+  int c = 0;
+  if (tiled) {
+    const int chan0 = (int)(b * I.K);
+    if (tid == 0) {
+      mbar_init(&bar[0], 1);
+      mbar_init(&bar[1], 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (tid == 0) {
+      for (int s = 0; s < 2 && s < I.K; s++) {
+        mbar_expect_tx(&bar[s], ITILE_BOX * sizeof(float));
+        tma_load_box(box[s], &map, &bar[s], bz0, by0, bx0, chan0 + s);
+      }
+    }
+    int inflight = min(2, I.K);
+    for (; c < I.K; c++) {
+      const int s = c & 1;
+      bool ok = mbar_wait_bounded(&bar[s], (c >> 1) & 1);
+      if (__syncthreads_or(!ok)) break;  // a copy did not arrive: finish through the direct reads
+      inflight--;
+      const float* sm = box[s];
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        if (!live[u]) continue;
+        const float* p = sm + base[u];
+        float res = interp_blend(C[u], p[0], p[sz[u]], p[sy[u]], p[sy[u] + sz[u]], p[sx[u]], p[sx[u] + sz[u]],
+                                 p[sx[u] + sy[u]], p[sx[u] + sy[u] + sz[u]]);
+        __stcs(outb + c * ochan + ov[u], res);
+      }
+      __syncthreads();  // everyone is done with box[s] before it is refilled
+      if (tid == 0 && c + 2 < I.K) {
+        mbar_expect_tx(&bar[s], ITILE_BOX * sizeof(float));
+        tma_load_box(box[s], &map, &bar[s], bz0, by0, bx0, chan0 + c + 2);
+      }
+      if (c + 2 < I.K) inflight++;
+    }
+    if (c < I.K) {
+      // give the copies still in flight a second, equally bounded chance to land before the shared
+      // memory is given up; then fall through to the direct reads
+      if (tid == 0) atomicAdd(&g_tma_timeouts, 1u);
+      for (int w = 0; w < inflight; w++) {
+        int cc = c + w;
+        if (cc < I.K) mbar_wait_bounded(&bar[cc & 1], (cc >> 1) & 1);
+      }
+      __syncthreads();
+    }
+  }
+  for (; c < I.K; c++) {
+#pragma unroll
+    for (int u = 0; u < 2; u++)
+      if (live[u]) __stcs(outb + c * ochan + ov[u], interp_direct(C[u], in + c * ichan, id));
+  }
+}
+
+unsigned interp_tile_count(unsigned out_dim) {
+  unsigned nt = (out_dim + ITILE - 1) / ITILE;
+  return nt * nt * nt;
+}
+
+cudaError_t launch_interpolate_tiled(const CUtensorMap& map, const InterpArgs& I, int nb, cudaStream_t st) {
+  unsigned ntiles = interp_tile_count(I.out_dim);
+  if (ntiles == 0 || nb == 0 || I.K == 0) return cudaSuccess;
+  dim3 grid(ntiles, nb);
+  k_interpolate_tiled<<<grid, 256, 0, st>>>(map, I);
+  return cudaGetLastError();
+}
+
+cudaError_t read_tma_timeouts(unsigned* count) {
+  return cudaMemcpyFromSymbol(count, g_tma_timeouts, sizeof(unsigned));
 }
 
 cudaError_t launch_interpolate(const InterpArgs& I, int nb, cudaStream_t st) {

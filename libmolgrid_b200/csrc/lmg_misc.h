@@ -1,5 +1,6 @@
 // Launchers of the Transform and GridInterpolater kernels.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include "lmg_device.cuh"
@@ -28,5 +29,15 @@ struct InterpArgs {
 cudaError_t launch_transform(const Xform& X, int n, const float* in, float* out, int dotranslate,
                              bool forward, cudaStream_t st);
 cudaError_t launch_interpolate(const InterpArgs& I, int nb, cudaStream_t st);
+
+// Tiled kernel: output tiles of ITILE^3 voxels read a staged box of the input of at most
+// ITILE_BX x ITILE_BY x ITILE_BZ voxels (z is the contiguous axis; the box starts on a multiple of four).
+constexpr int ITILE = 8;
+constexpr int ITILE_BX = 16, ITILE_BY = 16, ITILE_BZ = 20;
+constexpr int ITILE_BOX = ITILE_BX * ITILE_BY * ITILE_BZ;
+// `map` describes the input as a 4-d tensor {z, y, x, example*channels} with that box
+cudaError_t launch_interpolate_tiled(const CUtensorMap& map, const InterpArgs& I, int nb, cudaStream_t st);
+// how many blocks ever gave up waiting for a staged box (they finish through direct reads)
+cudaError_t read_tma_timeouts(unsigned* count);
 
 }  // namespace lmg

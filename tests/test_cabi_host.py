@@ -24,6 +24,12 @@ def test_exports_every_declared_symbol(lib):
     from libmolgrid_b200 import _cabi
     assert declared == {n for n, _, _ in _cabi.SYMBOLS}
     assert lib.lmg_version() >= 100
+    tuning = open(os.path.join(ROOT, "include", "lmg_b200_tuning.h")).read()
+    tuning = re.sub(r"/\*.*?\*/", "", tuning, flags=re.S)
+    knobs = set(re.findall(r"\b(lmg_[a-z_0-9]+)\s*\(", tuning))
+    assert knobs == {n for n, _, _ in _cabi.EXTRA_SYMBOLS}
+    for name in knobs:
+        assert hasattr(lib, name), name
 
 
 def test_struct_layouts_match_header(lib):

@@ -585,6 +585,7 @@ int lmg_backward_gradients(const lmg_gridmaker* g, const lmg_atoms* a, const flo
     B.plain_reduce = 1;
     B.partial = reinterpret_cast<float*>(ws + L.partial);
     B.out_grid = diffdiff;
+    B.quads = g_quads;
     if (g_forward_mode == 1) {
       E.cnt = nullptr;  // no lists
       e = lmg::launch_emit(E, st);

@@ -1298,16 +1298,19 @@ __global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads(BwdArgs G) {
   }
 }
 
-// backward, index types (MODE 0 of k_backward_warp) on aligned quads
+// The backward passes (modes as in k_backward_warp) on aligned quads.
+template <int MODE, bool BINARY>
 __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads(BwdArgs G) {
+  constexpr bool VEC = MODE == 1 || MODE == 3;
   __shared__ ColBufD bufs[BWD2_WARPS];
   __shared__ ZTabs ztabs[BWD2_WARPS];
   const GMParams& gm = G.gm;
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int items_per_ex = VEC ? G.N * G.T : G.N;
   int item = blockIdx.x * BWD2_WARPS + wid;
   int bl = blockIdx.y;
   int b = G.b0 + bl;
-  if (item >= G.N) return;
+  if (item >= items_per_ex) return;
   ColBufD& buf = bufs[wid];
   ZTabs& zt = ztabs[wid];
 
@@ -1318,20 +1321,32 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads(BwdArgs G) {
     cx = G.center_host[0]; cy = G.center_host[1]; cz = G.center_host[2];
   }
   float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
-  ItemParams P = load_item<false>(G, bl, b, item, ox, oy, oz);
+  ItemParams P = load_item<VEC>(G, bl, b, item, ox, oy, oz);
 
   size_t dim = gm.dim;
-  const float* diff = G.diff + ((size_t)b * G.T + P.chan) * dim * dim * dim;
-  float agx = 0.f, agy = 0.f, agz = 0.f;
+  size_t chan_off = ((size_t)b * G.T + P.chan) * dim * dim * dim;
+  const float* diff = G.diff + chan_off;
+  const float* dens = MODE == 2 ? G.density + chan_off : nullptr;
+  float agx = 0.f, agy = 0.f, agz = 0.f, tg = 0.f;
+  bool want_ag = MODE == 0 || ((MODE == 1 || MODE == 3) && P.w != 0.f);
+  const float Tcull = (MODE == 0 || MODE == 3) ? P.Tcut : fmaxf(P.Tcut, BINARY ? P.Tbin : -1.f);
+  float inx = 0.f, iny = 0.f, inz = 0.f, intg = 0.f;  // MODE 3: incoming gradients of this item
+  if (MODE == 3) {
+    size_t gi = (size_t)b * G.N + item / G.T;
+    inx = G.ag_in[gi * 3]; iny = G.ag_in[gi * 3 + 1]; inz = G.ag_in[gi * 3 + 2];
+    intg = G.tg_in[gi * G.T + P.chan];
+    if (!want_ag) P.valid = false;  // zero-weight channels contribute nothing (src/grid_maker.cpp:573)
+  }
   const float kexp = P.inv_ar2 * NEG2_LOG2E;
   const float k4 = 4.f * P.inv_ar2, kD = -gm.D * P.inv_ar2, kE = -gm.E * P.inv_ar;
+  const float ta = gm.ta, ntb = -gm.tb;
 
   if (P.valid) {
     unsigned nx = P.hix - P.lox, ny = P.hiy - P.loy;
     unsigned ncols = nx * ny;
     float inv_ny = 1.f / (float)ny;
     for (unsigned cbase = 0; cbase < ncols;) {
-      unsigned nkept = compact_columns<ColBufD, true>(buf, P, cbase, ncols, ny, inv_ny, P.Tcut, ox, oy,
+      unsigned nkept = compact_columns<ColBufD, true>(buf, P, cbase, ncols, ny, inv_ny, Tcull, ox, oy,
                                                       gm.res, gm.dim, lane);
       for (unsigned zc = P.loz & ~3u; zc < P.hiz; zc += 4 * QPASS) {
         __syncwarp();
@@ -1343,9 +1358,12 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads(BwdArgs G) {
           bool have = i < nkept;
           float dxy2 = have ? buf.dxy2[i] : CUDART_NAN_F;
           float dx = have ? buf.dx[i] : 0.f, dy = have ? buf.dy[i] : 0.f;
-          const float4* row = reinterpret_cast<const float4*>(diff + (size_t)(have ? buf.row[i] : 0u) * dim + zc);
-          float exy4 = k4 * ex2_approx(dxy2 * kexp);
+          size_t rowoff = (size_t)(have ? buf.row[i] : 0u) * dim + zc;
+          const float4* row = reinterpret_cast<const float4*>(diff + rowoff);
+          float exy = ex2_approx(dxy2 * kexp);
+          float exy4 = k4 * exy;
           float fsum = 0.f;
+          float dotxy = MODE == 3 ? fmaf(dx, inx, dy * iny) : 0.f;
           for (unsigned q0 = 0; q0 < nq; q0 += 4) {
             // up to four quads of the column are requested together, then used
             float4 dv[4];
@@ -1355,7 +1373,7 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads(BwdArgs G) {
               if (q0 + u < nq) {
                 float4 d2 = zt.dz2[q0 + u];
                 float lo = fminf(fminf(d2.x, d2.y), fminf(d2.z, d2.w));  // fminf skips the NaN entries
-                if (__fadd_rn(dxy2, lo) <= P.Tcut) dv[u] = __ldg(row + q0 + u);
+                if (__fadd_rn(dxy2, lo) <= Tcull) dv[u] = __ldg(row + q0 + u);
               }
             }
 #pragma unroll
@@ -1364,21 +1382,76 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads(BwdArgs G) {
                 float4 d2 = zt.dz2[q0 + u], e = zt.ez[q0 + u], dz = zt.dz[q0 + u];
                 float d2v[4] = {d2.x, d2.y, d2.z, d2.w}, ev[4] = {e.x, e.y, e.z, e.w};
                 float dzv[4] = {dz.x, dz.y, dz.z, dz.w}, dvv[4] = {dv[u].x, dv[u].y, dv[u].z, dv[u].w};
+                float dev[4] = {0.f, 0.f, 0.f, 0.f};
+                if (MODE == 2) {
+                  // the density is only needed where this quad can hold a voxel of the atom
+                  float lo = fminf(fminf(d2.x, d2.y), fminf(d2.z, d2.w));
+                  if (__fadd_rn(dxy2, lo) <= Tcull) {
+                    float4 de = __ldg(reinterpret_cast<const float4*>(dens + rowoff) + q0 + u);
+                    dev[0] = de.x; dev[1] = de.y; dev[2] = de.z; dev[3] = de.w;
+                  }
+                }
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                   float rsq = __fadd_rn(dxy2, d2v[j]);
-                  // -(d density / d dist) / dist * dv, src/grid_maker.cu:881-919; rsq == 0 contributes
-                  // nothing because dx = dy = dz = 0 there
-                  float sg = rsq <= P.Tg ? exy4 * ev[j] : fmaf(kE, rsqrt_approx(rsq), kD);
-                  float f = rsq <= P.Tcut ? sg * dvv[j] : 0.f;
-                  fsum += f;
-                  agz = fmaf(f, dzv[j], agz);
+                  float g = exy * ev[j];  // exp(-2 rsq / ar^2)
+                  if (MODE == 0 || MODE == 1) {
+                    // -(d density / d dist) / dist * dv, src/grid_maker.cu:881-919; rsq == 0
+                    // contributes nothing because dx = dy = dz = 0 there
+                    float sg = rsq <= P.Tg ? exy4 * ev[j] : fmaf(kE, rsqrt_approx(rsq), kD);
+                    float f = (want_ag && rsq <= P.Tcut) ? sg * dvv[j] : 0.f;
+                    fsum += f;
+                    agz = fmaf(f, dzv[j], agz);
+                  }
+                  if (MODE == 1) {
+                    float v;
+                    if (BINARY) {
+                      v = rsq < P.Tbin ? 1.f : 0.f;
+                    } else {
+                      float tq = fminf(fmaf(ta, sqrt_approx(rsq * P.inv_ar2), ntb), 0.f);
+                      v = rsq <= P.Tg ? g : tq * tq;
+                      v = rsq <= P.Tcut ? v : 0.f;
+                    }
+                    tg = fmaf(v, dvv[j], tg);
+                  }
+                  if (MODE == 2) {
+                    float v = BINARY ? (rsq < P.Tbin ? 1.f : 0.f)
+                                     : density_precise(rsq, P.ar, P.Tg, P.Tcut, gm.A, gm.B, gm.C);
+                    if (v > 0.f && dev[j] > 0.f) tg += __fdiv_rn(__fmul_rn(dvv[j], v), dev[j]);
+                  }
+                  if (MODE == 3) {
+                    if (rsq <= P.Tcut) {
+                      // second derivatives H_ab = alpha*delta_a*delta_b + [a==b]*beta of the density
+                      // (src/grid_maker.cu:812-878); delta = atom - grid point
+                      float alpha, beta;
+                      if (rsq <= P.Tg) {
+                        alpha = 16.f * g * P.inv_ar2 * P.inv_ar2;
+                        beta = -4.f * g * P.inv_ar2;
+                      } else {
+                        float id = rsqrt_approx(rsq);
+                        float S = fmaf(gm.D * P.inv_ar, rsq * id, gm.E);
+                        beta = S * id * P.inv_ar;
+                        alpha = fmaf(gm.D * P.inv_ar2, id * id, -beta * id * id);
+                      }
+                      float dzj = dzv[j], dvj = dvv[j];
+                      float dot = fmaf(dzj, inz, dotxy);
+                      float wa = P.w * alpha * dot;
+                      float wb = P.w * beta;
+                      float tt = alpha * intg;
+                      float bt = beta * intg;
+                      agx = fmaf(dvj, fmaf(wa, dx, fmaf(wb, inx, fmaf(tt, dx * dx, bt))), agx);
+                      agy = fmaf(dvj, fmaf(wa, dy, fmaf(wb, iny, fmaf(tt, dy * dy, bt))), agy);
+                      agz = fmaf(dvj, fmaf(wa, dzj, fmaf(wb, inz, fmaf(tt, dzj * dzj, bt))), agz);
+                    }
+                  }
                 }
               }
             }
           }
-          agx = fmaf(fsum, dx, agx);
-          agy = fmaf(fsum, dy, agy);
+          if (MODE == 0 || MODE == 1) {
+            agx = fmaf(fsum, dx, agx);
+            agy = fmaf(fsum, dy, agy);
+          }
         }
       }
       __syncwarp();
@@ -1386,15 +1459,104 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads(BwdArgs G) {
   }
 #pragma unroll
   for (int o = 16; o >= 1; o >>= 1) {
-    agx += __shfl_xor_sync(0xffffffffu, agx, o);
-    agy += __shfl_xor_sync(0xffffffffu, agy, o);
-    agz += __shfl_xor_sync(0xffffffffu, agz, o);
+    if (MODE != 2) {
+      agx += __shfl_xor_sync(0xffffffffu, agx, o);
+      agy += __shfl_xor_sync(0xffffffffu, agy, o);
+      agz += __shfl_xor_sync(0xffffffffu, agz, o);
+    }
+    if (MODE == 1 || MODE == 2) tg += __shfl_xor_sync(0xffffffffu, tg, o);
   }
   if (lane == 0) {
-    size_t ai = (size_t)b * G.N + item;
-    G.atom_gradients[ai * 3] = agx;
-    G.atom_gradients[ai * 3 + 1] = agy;
-    G.atom_gradients[ai * 3 + 2] = agz;
+    size_t ai = (size_t)b * G.N + (VEC ? item / G.T : item);
+    if (MODE == 0) {
+      G.atom_gradients[ai * 3] = agx;
+      G.atom_gradients[ai * 3 + 1] = agy;
+      G.atom_gradients[ai * 3 + 2] = agz;
+    } else if (MODE == 1 || MODE == 3) {
+      size_t pi = (size_t)bl * G.N * G.T + item;
+      G.partial[pi * 3] = agx;
+      G.partial[pi * 3 + 1] = agy;
+      G.partial[pi * 3 + 2] = agz;
+      if (MODE == 1) G.type_gradients[ai * G.T + P.chan] = tg;
+    } else {
+      G.relevance[ai] = tg;
+    }
+  }
+}
+
+// Grid term of backward_gradients on aligned quads (see k_gradgrad_scatter).
+__global__ void __launch_bounds__(SCAT_WARPS * 32) k_gradgrad_quads(BwdArgs G) {
+  __shared__ ColBufD bufs[SCAT_WARPS];
+  __shared__ ZTabs ztabs[SCAT_WARPS];
+  const GMParams& gm = G.gm;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int item = blockIdx.x * SCAT_WARPS + wid;
+  int bl = blockIdx.y;
+  int b = G.b0 + bl;
+  if (item >= G.N * G.T) return;
+  ColBufD& buf = bufs[wid];
+  ZTabs& zt = ztabs[wid];
+
+  float cx, cy, cz;
+  if (G.centers != nullptr) {
+    cx = G.centers[b * 3]; cy = G.centers[b * 3 + 1]; cz = G.centers[b * 3 + 2];
+  } else {
+    cx = G.center_host[0]; cy = G.center_host[1]; cz = G.center_host[2];
+  }
+  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
+  ItemParams P = load_item<true>(G, bl, b, item, ox, oy, oz);
+  if (!P.valid || P.w == 0.f) return;
+
+  size_t dim = gm.dim;
+  float* out = G.out_grid + ((size_t)b * G.T + P.chan) * dim * dim * dim;
+  size_t gi = (size_t)b * G.N + item / G.T;
+  const float inx = G.ag_in[gi * 3], iny = G.ag_in[gi * 3 + 1], inz = G.ag_in[gi * 3 + 2];
+  const float intg = G.tg_in[gi * G.T + P.chan];
+  const float kexp = P.inv_ar2 * NEG2_LOG2E;
+  const float k4 = 4.f * P.inv_ar2 * P.w, kD = -gm.D * P.inv_ar2 * P.w, kE = -gm.E * P.inv_ar * P.w;
+  const float ta = gm.ta, ntb = -gm.tb;
+
+  unsigned nx = P.hix - P.lox, ny = P.hiy - P.loy;
+  unsigned ncols = nx * ny;
+  float inv_ny = 1.f / (float)ny;
+  for (unsigned cbase = 0; cbase < ncols;) {
+    unsigned nkept = compact_columns<ColBufD, true>(buf, P, cbase, ncols, ny, inv_ny, P.Tcut, ox, oy,
+                                                    gm.res, gm.dim, lane);
+    for (unsigned zc = P.loz & ~3u; zc < P.hiz; zc += 4 * QPASS) {
+      __syncwarp();
+      fill_ztabs(zt, zc, P, oz, gm.res, kexp, lane);
+      __syncwarp();
+      unsigned nq = min((unsigned)QPASS, (P.hiz - zc + 3) >> 2);
+      for (unsigned c0 = 0; c0 < nkept; c0 += 32) {
+        unsigned i = c0 + lane;
+        bool have = i < nkept;
+        float dxy2 = have ? buf.dxy2[i] : CUDART_NAN_F;
+        float dotxy = have ? fmaf(buf.dx[i], inx, buf.dy[i] * iny) : 0.f;
+        float* row = out + (size_t)(have ? buf.row[i] : 0u) * dim + zc;
+        float exy = ex2_approx(dxy2 * kexp);
+        for (unsigned q = 0; q < nq; q++) {
+          float4 d2 = zt.dz2[q], e = zt.ez[q], dz = zt.dz[q];
+          float d2v[4] = {d2.x, d2.y, d2.z, d2.w}, ev[4] = {e.x, e.y, e.z, e.w};
+          float dzv[4] = {dz.x, dz.y, dz.z, dz.w}, v[4];
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            float rsq = __fadd_rn(dxy2, d2v[j]);
+            float g = exy * ev[j];
+            float tq = fminf(fmaf(ta, sqrt_approx(rsq * P.inv_ar2), ntb), 0.f);
+            bool gauss = rsq <= P.Tg;
+            float val = gauss ? g : tq * tq;
+            float sg = gauss ? k4 * g : fmaf(kE, rsqrt_approx(rsq), kD);
+            float dot = rsq > 0.f ? fmaf(dzv[j], inz, dotxy) : 0.f;
+            float gval = fmaf(val, intg, sg * dot);
+            v[j] = rsq <= P.Tcut ? gval : 0.f;
+          }
+          unsigned any = __float_as_uint(v[0]) | __float_as_uint(v[1]) | __float_as_uint(v[2]) |
+                         __float_as_uint(v[3]);
+          if (any != 0u) red_add_v4(row + 4 * q, v[0], v[1], v[2], v[3]);
+        }
+      }
+    }
+    __syncwarp();
   }
 }
 
@@ -1477,22 +1639,28 @@ cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st) {
   if (items == 0 || G.nb == 0) return cudaSuccess;
   dim3 grid((unsigned)((items + BWD2_WARPS - 1) / BWD2_WARPS), G.nb);
   bool bin = G.gm.binary != 0;
+  // rows of diff (and of the density, for relevance) start on 16-byte boundaries
+  bool quads = G.quads && G.gm.dim % 4 == 0 && (uintptr_t)G.diff % 16 == 0 &&
+               (mode != 2 || (uintptr_t)G.density % 16 == 0);
   if (mode == 0) {
-    if (G.quads && G.gm.dim % 4 == 0 && (uintptr_t)G.diff % 16 == 0)
-      k_backward_quads<<<grid, BWD2_WARPS * 32, 0, st>>>(G);
-    else
-      k_backward_warp<0, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    if (quads) k_backward_quads<0, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    else k_backward_warp<0, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
   } else if (mode == 1) {
-    if (bin) k_backward_warp<1, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    if (quads && bin) k_backward_quads<1, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    else if (quads) k_backward_quads<1, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    else if (bin) k_backward_warp<1, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
     else k_backward_warp<1, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
     int n = G.nb * G.N;
     k_reduce_types<<<(n + 255) / 256, 256, 0, st>>>(G);
   } else if (mode == 3) {
-    k_backward_warp<3, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    if (quads) k_backward_quads<3, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    else k_backward_warp<3, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
     int n = G.nb * G.N;
     k_reduce_types<<<(n + 255) / 256, 256, 0, st>>>(G);
   } else {
-    if (bin) k_backward_warp<2, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    if (quads && bin) k_backward_quads<2, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    else if (quads) k_backward_quads<2, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    else if (bin) k_backward_warp<2, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
     else k_backward_warp<2, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
   }
   return cudaGetLastError();
@@ -1502,7 +1670,10 @@ cudaError_t launch_gradgrad_scatter(const BwdArgs& G, cudaStream_t st) {
   long items = (long)G.N * G.T;
   if (items == 0 || G.nb == 0) return cudaSuccess;
   dim3 grid((unsigned)((items + SCAT_WARPS - 1) / SCAT_WARPS), G.nb);
-  k_gradgrad_scatter<<<grid, SCAT_WARPS * 32, 0, st>>>(G);
+  if (G.quads && G.gm.dim % 4 == 0 && (uintptr_t)G.out_grid % 16 == 0)
+    k_gradgrad_quads<<<grid, SCAT_WARPS * 32, 0, st>>>(G);
+  else
+    k_gradgrad_scatter<<<grid, SCAT_WARPS * 32, 0, st>>>(G);
   return cudaGetLastError();
 }
 

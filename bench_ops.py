@@ -12,7 +12,11 @@ inputs with the shapes of the benchmark configurations:
 * vector types, 28x96^3 @0.25 A, batch 4 x 3000 atoms, Dirichlet(0.3) type vectors, type-indexed radii
   1.7 A x U[0.8,1.2] (forward, backward, backward_gradients) - compute bound: pair evaluations/s are
   reported next to the byte figure;
-* interpolation 28x48^3 -> 28x48^3, batch 48, random rotation + translation.
+* interpolation 28x48^3 -> 28x48^3, batch 48, random rotation + translation;
+* provider: batches of 50 examples (receptor 2000-3900 + ligand 20-60 pre-typed records each, read
+  once from .gninatypes files written to a temporary directory) assembled by
+  ``ExampleProvider.next_device_batch`` (one host-to-device copy + the decode kernel) and gridded with
+  random rotations: wall-clock examples/s of records -> grids, host work included.
 """
 import argparse
 import json
@@ -40,7 +44,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--ops", default="forward,forward_binary,backward,relevance,forward_vector,"
-                                      "backward_vector,backward_gradients,interpolate")
+                                      "backward_vector,backward_gradients,interpolate,provider")
     args = ap.parse_args()
     import torch
     import libmolgrid_b200 as lmg
@@ -154,6 +158,50 @@ def main():
         ms = timeit(lambda: gi.forward(src, trs, dst))
         report("interpolate", "28x48^3 -> 28x48^3, batch 48, random rotation and translation", ms, B,
                2 * src.numel() * 4)
+
+
+    # ---- records -> grids -----------------------------------------------------------------------
+    if "provider" in ops:
+        import tempfile
+        import time
+        from libmolgrid_b200 import coord_cache
+        rng = np.random.default_rng(1006)
+        B, nex = 50, 100
+        with tempfile.TemporaryDirectory() as tmp:
+            lines = []
+            for i in range(nex):
+                n = int(rng.integers(2000, 3900))
+                pts = cases.blob_batch(2000 + i, 1, n, n, T)[0][0]
+                coord_cache.write_gninatypes(os.path.join(tmp, "r%d.gninatypes" % i), pts, rng.integers(2, 28, n))
+                m = int(rng.integers(20, 60))
+                coord_cache.write_gninatypes(os.path.join(tmp, "l%d.gninatypes" % i),
+                                             cases.sphere(rng, m, 4.0), rng.integers(2, 21, m))
+                lines.append("1 r%d.gninatypes l%d.gninatypes" % (i, i))
+            with open(os.path.join(tmp, "list.types"), "w") as f:
+                f.write("\n".join(lines) + "\n")
+            prov = coord_cache.ExampleProvider(data_root=tmp)
+            prov.populate(os.path.join(tmp, "list.types"))
+            g = lmg.GridMaker(0.5, 23.5)
+            grid = torch.empty((B,) + g.grid_dimensions(prov.num_types()), device=dev)
+            nbytes = 0
+
+            def one():
+                batch = prov.next_device_batch(B)
+                g.forward(batch, grid, 2.0, True)
+                return batch
+
+            for _ in range(4):
+                one()                       # also reads every file once
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(args.reps):
+                batch = one()
+                nbytes += int(batch.n_atoms.numel()) * 4 + int(batch.coords.shape[0]) * 0
+            torch.cuda.synchronize()
+            wall = (time.perf_counter() - t0) / args.reps
+            h2d = float(batch.n_atoms.sum().item()) * 16
+        report("provider", "records -> device batch -> forward, batch 50, wall clock incl. host assembly",
+               wall * 1e3, B, grid.numel() * 4 + h2d, {"h2d_bytes_per_call": h2d})
 
 
 if __name__ == "__main__":

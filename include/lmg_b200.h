@@ -70,6 +70,10 @@ typedef struct lmg_transform {
  * (python/bindings.in.cpp:400, src/libmolgrid.cpp:11).  Host only. */
 int lmg_transform_random(lmg_transform* t, const float center[3], float random_translate,
                          int random_rotate);
+/* n such transforms drawn one after the other into t[n] (the loop of
+ * include/libmolgrid/grid_maker.h:194-201, one Transform per example in order). */
+int lmg_transform_random_batch(lmg_transform* t, int n, const float center[3], float random_translate,
+                               int random_rotate);
 void lmg_set_random_seed(unsigned seed);
 
 /* The atoms of a batch of `batch` examples, padded to `max_atoms` per example: the argument
@@ -185,6 +189,37 @@ int lmg_interpolater_init(lmg_interpolater* gi, float in_resolution, float in_di
 int lmg_interpolate(const lmg_interpolater* gi, int batch, int nchannels, const float* in,
                     const lmg_transform* transforms, const float* in_centers,
                     const float* out_centers, float* out, void* stream);
+
+/* ---- batch assembly from pre-typed atom records --------------------------------------------
+ * A record is the 16-byte {float x, y, z; int type} of the reference's .gninatypes / .molcache2 files
+ * (src/coord_cache.cpp:82-148).  One call turns the records of a whole batch into the padded batch
+ * arrays lmg_forward / lmg_backward read: per coordinate set it looks channel and radius up in the
+ * typer's tables (AtomIndexTyper::get_int_type, src/atom_typer.cpp:167-178; type numbers outside
+ * [0, LMG_RECORD_TYPES) use the GenericMetal row), adds the set's type offset (Example::merge_coordinates,
+ * src/example.cpp:69-100) and writes the atoms to their slots of the example.  Atoms whose mapped type
+ * is negative keep their slot with type -1 and radius 0 (the reference drops them; the gridding
+ * kernels skip them, so grids and gradients agree).  Optionally each example's grid centre - the mean
+ * of the mapped atoms of its centre set, the reference's default for forward(Example, grid)
+ * (src/grid_maker.cpp:126-137, src/coordinateset.cpp:228-243) - is written to centers[batch][3]
+ * and into transforms[batch].center.  All pointers are device pointers. */
+#define LMG_RECORD_TYPES 28
+typedef struct lmg_record_set {
+  long long first_record; /* index of the set's first record in `records` */
+  int count;              /* records in the set */
+  int example;            /* destination example */
+  int typer;              /* row block of type_map / type_radius that applies */
+  int type_offset;        /* added to mapped types: the types of earlier sets of the example */
+  int dst_atom;           /* first atom slot of the set within the example */
+  int is_center_set;      /* 1 for the set whose mean is the example's grid centre */
+} lmg_record_set;
+
+/* type_map[ntypers][LMG_RECORD_TYPES] (channel or -1) and type_radius[ntypers][LMG_RECORD_TYPES];
+ * max_set_records = the largest `count`; *status (device int) becomes 1 if a set does not fit
+ * max_atoms.  centers and transforms may be NULL. */
+int lmg_decode_records(const void* records, const lmg_record_set* sets, int nsets, const int* type_map,
+                       const float* type_radius, int batch, int max_atoms, int max_set_records,
+                       float* coords, float* type_index, float* radii, float* centers,
+                       lmg_transform* transforms, int* status, void* stream);
 
 /* Reads back (synchronising `stream`) the status word that kernels of the last call that used
  * `workspace` wrote: 0, or LMG_ERR_OUT_OF_RANGE / LMG_ERR_INVALID_ARGUMENT when an atom's type

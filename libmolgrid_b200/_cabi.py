@@ -45,6 +45,14 @@ class InterpolaterStruct(ctypes.Structure):
                 ("in_dim", ctypes.c_uint), ("out_dim", ctypes.c_uint)]
 
 
+class RecordSetStruct(ctypes.Structure):
+    _fields_ = [("first_record", ctypes.c_longlong), ("count", ctypes.c_int), ("example", ctypes.c_int),
+                ("typer", ctypes.c_int), ("type_offset", ctypes.c_int), ("dst_atom", ctypes.c_int),
+                ("is_center_set", ctypes.c_int)]
+
+
+RECORD_TYPES = 28
+
 # every symbol include/lmg_b200.h declares: (name, restype, argtypes)
 _VP = ctypes.c_void_p
 _GM = ctypes.POINTER(GridMakerStruct)
@@ -55,6 +63,8 @@ SYMBOLS = [
     ("lmg_gridmaker_init", ctypes.c_int, [_GM, ctypes.c_float, ctypes.c_float, ctypes.c_int, ctypes.c_int,
                                           ctypes.c_float, ctypes.c_float]),
     ("lmg_transform_random", ctypes.c_int, [_TR, ctypes.c_float * 3, ctypes.c_float, ctypes.c_int]),
+    ("lmg_transform_random_batch", ctypes.c_int, [_VP, ctypes.c_int, ctypes.c_float * 3, ctypes.c_float,
+                                                  ctypes.c_int]),
     ("lmg_set_random_seed", None, [ctypes.c_uint]),
     ("lmg_workspace_bytes", ctypes.c_size_t, [_GM, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                               ctypes.c_int]),
@@ -71,6 +81,8 @@ SYMBOLS = [
                                              ctypes.c_float]),
     ("lmg_interpolate", ctypes.c_int, [_GI, ctypes.c_int, ctypes.c_int, _VP, _TR, c_float_p, c_float_p,
                                        _VP, _VP]),
+    ("lmg_decode_records", ctypes.c_int, [_VP, _VP, ctypes.c_int, _VP, _VP, ctypes.c_int, ctypes.c_int,
+                                          ctypes.c_int, _VP, _VP, _VP, _VP, _VP, _VP, _VP]),
     ("lmg_check_status", ctypes.c_int, [_VP, _VP]),
     ("lmg_last_error", ctypes.c_char_p, []),
     ("lmg_version", ctypes.c_int, []),

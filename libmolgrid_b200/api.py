@@ -429,7 +429,15 @@ class GridMaker(object):
           (plus the ``transforms=`` / ``n_atoms=`` extensions of :meth:`forward_arrays`).
         """
         from .coordinates import CoordinateSet, Example
+        from .coord_cache import DeviceBatch
         a0 = args[0] if args else kw.get("example", kw.get("examples", kw.get("examplevec")))
+        if isinstance(a0, DeviceBatch):
+            rest = list(args[1:])
+            grid = rest[0] if rest else kw["grid"]
+            rt = rest[1] if len(rest) > 1 else kw.get("random_translation", 0.0)
+            rr = rest[2] if len(rest) > 2 else kw.get("random_rotation", False)
+            return self.forward_arrays(a0.centers, a0.coords, a0.type_index, a0.radii, grid,
+                                       transforms=self.batch_transforms(a0, rt, rr), n_atoms=a0.n_atoms)
         if isinstance(a0, Example):
             rest = list(args[1:])
             if rest and isinstance(rest[0], Transform):
@@ -451,6 +459,20 @@ class GridMaker(object):
                 return self.forward_arrays(center, cs.coords, cs.type_vector, cs.radii, grid)
             return self.forward_arrays(center, cs.coords, cs.type_index, cs.radii, grid)
         return self.forward_arrays(*args, **kw)
+
+    @staticmethod
+    def batch_transforms(batch, random_translation=0.0, random_rotation=False):
+        """(B,10) device array of per-example random Transforms about the batch's grid centres, drawn
+        in example order like the reference's loop (include/libmolgrid/grid_maker.h:194-201).  Keep
+        it to hand the same transforms to ``backward``."""
+        B = len(batch)
+        rows = torch.empty((B, 10), dtype=torch.float32)   # B x lmg_transform
+        zero = (ctypes.c_float * 3)(0, 0, 0)
+        check(_cabi.lib().lmg_transform_random_batch(ctypes.c_void_p(rows.data_ptr()), B, zero,
+                                                     float(random_translation), int(bool(random_rotation))))
+        tr = rows.to(batch.centers.device)
+        tr[:, 4:7] = batch.centers
+        return tr
 
     @staticmethod
     def _default_center(ex):
@@ -554,6 +576,13 @@ class GridMaker(object):
         ``backward(center, coordinate_set, diff, atom_gradients[, type_gradients])`` or
         ``backward(center, coords, types, radii, diff, atom_gradients[, type_gradients])``."""
         from .coordinates import CoordinateSet
+        from .coord_cache import DeviceBatch
+        if args and isinstance(args[0], DeviceBatch):
+            # backward(batch, diff, atom_gradients, transforms=...): the arrays of a DeviceBatch
+            batch, diff, ag = args[:3]
+            tr = args[3] if len(args) > 3 else kw.get("transforms")
+            return self.backward_arrays(batch.centers, batch.coords, batch.type_index, batch.radii, diff, ag,
+                                        transforms=tr, n_atoms=batch.n_atoms)
         if len(args) >= 2 and isinstance(args[1], CoordinateSet):
             center, cs, diff, ag = args[:4]
             tg = args[4] if len(args) > 4 else kw.get("type_gradients")

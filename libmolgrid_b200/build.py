@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "liblmg_b200.so")
-SOURCES = ["lmg_gridmaker.cu", "lmg_misc.cu", "lmg_cabi.cu", "lmg_noalloc.cu"]
+SOURCES = ["lmg_gridmaker.cu", "lmg_misc.cu", "lmg_cabi.cu", "lmg_noalloc.cu", "lmg_records.cu"]
 HEADERS = ["lmg_device.cuh", "lmg_launch.h", "lmg_misc.h", os.path.join("..", "..", "include", "lmg_b200.h")]
 
 NVCC_FLAGS = [

@@ -12,10 +12,13 @@ Atoms whose mapped type is negative are dropped, as in the reference.  Records a
 vectorised numpy on the host; the result is a CoordinateSet whose arrays go to the GPU in one copy.
 Shuffling, balancing, stratification and molecule parsing (OpenBabel) are not part of this path.
 """
+import ctypes
 import os
 
 import numpy as np
+import torch
 
+from . import _cabi
 from .atom_typing import default_ligand_typer, default_receptor_typer
 from .coordinates import CoordinateSet, Example, ExampleVec
 
@@ -106,6 +109,7 @@ class CoordCache(object):
         self.typer = typer or default_ligand_typer()
         self.data_root = data_root
         self.cache = None
+        self._raw = {}
         if molcache:
             if not os.path.exists(molcache):
                 molcache = os.path.join(data_root, molcache)
@@ -116,6 +120,31 @@ class CoordCache(object):
 
     def get_type_names(self):
         return self.typer.get_type_names()
+
+    def records(self, fname):
+        """The raw records of ``fname`` (kept in memory after the first read)."""
+        rec = self._raw.get(fname)
+        if rec is None:
+            if self.cache is not None and fname in self.cache:
+                rec = self.cache.records(fname)
+            elif fname.endswith("none"):
+                rec = np.zeros(0, dtype=RECORD)
+            elif fname.endswith(".gninatypes"):
+                full = fname if os.path.isabs(fname) or not self.data_root else os.path.join(self.data_root, fname)
+                try:
+                    raw = np.fromfile(full, dtype=np.uint8)
+                except OSError:
+                    raise ValueError("Could not read " + full)
+                rec = raw[:raw.size // RECORD.itemsize * RECORD.itemsize].view(RECORD)
+            else:
+                raise ValueError("Only pre-typed input (.gninatypes, .molcache2) is read here: " + fname)
+            self._raw[fname] = rec
+        return rec
+
+    def tables(self):
+        """(channel or -1, radius) for the record type numbers 0..27, as the device decoder wants them."""
+        t, r = self.typer.map_types(np.arange(_cabi.RECORD_TYPES))
+        return np.asarray(t, dtype=np.int32), np.asarray(r, dtype=np.float32)
 
     def make_coords(self, fname):
         if self.cache is not None and fname in self.cache:
@@ -166,6 +195,29 @@ class ExampleRef(object):
             raise ValueError("Missing molecular data in line: " + line)
 
 
+_SET_TABLE = np.dtype([("first", "<i8"), ("count", "<i4"), ("example", "<i4"), ("typer", "<i4"),
+                       ("toff", "<i4"), ("dst", "<i4"), ("center", "<i4")])   # = lmg_record_set
+
+
+class DeviceBatch(object):
+    """A batch assembled on the GPU by ``ExampleProvider.next_device_batch``: padded
+    ``coords (B,N,3)``, ``type_index (B,N)`` (-1 for atoms the typer does not map), ``radii (B,N)``,
+    ``n_atoms (B)``, the default grid ``centers (B,3)`` and ``labels (B,L)``.  ``GridMaker.forward``
+    and ``GridMaker.backward`` take it in place of a list of Examples."""
+
+    def __init__(self, coords, type_index, radii, n_atoms, centers, labels, num_types, keep):
+        self.coords, self.type_index, self.radii = coords, type_index, radii
+        self.n_atoms, self.centers, self.labels = n_atoms, centers, labels
+        self._num_types = num_types
+        self._keep = keep  # staging buffers of this batch
+
+    def __len__(self):
+        return int(self.coords.shape[0])
+
+    def num_types(self):
+        return self._num_types
+
+
 class ExampleProvider(object):
     """Examples in file order: ``populate`` reads example lists, ``next``/``next_batch`` walk them
     cyclically.  The typers apply to the files of a line in order, the last one repeating
@@ -179,6 +231,10 @@ class ExampleProvider(object):
         self.refs = []
         self.pos = 0
         self._num_labels = num_labels
+        self._stage = [(None, None), (None, None)]   # two pinned staging buffers (+ "copy done" events)
+        self._stage_slot = 0
+        self._packs = {}
+        self._tables = None
 
     def populate(self, fname, num_labels=-1):
         names = [fname] if isinstance(fname, str) else list(fname)
@@ -228,3 +284,102 @@ class ExampleProvider(object):
 
     def next_batch(self, batch_size):
         return ExampleVec([self.next() for _ in range(int(batch_size))])
+
+    def _packed(self, i):
+        """Example i ready for staging: the bytes of all its sets' records back to back, and per set
+        the record count, typer, type offset and first atom slot (built once per example)."""
+        p = self._packs.get(i)
+        if p is None:
+            ref = self.refs[i]
+            recs, counts, typers, toffs, dst = [], [], [], [], []
+            toffset = natoms = 0
+            for k, fname in enumerate(ref.files):
+                ci = min(k, len(self.caches) - 1)
+                r = self.caches[ci].records(fname)
+                recs.append(np.ascontiguousarray(r).view(np.uint8))
+                counts.append(len(r)); typers.append(ci); toffs.append(toffset); dst.append(natoms)
+                natoms += len(r)
+                toffset += self.caches[ci].num_types()
+            p = (np.concatenate(recs) if recs else np.zeros(0, np.uint8), np.array(counts, np.int32),
+                 np.array(typers, np.int32), np.array(toffs, np.int32), np.array(dst, np.int32))
+            self._packs[i] = p
+        return p
+
+    def next_device_batch(self, batch_size, device=None):
+        """The next ``batch_size`` examples as a DeviceBatch.  The raw records of all their files go
+        to the GPU in ONE copy from pinned memory together with a table of their coordinate sets; a
+        kernel does the type lookup, the merge of each example's sets with type offsets and the
+        padding (``lmg_decode_records``).  Work is queued on the current stream of ``device``."""
+        if not self.refs:
+            raise RuntimeError("No examples: populate() first")
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device: this library has no CPU path")
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        B = int(batch_size)
+        idx = [(self.pos + k) % len(self.refs) for k in range(B)]
+        self.pos = (self.pos + B) % len(self.refs)
+        packs = [self._packed(i) for i in idx]
+        nl = len(self.refs[idx[0]].labels)
+        # set table, vectorised over the batch
+        nset = np.array([len(p[1]) for p in packs], dtype=np.int64)
+        counts = np.concatenate([p[1] for p in packs])
+        typers = np.concatenate([p[2] for p in packs])
+        toffs = np.concatenate([p[3] for p in packs])
+        dst = np.concatenate([p[4] for p in packs])
+        nsets = int(counts.size)
+        table = np.zeros(nsets, dtype=_SET_TABLE)
+        table["first"] = np.concatenate(([0], np.cumsum(counts[:-1])))
+        table["count"], table["typer"], table["toff"], table["dst"] = counts, typers, toffs, dst
+        table["example"] = np.repeat(np.arange(B), nset)
+        last = np.cumsum(nset) - 1
+        table["center"][last] = 1
+        n_atoms = np.array([p[0].size // RECORD.itemsize for p in packs], dtype=np.int32)
+        nmax = max(1, int(n_atoms.max()))
+        labels = np.array([list(self.refs[i].labels)[:nl] for i in idx], dtype=np.float32).reshape(B, nl)
+        if self._tables is None:
+            tabs = [c.tables() for c in self.caches]
+            self._tables = (np.concatenate([t for t, _ in tabs]).astype(np.int32).view(np.uint8),
+                            np.concatenate([r for _, r in tabs]).astype(np.float32).view(np.uint8))
+        # one pinned blob: records of every example | set table | atom counts | type tables | labels
+        small = [table.view(np.uint8), n_atoms.view(np.uint8), self._tables[0], self._tables[1],
+                 labels.view(np.uint8).reshape(-1)]
+        rec_bytes = int(n_atoms.sum()) * RECORD.itemsize
+        offs, total = [0], (rec_bytes + 15) // 16 * 16
+        for p in small:
+            offs.append(total)
+            total += (p.size + 15) // 16 * 16
+        slot = self._stage_slot
+        self._stage_slot ^= 1
+        host, busy = self._stage[slot]
+        if busy is not None:
+            busy.synchronize()               # the copy that last read this staging buffer has finished
+        if host is None or host.numel() < total:
+            host = torch.empty(max(2 * total, 1 << 20), dtype=torch.uint8).pin_memory()
+        hv = host.numpy()
+        o = 0
+        for p in packs:
+            hv[o:o + p[0].size] = p[0]
+            o += p[0].size
+        for p, o in zip(small, offs[1:]):
+            hv[o:o + p.size] = p
+        blob = torch.empty(total, dtype=torch.uint8, device=dev)
+        blob.copy_(host[:total], non_blocking=True)
+        busy = torch.cuda.Event()
+        busy.record(torch.cuda.current_stream(dev))
+        self._stage[slot] = (host, busy)
+        coords = torch.empty((B, nmax, 3), dtype=torch.float32, device=dev)
+        types = torch.empty((B, nmax), dtype=torch.float32, device=dev)
+        radii = torch.empty((B, nmax), dtype=torch.float32, device=dev)
+        centers = torch.empty((B, 3), dtype=torch.float32, device=dev)
+        status = torch.empty(1, dtype=torch.int32, device=dev)
+        base = blob.data_ptr()
+        vp = ctypes.c_void_p
+        _cabi.check(_cabi.lib().lmg_decode_records(
+            vp(base + offs[0]), vp(base + offs[1]), nsets, vp(base + offs[3]), vp(base + offs[4]), B, nmax,
+            int(counts.max()) if nsets else 0, vp(coords.data_ptr()), vp(types.data_ptr()),
+            vp(radii.data_ptr()), vp(centers.data_ptr()), None, vp(status.data_ptr()),
+            vp(torch.cuda.current_stream(dev).cuda_stream)))
+        dn = blob[offs[2]:offs[2] + 4 * B].view(torch.int32)
+        lab = blob[offs[5]:offs[5] + 4 * B * nl].view(torch.float32).view(B, nl)
+        ntypes = self.num_types()
+        return DeviceBatch(coords, types, radii, dn, centers, lab, ntypes, (blob, status, host))

@@ -341,6 +341,16 @@ int lmg_transform_random(lmg_transform* t, const float center[3], float random_t
   return LMG_OK;
 }
 
+int lmg_transform_random_batch(lmg_transform* t, int n, const float center[3], float random_translate,
+                               int random_rotate) {
+  if (n < 0) return fail(LMG_ERR_INVALID_ARGUMENT, "negative size");
+  for (int i = 0; i < n; i++) {
+    int rc = lmg_transform_random(&t[i], center, random_translate, random_rotate);
+    if (rc) return rc;
+  }
+  return LMG_OK;
+}
+
 size_t lmg_workspace_bytes(const lmg_gridmaker* g, int op, int batch, int max_atoms, int ntypes,
                            int vector_types) {
   if (g == nullptr || batch < 0 || max_atoms < 0 || ntypes <= 0) return 0;

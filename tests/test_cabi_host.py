@@ -37,6 +37,7 @@ def test_struct_layouts_match_header(lib):
     assert ctypes.sizeof(_cabi.GridMakerStruct) == 13 * 4
     assert ctypes.sizeof(_cabi.TransformStruct) == 40
     assert ctypes.sizeof(_cabi.InterpolaterStruct) == 24
+    assert ctypes.sizeof(_cabi.RecordSetStruct) == 32
     assert ctypes.sizeof(_cabi.AtomsStruct) == 3 * 4 + 4 + 6 * 8 + 3 * 4 + 4 + 2 * 8
 
 

@@ -1,0 +1,121 @@
+"""Batch assembly on the device (lmg_decode_records) against the host-side path: the same atoms, the
+same grid centres bit for bit, the same grids and gradients."""
+import numpy as np
+import pytest
+import torch
+
+import libmolgrid_b200 as molgrid
+from libmolgrid_b200 import coord_cache
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def provider_dir(tmp_path):
+    rng = np.random.default_rng(31)
+    lines = []
+    for i in range(7):
+        nrec, nlig = int(rng.integers(150, 400)), int(rng.integers(5, 40))
+        for name, n, spread in (("r%d.gninatypes" % i, nrec, 9.0), ("l%d.gninatypes" % i, nlig, 2.5)):
+            coords = rng.normal(size=(n, 3)) * spread + (3.0, -2.0, 1.0)
+            types = rng.integers(0, 30, n)     # includes hydrogens (dropped) and out-of-table numbers
+            coord_cache.write_gninatypes(tmp_path / name, coords, types)
+        lines.append("%d %.3f r%d.gninatypes l%d.gninatypes" % (i % 2, rng.normal(), i, i))
+    # an example whose ligand has no mapped atom at all, and one with an empty ("none") ligand
+    coord_cache.write_gninatypes(tmp_path / "h.gninatypes", rng.normal(size=(4, 3)), [0, 1, 0, 1])
+    lines.append("0 0.5 r0.gninatypes h.gninatypes")
+    lines.append("1 1.5 r1.gninatypes none")
+    (tmp_path / "list.types").write_text("\n".join(lines) + "\n")
+    return tmp_path
+
+
+def providers(d):
+    out = []
+    for _ in range(2):
+        p = coord_cache.ExampleProvider(data_root=str(d))
+        p.populate(str(d / "list.types"))
+        out.append(p)
+    return out
+
+
+def test_device_batch_matches_host_examples(provider_dir):
+    pa, pb = providers(provider_dir)
+    B = 9
+    exs = pa.next_batch(B)
+    batch = pb.next_device_batch(B)
+    torch.cuda.synchronize()
+    assert len(batch) == B and batch.num_types() == 28 and pb.pos == pa.pos
+    labels = np.zeros((B, 2), np.float32)
+    exs.extract_labels(labels)
+    np.testing.assert_array_equal(batch.labels.cpu().numpy(), labels)
+    coords, types, radii = (x.cpu().numpy() for x in (batch.coords, batch.type_index, batch.radii))
+    ns = batch.n_atoms.cpu().numpy()
+    for b, ex in enumerate(exs):
+        m = ex.merge_coordinates()
+        keep = types[b, :ns[b]] >= 0
+        assert keep.sum() == m.size()
+        np.testing.assert_array_equal(coords[b, :ns[b]][keep], m.coords.tonumpy())
+        np.testing.assert_array_equal(types[b, :ns[b]][keep], m.type_index.tonumpy())
+        np.testing.assert_array_equal(radii[b, :ns[b]][keep], m.radii.tonumpy())
+        assert np.all(radii[b, :ns[b]][~keep] == 0)
+        want = np.array(tuple(molgrid.GridMaker._default_center(ex)), np.float32)
+        np.testing.assert_array_equal(batch.centers[b].cpu().numpy(), want)   # bit for bit
+    assert np.all(batch.centers[7].cpu().numpy() == 0) and np.all(batch.centers[8].cpu().numpy() == 0)
+
+    gm = molgrid.GridMaker(0.5, 15.5)
+    dims = gm.grid_dimensions(28)
+    a, c = torch.zeros((B,) + dims, device="cuda"), torch.zeros((B,) + dims, device="cuda")
+    molgrid.set_random_seed(5)
+    gm.forward(exs, a, random_translation=1.5, random_rotation=True)
+    molgrid.set_random_seed(5)
+    tr = gm.batch_transforms(batch, 1.5, True)
+    gm.forward_arrays(batch.centers, batch.coords, batch.type_index, batch.radii, c, transforms=tr,
+                      n_atoms=batch.n_atoms)
+    assert float(a.sum()) > 100
+    torch.testing.assert_close(a, c, rtol=1e-5, atol=1e-6)
+    molgrid.set_random_seed(5)
+    gm.forward(batch, c, 1.5, True)          # the overload that draws the transforms itself
+    torch.testing.assert_close(a, c, rtol=1e-5, atol=1e-6)
+
+    # backward on the batch equals backward on each merged example with the same transform
+    diff = torch.randn((B,) + dims, device="cuda")
+    grads = torch.zeros((B, batch.coords.shape[1], 3), device="cuda")
+    gm.backward(batch, diff, grads, transforms=tr)
+    trs = tr.cpu().numpy()
+    for b in (0, 3, 6):
+        m = exs[b].merge_coordinates()
+        t = molgrid.Transform(molgrid.Quaternion(*trs[b, :4]), tuple(trs[b, 4:7]), tuple(trs[b, 7:]))
+        moved = m.clone()
+        t.forward(moved, moved)
+        one = torch.zeros((m.size(), 3), device="cuda")
+        gm.backward(t.get_rotation_center(), moved, diff[b], one)
+        keep = (batch.type_index[b, :ns[b]] >= 0)
+        got = grads[b, :ns[b]][keep]
+        scale = max(1.0, float(one.abs().max()))
+        # the batch path differentiates with respect to the transformed position as well
+        assert torch.allclose(got, one, rtol=1e-4, atol=1e-5 * scale)
+        assert float(grads[b, :ns[b]][~keep].abs().sum()) == 0
+
+
+def test_decode_reports_sets_that_do_not_fit(provider_dir):
+    from libmolgrid_b200 import _cabi
+    import ctypes
+    rec = np.zeros(8, dtype=coord_cache.RECORD)
+    rec["type"] = 2
+    table = (_cabi.RecordSetStruct * 1)(_cabi.RecordSetStruct(0, 8, 0, 0, 0, 0, 1))
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    drec = d(rec.view(np.uint8))
+    dtab = d(np.frombuffer(bytes(table), dtype=np.uint8).copy())
+    tmap, trad = d(np.arange(28, dtype=np.int32)), d(np.ones(28, np.float32))
+    coords, types, radii = (torch.zeros(s, device="cuda") for s in ((1, 4, 3), (1, 4), (1, 4)))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    vp = ctypes.c_void_p
+    rc = _cabi.lib().lmg_decode_records(vp(drec.data_ptr()), vp(dtab.data_ptr()), 1, vp(tmap.data_ptr()),
+                                        vp(trad.data_ptr()), 1, 4, 8, vp(coords.data_ptr()), vp(types.data_ptr()),
+                                        vp(radii.data_ptr()), None, None, vp(status.data_ptr()), None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1 and float(types.sum()) == 8.0   # four atoms written, four refused
+    with pytest.raises(ValueError):
+        _cabi.check(_cabi.lib().lmg_decode_records(None, None, 1, None, None, 1, 4, 8, None, None, None, None,
+                                                   None, None, None))

@@ -45,6 +45,7 @@ def main():
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--ops", default="forward,forward_binary,backward,relevance,forward_vector,"
                                       "backward_vector,backward_gradients,interpolate,provider")
+    ap.add_argument("--interp-batch", type=int, default=48)
     args = ap.parse_args()
     import torch
     import libmolgrid_b200 as lmg
@@ -147,7 +148,7 @@ def main():
 
     # ---- interpolation --------------------------------------------------------------------------
     if "interpolate" in ops:
-        B = 48
+        B = args.interp_batch
         rng = np.random.default_rng(1005)
         gi = lmg.GridInterpolater(0.5, 23.5, 0.5, 23.5)
         src = torch.rand((B, T, 48, 48, 48), device=dev)
@@ -156,7 +157,7 @@ def main():
         trs = [lmg.Transform(lmg.Quaternion(*[float(v) for v in q[b]]), (0, 0, 0),
                              tuple(float(v) for v in rng.uniform(-2, 2, 3))) for b in range(B)]
         ms = timeit(lambda: gi.forward(src, trs, dst))
-        report("interpolate", "28x48^3 -> 28x48^3, batch 48, random rotation and translation", ms, B,
+        report("interpolate", "28x48^3 -> 28x48^3, batch %d, random rotation and translation" % B, ms, B,
                2 * src.numel() * 4)
 
 

@@ -126,7 +126,7 @@ def test_interpolate_tiled_equals_direct_at_benchmark_shape():
     ts = rng.uniform(-2, 2, (B, 3)).astype(np.float32)
     ts[2] = (40, 0, 0)                                    # mostly outside the input
     trs = [make_transform(qs[b], (0, 0, 0), ts[b]) for b in range(B)]
-    tiled, direct = torch.empty_like(src), torch.empty_like(src)
+    tiled, direct = torch.full_like(src, -2.0), torch.empty_like(src)
     lib = _cabi.lib()
     g.forward(src, trs, tiled)
     try:
@@ -144,3 +144,22 @@ def test_interpolate_tiled_equals_direct_at_benchmark_shape():
     one = torch.empty_like(src[0])
     g.forward(shifted, trs[3], one)
     assert torch.equal(one, tiled[3])
+
+
+@pytest.mark.parametrize("gi", [(0.5, 23.5, 0.6, 21.0), (0.5, 23.5, 0.41, 15.17), (0.5, 15.5, 1.5, 30.0)])
+def test_interpolate_staged_resampling(port, gi):
+    """Coarser and finer output grids than the input (input rows 16-byte aligned: the finer one
+    takes the staged kernel, the coarser ones the direct kernel), against the oracle."""
+    import libmolgrid_b200 as lmg
+    rng = np.random.default_rng(33)
+    g = lmg.GridInterpolater(*gi)
+    din, dout = g.s.in_dim, g.s.out_dim
+    assert din % 4 == 0
+    K = 3
+    grid = rng.uniform(size=(K, din, din, din)).astype(np.float32)
+    q = cases.random_quaternion(rng, 1)[0]
+    c, t = (0.25, -0.5, 0.75), (1.0, -2.0, 0.5)
+    want = port.interpolate(gi, c, grid, port.tr(q, c, t), (0.0, 0.5, 0.0))
+    out = torch.full((K, dout, dout, dout), -3.0, device="cuda")
+    g.forward(c, dev(grid), make_transform(q, c, t), (0.0, 0.5, 0.0), out)
+    assert np.array_equal(out.cpu().numpy(), want)

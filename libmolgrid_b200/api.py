@@ -332,8 +332,16 @@ class GridMaker(object):
     def grid_dimensions(self, ntypes):
         return (int(ntypes),) + self.spatial_grid_dimensions()
 
-    def make_tensor(self, ntypes, batch=None, device=None):
-        """Zero tensor sized for this grid maker (GridMaker.make_tensor, python/torch_bindings.py:32-42)."""
+    def make_tensor(self, center, c):
+        """New torch tensor holding the grid of CoordinateSet ``c`` about ``center``: on the current
+        GPU while ``get_gpu_enabled()``, else on the host (python/torch_bindings.py:32-42)."""
+        dims = self.grid_dimensions(c.max_type)
+        t = torch.zeros(dims, dtype=torch.float32, device=_current_device() if _grids.get_gpu_enabled() else "cpu")
+        self.forward(center, c, t)
+        return t
+
+    def empty_grid(self, ntypes, batch=None, device=None):
+        """Zero tensor of this grid maker's shape for ``ntypes`` channels (optionally batched)."""
         shape = self.grid_dimensions(ntypes)
         if batch is not None:
             shape = (batch,) + shape

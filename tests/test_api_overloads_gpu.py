@@ -198,3 +198,114 @@ def test_gpu_disabled_keeps_results_on_the_host_side():
     dev = molgrid.Grid1fCUDA(torch.arange(4, dtype=torch.float32, device="cuda"))
     alias = molgrid.Grid1fCUDA(molgrid.tofloatptr(dev.data()), 4)
     assert alias[3] == 3.0
+
+
+def test_vector_types_through_coordinate_sets():
+    """test/test_gridmaker.py:217-277: index and one-hot vector types give the same grid, half
+    weights half the density, and the gradients of two atoms towards a target between them are
+    opposite."""
+    g1 = molgrid.GridMaker(resolution=.25, dimension=6.0)
+    c = np.array([[0, 0, 0], [2, 0, 0]], np.float32)
+    t = np.array([0, 1], np.float32)
+    vt = np.array([[1.0, 0], [0, 1.0]], np.float32)
+    vt2 = np.array([[0.5, 0.0], [0.0, 0.5]], np.float32)
+    r = np.array([1.0, 1.0], np.float32)
+    coords = molgrid.CoordinateSet(molgrid.Grid2f(c), molgrid.Grid1f(t), molgrid.Grid1f(r), 2)
+    vcoords = molgrid.CoordinateSet(molgrid.Grid2f(c), molgrid.Grid2f(vt), molgrid.Grid1f(r))
+    v2coords = molgrid.CoordinateSet(molgrid.Grid2f(c), molgrid.Grid2f(vt2), molgrid.Grid1f(r))
+    shape = g1.grid_dimensions(2)
+    reference, vgrid, v2grid, v3grid = (molgrid.MGrid4f(*shape) for _ in range(4))
+    g1.forward((0, 0, 0), coords, reference.cpu())
+    g1.forward((0, 0, 0), vcoords, vgrid.gpu())
+    g1.forward((0, 0, 0), v2coords, v2grid.gpu())
+    g1.forward((0, 0, 0), c, vt, r, v3grid.cpu())
+    g = reference.tonumpy()
+    assert g.sum() > 50
+    np.testing.assert_allclose(g, vgrid.tonumpy(), atol=1e-5)
+    np.testing.assert_allclose(vgrid.tonumpy(), v3grid.tonumpy(), atol=1e-6)
+    np.testing.assert_allclose(g, v2grid.tonumpy() * 2.0, atol=1e-5)
+
+    tc = molgrid.Grid2f(np.array([[1, 0, 0]], np.float32))
+    tv = molgrid.Grid2f(np.array([[0.5, 0.5]], np.float32))
+    tr = molgrid.Grid1f(np.array([1.0], np.float32))
+    tgrid = molgrid.MGrid4f(*shape)
+    g1.forward((0, 0, 0), molgrid.CoordinateSet(tc, tv, tr), tgrid.cpu())
+    gradc, gradt = molgrid.MGrid2f(2, 3), molgrid.MGrid2f(2, 2)
+    g1.backward((0, 0, 0), vcoords, tgrid.gpu(), gradc.gpu(), gradt.gpu())
+    assert gradc[0, 0] == pytest.approx(-gradc[1, 0], abs=1e-4)
+    assert gradc[0, 0] > 0
+
+
+def test_vector_backward_signs():
+    """test/test_gridmaker.py:364-391."""
+    g1 = molgrid.GridMaker(resolution=.1, dimension=6.0)
+    c = np.array([[1.0, 0, 0], [-1, -1, 0]], np.float32)
+    t = np.array([[0, 1.0, 0], [1.0, 0, 0]], np.float32)
+    r = np.array([2.0, 2.0], np.float32)
+    coords = molgrid.CoordinateSet(c, t, r)
+    shape = g1.grid_dimensions(3)
+    diff = molgrid.MGrid4f(*shape)
+    diff[0, 30, 30, 30] = 1.0
+    diff[1, 30, 30, 30] = -1.0
+    atoms, types = molgrid.MGrid2f(2, 3), molgrid.MGrid2f(2, 3)
+    g1.backward((0, 0, 0), coords, diff.gpu(), atoms.gpu(), types.gpu())
+    assert types[0][0] > 0 and types[0][1] < 0 and types[0][2] == 0
+    host_atoms, host_types = molgrid.MGrid2f(2, 3), molgrid.MGrid2f(2, 3)
+    g1.backward((0, 0, 0), coords, diff.cpu(), host_atoms.cpu(), host_types.cpu())
+    np.testing.assert_array_equal(atoms.tonumpy(), host_atoms.tonumpy())
+    np.testing.assert_array_equal(types.tonumpy(), host_types.tonumpy())
+
+
+def test_type_indexed_radii_with_dummy_type():
+    """test/test_gridmaker.py:393-437: make_vector_types(True, radii) adds an empty dummy type and
+    turns the radii into per-type radii."""
+    g1 = molgrid.GridMaker(resolution=.25, dimension=6.0, radius_type_indexed=True)
+    c = np.array([[0, 0, 0]], np.float32)
+    coords = molgrid.CoordinateSet(molgrid.Grid2f(c), molgrid.Grid1f(np.array([0], np.float32)),
+                                   molgrid.Grid1f(np.array([1.0], np.float32)), 2)
+    coords.make_vector_types(True, [3.0, 1.0])
+    shape = g1.grid_dimensions(3)
+    assert g1.get_radii_type_indexed()
+    data = molgrid.MGrid4f(*shape)
+    g1.forward((0, 0, 0), coords, data.gpu())
+    assert data.tonumpy().sum() > 2980          # a radius of 1 would give 116
+    data.fill_zero()
+    data[0, 20, 12, 12] = -1
+    data[1, 20, 12, 12] = 1
+    data[2, 20, 12, 12] = 2
+    atoms, types = molgrid.MGrid2f(1, 3), molgrid.MGrid2f(1, 3)
+    g1.backward((0, 0, 0), coords, data.gpu(), atoms.gpu(), types.gpu())
+    assert atoms[0][0] < 0 and atoms[0][1] == 0 and atoms[0][2] == 0
+    assert types[0][0] < 0 and types[0][1] == 0 and types[0][2] == 0
+
+
+def test_second_derivative_along_each_axis():
+    """test/test_gridmaker.py:439-487: with a truncated Gaussian (gaussian_radius_multiple = -2) the
+    gradient of |d grid point / d coords|^2 is -128 d^3 e^{-4 d^2} + 32 d e^{-4 d^2} along each axis,
+    and symmetric on the diagonal."""
+    gmaker = molgrid.GridMaker(resolution=0.5, dimension=6.0, gaussian_radius_multiple=-2.0)
+    types = torch.ones(1, 1, dtype=torch.float32, device="cuda")
+    radii = torch.ones(1, dtype=torch.float32, device="cuda")
+    for i in range(3):
+        for x in np.arange(-0.9, 3, .3):
+            coords = torch.zeros(1, 3, dtype=torch.float32, device="cuda")
+            coords[0][i] = x
+            coords.requires_grad = True
+            outgrid = molgrid.Coords2GridFunction.apply(gmaker, (0, 0, 0), coords, types, radii)
+            idx = [0, 6, 6, 6]
+            idx[i + 1] = 8
+            gp = outgrid[tuple(idx)]
+            Lg = torch.autograd.grad(gp, coords, create_graph=True)[0]
+            val = float(torch.autograd.grad(torch.sum(Lg ** 2), coords)[0][0][i])
+            d = x - 1
+            assert val == pytest.approx(-128 * d ** 3 * np.exp(-4 * d ** 2) + 32 * d * np.exp(-4 * d ** 2), abs=1e-4)
+    coords = torch.zeros(1, 3, dtype=torch.float32, requires_grad=True, device="cuda")
+    outgrid = molgrid.Coords2GridFunction.apply(gmaker, (0, 0, 0), coords, types, radii)
+    f = []
+    for p in (7, 8):
+        Lg = torch.autograd.grad(outgrid[0][p][p][p], coords, create_graph=True)[0]
+        f.append(torch.autograd.grad(torch.sum(Lg ** 2), coords, retain_graph=True)[0][0])
+    for fl in f:
+        assert float(fl[0]) == pytest.approx(float(fl[1]), rel=1e-5)
+        assert float(fl[2]) == pytest.approx(float(fl[1]), rel=1e-5)
+    assert float(f[1][0]) < float(f[0][0])

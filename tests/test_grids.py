@@ -171,3 +171,9 @@ def test_examplevec_labels():
     one = molgrid.MGrid1f(2)
     ev.extract_label(1, one)
     assert np.array_equal(one.tonumpy(), [2.5, 3.5])
+
+
+def test_reference_module_name():
+    import molgrid as mg
+    assert mg.GridMaker is molgrid.GridMaker and mg.MGrid4f is molgrid.MGrid4f
+    assert mg.Coords2Grid is molgrid.Coords2Grid and mg.ExampleProvider is molgrid.ExampleProvider

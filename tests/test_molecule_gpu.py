@@ -27,7 +27,9 @@ def test_molecule_maxima_and_samples():
     gmaker.forward(center, c, npout)
     gmaker.forward(center, c, torchout)
     gmaker.forward(center, c, cudaout)
-    for got in (mgridgpu.tonumpy(), npout, torchout.numpy(), cudaout.cpu().numpy(),
+    newt = gmaker.make_tensor(center, c)
+    assert newt.is_cuda
+    for got in (mgridgpu.tonumpy(), npout, torchout.numpy(), cudaout.cpu().numpy(), newt.cpu().numpy(),
                 gmaker.make_ndarray(center, c)):
         assert float(got.max()) == pytest.approx(1.438691, abs=2e-6)
     np.testing.assert_allclose(npout.reshape(14, -1).sum(1), MOL["lig_channel_sums"], rtol=1e-5)

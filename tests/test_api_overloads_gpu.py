@@ -309,3 +309,28 @@ def test_second_derivative_along_each_axis():
         assert float(fl[0]) == pytest.approx(float(fl[1]), rel=1e-5)
         assert float(fl[2]) == pytest.approx(float(fl[1]), rel=1e-5)
     assert float(f[1][0]) < float(f[0][0])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_devices():
+    """test/test_gridmaker.py:105-128: a tensor on another device than the current one is refused
+    with ValueError; after set_gpu_device it is accepted, and each device computes the same grid."""
+    gm = molgrid.GridMaker(0.5, 6.0)
+    c, t, r = one_atom()
+    cs = molgrid.CoordinateSet(c, t, r, 1)
+    dims = gm.grid_dimensions(1)
+    out0 = torch.zeros(dims, device="cuda:0")
+    out1 = torch.zeros(dims, device="cuda:1")
+    assert molgrid.get_gpu_device() == 0
+    gm.forward((0, 0, 0), cs, out0)
+    with pytest.raises(ValueError):
+        gm.forward((0, 0, 0), c, t, r, out1)
+    try:
+        molgrid.set_gpu_device(1)
+        assert molgrid.get_gpu_device() == 1
+        gm.forward((0, 0, 0), c, t, r, out1)
+        with pytest.raises(ValueError):
+            gm.forward((0, 0, 0), c, t, r, out0)
+    finally:
+        molgrid.set_gpu_device(0)
+    assert torch.equal(out0.cpu(), out1.cpu()) and float(out0[0, 6, 6, 6]) == pytest.approx(1.0)

@@ -12,6 +12,7 @@ inputs with the shapes of the benchmark configurations:
 * vector types, 28x96^3 @0.25 A, batch 4 x 3000 atoms, Dirichlet(0.3) type vectors, type-indexed radii
   1.7 A x U[0.8,1.2] (forward, backward, backward_gradients) - compute bound: pair evaluations/s are
   reported next to the byte figure;
+* one-hot type vectors with per-atom radii (what the autograd bindings pass), 28x48^3, batch 50;
 * interpolation 28x48^3 -> 28x48^3, batch 48, random rotation + translation;
 * provider: batches of 50 examples (receptor 2000-3900 + ligand 20-60 pre-typed records each, read
   once from .gninatypes files written to a temporary directory) assembled by
@@ -44,7 +45,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--ops", default="forward,forward_binary,backward,relevance,forward_vector,"
-                                      "backward_vector,backward_gradients,interpolate,provider")
+                                      "backward_vector,backward_gradients,onehot_forward,onehot_backward,interpolate,provider")
     ap.add_argument("--interp-batch", type=int, default=48)
     args = ap.parse_args()
     import torch
@@ -145,6 +146,37 @@ def main():
             report("backward_gradients", wl, ms, B, 2 * gb + B * N * (12 + 4 * T) * 3,
                    {"pair_evaluations_per_s": 2 * pairs_fwd / (ms * 1e-3)})
         del grid, diff, dd
+
+    # ---- vector types with per-atom radii (the autograd bindings' layout), 48^3 -------------------
+    if set(ops) & {"onehot_forward", "onehot_backward"}:
+        B = 50
+        coords, types, radii, ns, tr = cases.blob_batch(1001, B, 2000, 4000, T)
+        tv = np.zeros(types.shape + (T,), np.float32)
+        np.put_along_axis(tv, types.astype(np.int64)[..., None], 1.0, axis=2)
+        g = lmg.GridMaker(0.5, 23.5)
+        dc, dtv, dr, dtr, dn = d(coords), d(tv), d(radii), d(tr), d(ns)
+        cen = torch.zeros((B, 3), device=dev)
+        grid = torch.empty((B,) + g.grid_dimensions(T), device=dev)
+        diff = torch.randn(grid.shape, device=dev)
+        ag = torch.empty((B, coords.shape[1], 3), device=dev)
+        tg = torch.empty((B, coords.shape[1], T), device=dev)
+        natoms = float(ns.sum())
+        gb = grid.numel() * 4
+        wl = "one-hot type vectors, per-atom radii, 28x48^3, batch 50 x [2000,4000] atoms"
+        if "onehot_forward" in ops:
+            report("onehot_forward", wl,
+                   timeit(lambda: g.forward(cen, dc, dtv, dr, grid, transforms=dtr, n_atoms=dn)),
+                   B, gb + natoms * (16 + 4 * T))
+        if "onehot_backward" in ops:
+            report("onehot_backward", wl,
+                   timeit(lambda: g.backward(cen, dc, dtv, dr, diff, ag, tg, transforms=dtr, n_atoms=dn)),
+                   B, gb + natoms * (28 + 8 * T))
+        if "onehot_backward" in ops:
+            report("onehot_backward_atoms_only", wl,
+                   timeit(lambda: g.backward_arrays(cen, dc, dtv, dr, diff, ag, transforms=dtr, n_atoms=dn,
+                                                    want_type_gradients=False)),
+                   B, gb + natoms * (28 + 4 * T))
+        del grid, diff
 
     # ---- interpolation --------------------------------------------------------------------------
     if "interpolate" in ops:

@@ -124,6 +124,9 @@ int lmg_forward(const lmg_gridmaker* g, const lmg_atoms* atoms, float* out, void
 int lmg_backward(const lmg_gridmaker* g, const lmg_atoms* atoms, const float* diff,
                  float* atom_gradients, float* type_gradients, void* workspace,
                  size_t workspace_bytes, void* stream);
+/* With vector types, type_gradients may be NULL when only the atom gradients are wanted (types that
+ * are inputs rather than parameters); the reference always computes both.  With per-atom radii the
+ * kernels then read only the channels in which an atom carries weight. */
 
 /* Second-order pass for vector types: from diff and the incoming atom_gradients /
  * type_gradients produce diffdiff[batch][ntypes][D][D][D], atom_diffdiff[batch][max_atoms][3]

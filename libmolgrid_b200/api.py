@@ -604,8 +604,10 @@ class GridMaker(object):
         return self.backward_arrays(*args, **kw)
 
     def backward_arrays(self, center, coords, types, radii, diff, atom_gradients, type_gradients=None,
-                        transforms=None, n_atoms=None):
-        """Atom (and, for vector types, type) gradients from grid gradients ``diff``."""
+                        transforms=None, n_atoms=None, want_type_gradients=True):
+        """Atom (and, for vector types, type) gradients from grid gradients ``diff``.
+        ``want_type_gradients=False`` (vector types only) skips the type gradients, which lets the
+        kernels read just the channels in which an atom carries weight."""
         dev, A, keep, batched, vec, B, N, nr = self._atoms(center, coords, types, radii, transforms, n_atoms)
         df = _Arg(diff, dev, 5 if batched else 4, "diff")
         ag = _Arg(atom_gradients, dev, 3 if batched else 2, "atom_gradients", output=True)
@@ -618,7 +620,10 @@ class GridMaker(object):
             if dshape[i] != d:
                 raise ValueError("diff does not have correct dimension %d: %d vs %d" % (i, dshape[i], d))
         tg = None
-        if vec:
+        if vec and not want_type_gradients:
+            if A.ntypes != T:
+                raise ValueError("Channels in diff doesn't equal number of types")
+        elif vec:
             if type_gradients is None:
                 raise TypeError("vector types need type_gradients")
             tg = _Arg(type_gradients, dev, 3 if batched else 2, "type_gradients", output=True)

@@ -515,8 +515,6 @@ int lmg_backward(const lmg_gridmaker* g, const lmg_atoms* a, const float* diff, 
   int vec = a->type_vector != nullptr;
   if (diff == nullptr || atom_gradients == nullptr)
     return fail(LMG_ERR_INVALID_ARGUMENT, "diff/atom_gradients missing memory");
-  if (vec && type_gradients == nullptr)
-    return fail(LMG_ERR_INVALID_ARGUMENT, "type_gradients missing memory");
   if (!vec && type_gradients != nullptr)
     return fail(LMG_ERR_INVALID_ARGUMENT, "type_gradients given with index types");
   return backward_common(g, a, LMG_OP_BACKWARD, vec ? 1 : 0, diff, nullptr, atom_gradients,

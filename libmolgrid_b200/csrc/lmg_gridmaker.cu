@@ -1031,7 +1031,7 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_warp(BwdArgs G) {
       G.partial[pi * 3] = agx;
       G.partial[pi * 3 + 1] = agy;
       G.partial[pi * 3 + 2] = agz;
-      if (MODE == 1) G.type_gradients[ai * G.T + P.chan] = tg;
+      if (MODE == 1 && G.type_gradients != nullptr) G.type_gradients[ai * G.T + P.chan] = tg;
     } else {
       G.relevance[ai] = tg;
     }
@@ -1477,7 +1477,7 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads(BwdArgs G) {
       G.partial[pi * 3] = agx;
       G.partial[pi * 3 + 1] = agy;
       G.partial[pi * 3 + 2] = agz;
-      if (MODE == 1) G.type_gradients[ai * G.T + P.chan] = tg;
+      if (MODE == 1 && G.type_gradients != nullptr) G.type_gradients[ai * G.T + P.chan] = tg;
     } else {
       G.relevance[ai] = tg;
     }
@@ -1557,6 +1557,367 @@ __global__ void __launch_bounds__(SCAT_WARPS * 32) k_gradgrad_quads(BwdArgs G) {
       }
     }
     __syncwarp();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Vector types with per-atom radii (the layout of the autograd bindings): the footprint and the
+// density of an atom are the same for every channel, so one warp owns the ATOM, evaluates each voxel
+// once and loops over the channels inside - the reuse the reference's kernel makes too
+// (src/grid_maker.cu:322-325).  With one-hot type vectors this is the index-typed cost instead of
+// one work item per (atom, channel).  Channels are handled in rounds of VA_CH.
+// ---------------------------------------------------------------------------------------------
+constexpr int VA_CH = 32;  // channels per round
+
+template <bool BINARY, bool PRECISE>
+__global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads_atom(BwdArgs G) {
+  __shared__ ColBuf bufs[SCAT_WARPS];
+  __shared__ ZTabs ztabs[SCAT_WARPS];
+  __shared__ int nz_t[SCAT_WARPS][VA_CH];
+  __shared__ float nz_w[SCAT_WARPS][VA_CH];
+  const GMParams& gm = G.gm;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int item = blockIdx.x * SCAT_WARPS + wid;
+  int bl = blockIdx.y;
+  int b = G.b0 + bl;
+  if (item >= G.N) return;
+  ColBuf& buf = bufs[wid];
+  ZTabs& zt = ztabs[wid];
+
+  float cx, cy, cz;
+  if (G.centers != nullptr) {
+    cx = G.centers[b * 3]; cy = G.centers[b * 3 + 1]; cz = G.centers[b * 3 + 2];
+  } else {
+    cx = G.center_host[0]; cy = G.center_host[1]; cz = G.center_host[2];
+  }
+  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
+  ItemParams P = load_item<false>(G, bl, b, item, ox, oy, oz);
+  if (!P.valid) return;
+
+  size_t dim = gm.dim;
+  const size_t chan_stride = dim * dim * dim;
+  float* outb = G.out_grid + (size_t)b * G.T * chan_stride;
+  const float* wrow = G.type_vector + ((size_t)b * G.N + item) * G.T;
+  const float Tcull = BINARY ? P.Tbin : P.Tcut;
+  const float kexp = P.inv_ar2 * NEG2_LOG2E;
+  const float ta = gm.ta, ntb = -gm.tb;
+
+  unsigned nx = P.hix - P.lox, ny = P.hiy - P.loy;
+  unsigned ncols = nx * ny;
+  float inv_ny = 1.f / (float)ny;
+  for (int tb = 0; tb < G.T; tb += VA_CH) {
+    // channels of this round that carry weight (zero weights add nothing, src/grid_maker.cpp:229)
+    int t = tb + lane;
+    float w = t < G.T ? wrow[t] : 0.f;
+    unsigned m = __ballot_sync(0xffffffffu, w != 0.f);
+    int nnz = __popc(m);
+    if (nnz == 0) continue;
+    __syncwarp();
+    if (w != 0.f) {
+      int slot = __popc(m & ((1u << lane) - 1u));
+      nz_t[wid][slot] = t;
+      nz_w[wid][slot] = w;
+    }
+    __syncwarp();
+    for (unsigned cbase = 0; cbase < ncols;) {
+      unsigned nkept = compact_columns<ColBuf, false>(buf, P, cbase, ncols, ny, inv_ny, Tcull, ox, oy,
+                                                      gm.res, gm.dim, lane);
+      for (unsigned zc = P.loz & ~3u; zc < P.hiz; zc += 4 * QPASS) {
+        __syncwarp();
+        fill_ztabs(zt, zc, P, oz, gm.res, kexp, lane);
+        __syncwarp();
+        unsigned nq = min((unsigned)QPASS, (P.hiz - zc + 3) >> 2);
+        for (unsigned c0 = 0; c0 < nkept; c0 += 32) {
+          unsigned i = c0 + lane;
+          bool have = i < nkept;
+          float dxy2 = have ? buf.dxy2[i] : CUDART_NAN_F;
+          float* row = outb + (size_t)(have ? buf.row[i] : 0u) * dim + zc;
+          float exy = ex2_approx(dxy2 * kexp);
+          for (unsigned q = 0; q < nq; q++) {
+            float4 d2 = zt.dz2[q], e = zt.ez[q];
+            float d2v[4] = {d2.x, d2.y, d2.z, d2.w}, ev[4] = {e.x, e.y, e.z, e.w}, v[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              float rsq = __fadd_rn(dxy2, d2v[j]);
+              if (BINARY) {
+                v[j] = rsq < P.Tbin ? 1.f : 0.f;
+              } else if (PRECISE) {
+                v[j] = density_precise(rsq, P.ar, P.Tg, P.Tcut, gm.A, gm.B, gm.C);
+              } else {
+                float tq = fminf(fmaf(ta, sqrt_approx(rsq * P.inv_ar2), ntb), 0.f);
+                v[j] = rsq <= P.Tg ? exy * ev[j] : tq * tq;
+              }
+            }
+            unsigned any = __float_as_uint(v[0]) | __float_as_uint(v[1]) | __float_as_uint(v[2]) |
+                           __float_as_uint(v[3]);
+            if (any != 0u) {
+              for (int k = 0; k < nnz; k++) {
+                float wk = nz_w[wid][k];
+                red_add_v4(row + (size_t)nz_t[wid][k] * chan_stride + 4 * q, v[0] * wk, v[1] * wk, v[2] * wk,
+                           v[3] * wk);
+              }
+            }
+          }
+        }
+      }
+      __syncwarp();
+    }
+  }
+}
+
+// Backward for the same layout: atom gradient = sum over voxels of s * delta * (sum_t w_t diff_t),
+// type gradient of EVERY channel = sum over voxels of density * diff_t (src/grid_maker.cpp:508-517).
+// A lane keeps the type gradients of a round's channels in registers; rounds of VA_BCH channels.
+#ifndef LMG_VA_BCH
+#define LMG_VA_BCH 16
+#endif
+constexpr int VA_BCH = LMG_VA_BCH;
+
+template <bool BINARY>
+__global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads_atom(BwdArgs G) {
+  __shared__ ColBufD bufs[BWD2_WARPS];
+  __shared__ ZTabs ztabs[BWD2_WARPS];
+  const GMParams& gm = G.gm;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int item = blockIdx.x * BWD2_WARPS + wid;
+  int bl = blockIdx.y;
+  int b = G.b0 + bl;
+  if (item >= G.N) return;
+  ColBufD& buf = bufs[wid];
+  ZTabs& zt = ztabs[wid];
+
+  float cx, cy, cz;
+  if (G.centers != nullptr) {
+    cx = G.centers[b * 3]; cy = G.centers[b * 3 + 1]; cz = G.centers[b * 3 + 2];
+  } else {
+    cx = G.center_host[0]; cy = G.center_host[1]; cz = G.center_host[2];
+  }
+  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
+  ItemParams P = load_item<false>(G, bl, b, item, ox, oy, oz);
+
+  size_t dim = gm.dim;
+  const size_t chan_stride = dim * dim * dim;
+  const float* diffb = G.diff + (size_t)b * G.T * chan_stride;
+  const size_t ai = (size_t)b * G.N + item;
+  const float* wrow = G.type_vector + ai * G.T;
+  const float Tcull = fmaxf(P.Tcut, BINARY ? P.Tbin : -1.f);
+  const float kexp = P.inv_ar2 * NEG2_LOG2E;
+  const float k4 = 4.f * P.inv_ar2, kD = -gm.D * P.inv_ar2, kE = -gm.E * P.inv_ar;
+  const float ta = gm.ta, ntb = -gm.tb;
+  float agx = 0.f, agy = 0.f, agz = 0.f;
+
+  for (int tb = 0; tb < G.T; tb += VA_BCH) {
+    const int nch = min(VA_BCH, G.T - tb);
+    float wch[VA_BCH], tgacc[VA_BCH];
+#pragma unroll
+    for (int c = 0; c < VA_BCH; c++) {
+      wch[c] = c < nch ? wrow[tb + c] : 0.f;
+      tgacc[c] = 0.f;
+    }
+    if (P.valid) {
+      unsigned nx = P.hix - P.lox, ny = P.hiy - P.loy;
+      unsigned ncols = nx * ny;
+      float inv_ny = 1.f / (float)ny;
+      for (unsigned cbase = 0; cbase < ncols;) {
+        unsigned nkept = compact_columns<ColBufD, true>(buf, P, cbase, ncols, ny, inv_ny, Tcull, ox, oy,
+                                                        gm.res, gm.dim, lane);
+        for (unsigned zc = P.loz & ~3u; zc < P.hiz; zc += 4 * QPASS) {
+          __syncwarp();
+          fill_ztabs(zt, zc, P, oz, gm.res, kexp, lane);
+          __syncwarp();
+          unsigned nq = min((unsigned)QPASS, (P.hiz - zc + 3) >> 2);
+          for (unsigned c0 = 0; c0 < nkept; c0 += 32) {
+            unsigned i = c0 + lane;
+            bool have = i < nkept;
+            float dxy2 = have ? buf.dxy2[i] : CUDART_NAN_F;
+            float dx = have ? buf.dx[i] : 0.f, dy = have ? buf.dy[i] : 0.f;
+            const float* row = diffb + (size_t)(have ? buf.row[i] : 0u) * dim + zc;
+            float exy = ex2_approx(dxy2 * kexp);
+            float fsum = 0.f;
+            for (unsigned q = 0; q < nq; q++) {
+              float4 d2 = zt.dz2[q], e = zt.ez[q], dz = zt.dz[q];
+              float lo = fminf(fminf(d2.x, d2.y), fminf(d2.z, d2.w));  // fminf skips the NaN entries
+              if (!(__fadd_rn(dxy2, lo) <= Tcull)) continue;            // no voxel of this lane's quad
+              float d2v[4] = {d2.x, d2.y, d2.z, d2.w}, ev[4] = {e.x, e.y, e.z, e.w};
+              float dzv[4] = {dz.x, dz.y, dz.z, dz.w};
+              float v[4], sg[4], dsum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                float rsq = __fadd_rn(dxy2, d2v[j]);
+                float g = exy * ev[j];
+                float s1 = rsq <= P.Tg ? k4 * g : fmaf(kE, rsqrt_approx(rsq), kD);
+                sg[j] = rsq <= P.Tcut ? s1 : 0.f;
+                if (BINARY) {
+                  v[j] = rsq < P.Tbin ? 1.f : 0.f;
+                } else {
+                  float tq = fminf(fmaf(ta, sqrt_approx(rsq * P.inv_ar2), ntb), 0.f);
+                  float val = rsq <= P.Tg ? g : tq * tq;
+                  v[j] = rsq <= P.Tcut ? val : 0.f;
+                }
+              }
+              const float4* qp = reinterpret_cast<const float4*>(row) + q;
+#pragma unroll
+              for (int c4 = 0; c4 < VA_BCH; c4 += 4) {
+                // four channels requested together, then used
+                float4 dv[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                  dv[u] = (c4 + u < nch) ? __ldg(qp + (size_t)(tb + c4 + u) * (chan_stride / 4))
+                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                  float wk = wch[c4 + u];
+                  tgacc[c4 + u] = fmaf(v[0], dv[u].x, fmaf(v[1], dv[u].y, fmaf(v[2], dv[u].z,
+                                       fmaf(v[3], dv[u].w, tgacc[c4 + u]))));
+                  dsum[0] = fmaf(wk, dv[u].x, dsum[0]);
+                  dsum[1] = fmaf(wk, dv[u].y, dsum[1]);
+                  dsum[2] = fmaf(wk, dv[u].z, dsum[2]);
+                  dsum[3] = fmaf(wk, dv[u].w, dsum[3]);
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                float f = sg[j] * dsum[j];
+                fsum += f;
+                agz = fmaf(f, dzv[j], agz);
+              }
+            }
+            agx = fmaf(fsum, dx, agx);
+            agy = fmaf(fsum, dy, agy);
+          }
+        }
+        __syncwarp();
+      }
+    }
+    // type gradients of this round
+#pragma unroll
+    for (int c = 0; c < VA_BCH; c++) {
+      float x = tgacc[c];
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+      if (lane == 0 && c < nch) G.type_gradients[ai * G.T + tb + c] = x;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) {
+    agx += __shfl_xor_sync(0xffffffffu, agx, o);
+    agy += __shfl_xor_sync(0xffffffffu, agy, o);
+    agz += __shfl_xor_sync(0xffffffffu, agz, o);
+  }
+  if (lane == 0) {
+    G.atom_gradients[ai * 3] = agx;
+    G.atom_gradients[ai * 3 + 1] = agy;
+    G.atom_gradients[ai * 3 + 2] = agz;
+  }
+}
+
+// The same without type gradients (the caller passed none: types that are inputs, not parameters):
+// only the channels that carry weight are read.
+__global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads_atom_ag(BwdArgs G) {
+  __shared__ ColBufD bufs[BWD2_WARPS];
+  __shared__ ZTabs ztabs[BWD2_WARPS];
+  __shared__ int nz_t[BWD2_WARPS][VA_CH];
+  __shared__ float nz_w[BWD2_WARPS][VA_CH];
+  const GMParams& gm = G.gm;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int item = blockIdx.x * BWD2_WARPS + wid;
+  int bl = blockIdx.y;
+  int b = G.b0 + bl;
+  if (item >= G.N) return;
+  ColBufD& buf = bufs[wid];
+  ZTabs& zt = ztabs[wid];
+
+  float cx, cy, cz;
+  if (G.centers != nullptr) {
+    cx = G.centers[b * 3]; cy = G.centers[b * 3 + 1]; cz = G.centers[b * 3 + 2];
+  } else {
+    cx = G.center_host[0]; cy = G.center_host[1]; cz = G.center_host[2];
+  }
+  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
+  ItemParams P = load_item<false>(G, bl, b, item, ox, oy, oz);
+
+  size_t dim = gm.dim;
+  const size_t chan_stride = dim * dim * dim;
+  const float* diffb = G.diff + (size_t)b * G.T * chan_stride;
+  const size_t ai = (size_t)b * G.N + item;
+  const float* wrow = G.type_vector + ai * G.T;
+  const float kexp = P.inv_ar2 * NEG2_LOG2E;
+  const float k4 = 4.f * P.inv_ar2, kD = -gm.D * P.inv_ar2, kE = -gm.E * P.inv_ar;
+  float agx = 0.f, agy = 0.f, agz = 0.f;
+
+  for (int tb = 0; P.valid && tb < G.T; tb += VA_CH) {
+    int t = tb + lane;
+    float w = t < G.T ? wrow[t] : 0.f;
+    unsigned m = __ballot_sync(0xffffffffu, w != 0.f);
+    int nnz = __popc(m);
+    if (nnz == 0) continue;
+    __syncwarp();
+    if (w != 0.f) {
+      int slot = __popc(m & ((1u << lane) - 1u));
+      nz_t[wid][slot] = t;
+      nz_w[wid][slot] = w;
+    }
+    __syncwarp();
+    unsigned nx = P.hix - P.lox, ny = P.hiy - P.loy;
+    unsigned ncols = nx * ny;
+    float inv_ny = 1.f / (float)ny;
+    for (unsigned cbase = 0; cbase < ncols;) {
+      unsigned nkept = compact_columns<ColBufD, true>(buf, P, cbase, ncols, ny, inv_ny, P.Tcut, ox, oy,
+                                                      gm.res, gm.dim, lane);
+      for (unsigned zc = P.loz & ~3u; zc < P.hiz; zc += 4 * QPASS) {
+        __syncwarp();
+        fill_ztabs(zt, zc, P, oz, gm.res, kexp, lane);
+        __syncwarp();
+        unsigned nq = min((unsigned)QPASS, (P.hiz - zc + 3) >> 2);
+        for (unsigned c0 = 0; c0 < nkept; c0 += 32) {
+          unsigned i = c0 + lane;
+          bool have = i < nkept;
+          float dxy2 = have ? buf.dxy2[i] : CUDART_NAN_F;
+          float dx = have ? buf.dx[i] : 0.f, dy = have ? buf.dy[i] : 0.f;
+          const float4* row = reinterpret_cast<const float4*>(diffb + (size_t)(have ? buf.row[i] : 0u) * dim + zc);
+          float exy4 = k4 * ex2_approx(dxy2 * kexp);
+          float fsum = 0.f;
+          for (unsigned q = 0; q < nq; q++) {
+            float4 d2 = zt.dz2[q], e = zt.ez[q], dz = zt.dz[q];
+            float lo = fminf(fminf(d2.x, d2.y), fminf(d2.z, d2.w));  // fminf skips the NaN entries
+            bool live = __fadd_rn(dxy2, lo) <= P.Tcut;
+            float4 ds = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < nnz; k++) {
+              if (live) {
+                float wk = nz_w[wid][k];
+                float4 dv = __ldg(row + q + (size_t)nz_t[wid][k] * (chan_stride / 4));
+                ds.x = fmaf(wk, dv.x, ds.x); ds.y = fmaf(wk, dv.y, ds.y);
+                ds.z = fmaf(wk, dv.z, ds.z); ds.w = fmaf(wk, dv.w, ds.w);
+              }
+            }
+            float d2v[4] = {d2.x, d2.y, d2.z, d2.w}, ev[4] = {e.x, e.y, e.z, e.w};
+            float dzv[4] = {dz.x, dz.y, dz.z, dz.w}, dsv[4] = {ds.x, ds.y, ds.z, ds.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              float rsq = __fadd_rn(dxy2, d2v[j]);
+              float sg = rsq <= P.Tg ? exy4 * ev[j] : fmaf(kE, rsqrt_approx(rsq), kD);
+              float f = rsq <= P.Tcut ? sg * dsv[j] : 0.f;
+              fsum += f;
+              agz = fmaf(f, dzv[j], agz);
+            }
+          }
+          agx = fmaf(fsum, dx, agx);
+          agy = fmaf(fsum, dy, agy);
+        }
+      }
+      __syncwarp();
+    }
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) {
+    agx += __shfl_xor_sync(0xffffffffu, agx, o);
+    agy += __shfl_xor_sync(0xffffffffu, agy, o);
+    agz += __shfl_xor_sync(0xffffffffu, agz, o);
+  }
+  if (lane == 0) {
+    G.atom_gradients[ai * 3] = agx;
+    G.atom_gradients[ai * 3 + 1] = agy;
+    G.atom_gradients[ai * 3 + 2] = agz;
   }
 }
 
@@ -1645,6 +2006,12 @@ cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st) {
   if (mode == 0) {
     if (quads) k_backward_quads<0, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
     else k_backward_warp<0, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+  } else if (mode == 1 && quads && !G.gm.rti) {
+    // per-atom radii: one work item per atom writes both gradients, no reduction over channels after it
+    dim3 ga((unsigned)((G.N + BWD2_WARPS - 1) / BWD2_WARPS), G.nb);
+    if (G.type_gradients == nullptr) k_backward_quads_atom_ag<<<ga, BWD2_WARPS * 32, 0, st>>>(G);
+    else if (bin) k_backward_quads_atom<true><<<ga, BWD2_WARPS * 32, 0, st>>>(G);
+    else k_backward_quads_atom<false><<<ga, BWD2_WARPS * 32, 0, st>>>(G);
   } else if (mode == 1) {
     if (quads && bin) k_backward_quads<1, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
     else if (quads) k_backward_quads<1, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
@@ -1682,6 +2049,15 @@ cudaError_t launch_forward_scatter(const BwdArgs& G, bool vec, cudaStream_t st) 
   if (items == 0 || G.nb == 0) return cudaSuccess;
   dim3 grid((unsigned)((items + SCAT_WARPS - 1) / SCAT_WARPS), G.nb);
   bool bin = G.gm.binary != 0;
+  bool aligned = G.quads && G.gm.dim % 4 == 0 && (uintptr_t)G.out_grid % 16 == 0;
+  if (vec && !G.gm.rti && aligned) {
+    // per-atom radii: one work item per atom, channels inside
+    dim3 ga((unsigned)((G.N + SCAT_WARPS - 1) / SCAT_WARPS), G.nb);
+    if (bin) k_forward_quads_atom<true, false><<<ga, SCAT_WARPS * 32, 0, st>>>(G);
+    else if (G.precise) k_forward_quads_atom<false, true><<<ga, SCAT_WARPS * 32, 0, st>>>(G);
+    else k_forward_quads_atom<false, false><<<ga, SCAT_WARPS * 32, 0, st>>>(G);
+    return cudaGetLastError();
+  }
   if (G.quads && !bin && !G.precise && G.gm.dim % 4 == 0 && (uintptr_t)G.out_grid % 16 == 0) {
     if (vec) k_forward_quads<true><<<grid, SCAT_WARPS * 32, 0, st>>>(G);
     else k_forward_quads<false><<<grid, SCAT_WARPS * 32, 0, st>>>(G);

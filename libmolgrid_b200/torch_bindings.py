@@ -58,6 +58,13 @@ class Coords2GridFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grid_gradient):
         coords, types, radii = ctx.saved_tensors
+        if not ctx.needs_input_grad[3] and not torch.is_grad_enabled():
+            # types are inputs, not parameters, and no second derivative is being recorded: only the
+            # channels in which an atom carries weight need to be read
+            grad_coords = torch.empty_like(coords)
+            ctx.gmaker.backward_arrays(ctx.center, coords, types, radii, grid_gradient.contiguous(), grad_coords,
+                                       want_type_gradients=False)
+            return None, None, grad_coords, None, None
         grad_coords, grad_types = Grid2CoordsGradientFunction.apply(ctx.gmaker, ctx.center, coords, types, radii,
                                                                     grid_gradient)
         return None, None, grad_coords, grad_types, None

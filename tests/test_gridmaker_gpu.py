@@ -341,3 +341,25 @@ def test_backward_gradients(port, kw, rti):
         grad_close(dd[b].cpu().numpy(), wdd, "diffdiff")
         grad_close(add[b].cpu().numpy(), wadd, "atom_diffdiff")
     assert not tdd.any()
+
+
+@pytest.mark.parametrize("rti", [False, True])
+@pytest.mark.parametrize("kw", [dict(resolution=0.5, dimension=11.5), dict(resolution=0.5, dimension=11.0)])
+def test_backward_vector_without_type_gradients(port, kw, rti):
+    """Vector types, atom gradients only: same atom gradients as the full call, on the per-atom
+    kernels (per-atom radii, rows 16-byte aligned) and on the per-(atom, channel) kernels."""
+    g, og = gm_pair(port, radius_type_indexed=rti, **kw)
+    T, N = 6, 50
+    coords, tv, radii = cases.vector_case(5, N, T, kw["dimension"] / 2 + 1, rti=rti)
+    tv[:10] = 0
+    tv[np.arange(10), np.arange(10) % T] = 1.0      # some one-hot atoms
+    dims = g.grid_dimensions(T)
+    diff = np.random.default_rng(6).normal(size=dims).astype(np.float32)
+    ag, tg = torch.zeros((N, 3), device="cuda"), torch.zeros((N, T), device="cuda")
+    g.backward((0, 0, 0), dev(coords), dev(tv), dev(radii), dev(diff), ag, tg)
+    only = torch.full((N, 3), 9.0, device="cuda")
+    g.backward_arrays((0, 0, 0), dev(coords), dev(tv), dev(radii), dev(diff), only, want_type_gradients=False)
+    wag, wtg = port.backward_vector(og, (0, 0, 0), coords, tv, radii, diff)
+    grad_close(ag.cpu().numpy(), wag, "atom gradients")
+    grad_close(tg.cpu().numpy(), wtg, "type gradients")
+    grad_close(only.cpu().numpy(), wag, "atom gradients alone")

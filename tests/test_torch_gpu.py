@@ -80,3 +80,26 @@ def test_bad_ranks():
     c2g = lmg.Coords2Grid(lmg.GridMaker(0.5, 5.5))
     with pytest.raises(RuntimeError):
         c2g(torch.zeros(2, 4, 3, device="cuda"), torch.zeros(4, 2, device="cuda"), torch.ones(4, device="cuda"))
+
+
+def test_backward_skips_type_gradients_when_types_are_inputs(port):
+    """Coordinates' gradients are the same whether or not the types ask for gradients."""
+    import libmolgrid_b200 as lmg
+    rng = np.random.default_rng(8)
+    N, T = 40, 5
+    coords = torch.tensor(rng.uniform(-4, 4, (N, 3)).astype(np.float32), device="cuda")
+    types = torch.zeros((N, T), device="cuda")
+    types[torch.arange(N), torch.arange(N) % T] = 1.0
+    radii = torch.full((N,), 1.5, device="cuda")
+    gm = lmg.GridMaker(0.5, 11.5)
+    weight = torch.randn(gm.grid_dimensions(T), device="cuda")
+    grads = []
+    for types_need_grad in (False, True):
+        c = coords.clone().requires_grad_(True)
+        t = types.clone().requires_grad_(types_need_grad)
+        out = lmg.Coords2GridFunction.apply(gm, (0, 0, 0), c, t, radii)
+        (out * weight).sum().backward()
+        grads.append(c.grad.clone())
+        assert (t.grad is not None) == types_need_grad
+    assert float(grads[1].abs().max()) > 0.1
+    torch.testing.assert_close(grads[0], grads[1], rtol=1e-4, atol=1e-5)

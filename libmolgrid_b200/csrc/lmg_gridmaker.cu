@@ -1668,10 +1668,7 @@ __global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads_atom(BwdArgs 
 // Backward for the same layout: atom gradient = sum over voxels of s * delta * (sum_t w_t diff_t),
 // type gradient of EVERY channel = sum over voxels of density * diff_t (src/grid_maker.cpp:508-517).
 // A lane keeps the type gradients of a round's channels in registers; rounds of VA_BCH channels.
-#ifndef LMG_VA_BCH
-#define LMG_VA_BCH 16
-#endif
-constexpr int VA_BCH = LMG_VA_BCH;
+constexpr int VA_BCH = 16;
 
 template <bool BINARY>
 __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads_atom(BwdArgs G) {

@@ -878,6 +878,11 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_warp(BwdArgs G) {
   int bl = blockIdx.y;
   int b = G.b0 + bl;
   if (item >= items_per_ex) return;
+  if (MODE == 3) {
+    // an (atom, channel) pair without weight contributes nothing: leave before any other load
+    int ea = item / G.T;
+    if (G.type_vector[((size_t)b * G.N + ea) * G.T + (item - ea * G.T)] == 0.f) return;
+  }
   ColBufD& buf = bufs[wid];
 
   float cx, cy, cz;
@@ -1055,6 +1060,11 @@ __global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_scatter(BwdArgs G) 
   int bl = blockIdx.y;
   int b = G.b0 + bl;
   if (item >= items_per_ex) return;
+  if (VEC) {
+    // an (atom, channel) pair without weight contributes nothing: leave before any other load
+    int ea = item / G.T;
+    if (G.type_vector[((size_t)b * G.N + ea) * G.T + (item - ea * G.T)] == 0.f) return;
+  }
   ColBuf& buf = bufs[wid];
 
   float cx, cy, cz;
@@ -1134,6 +1144,11 @@ __global__ void __launch_bounds__(SCAT_WARPS * 32) k_gradgrad_scatter(BwdArgs G)
   int bl = blockIdx.y;
   int b = G.b0 + bl;
   if (item >= G.N * G.T) return;
+  if (true) {
+    // an (atom, channel) pair without weight contributes nothing: leave before any other load
+    int ea = item / G.T;
+    if (G.type_vector[((size_t)b * G.N + ea) * G.T + (item - ea * G.T)] == 0.f) return;
+  }
   ColBufD& buf = bufs[wid];
 
   float cx, cy, cz;
@@ -1242,6 +1257,11 @@ __global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads(BwdArgs G) {
   int bl = blockIdx.y;
   int b = G.b0 + bl;
   if (item >= items_per_ex) return;
+  if (VEC) {
+    // an (atom, channel) pair without weight contributes nothing: leave before any other load
+    int ea = item / G.T;
+    if (G.type_vector[((size_t)b * G.N + ea) * G.T + (item - ea * G.T)] == 0.f) return;
+  }
   ColBuf& buf = bufs[wid];
   ZTabs& zt = ztabs[wid];
 
@@ -1311,6 +1331,11 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads(BwdArgs G) {
   int bl = blockIdx.y;
   int b = G.b0 + bl;
   if (item >= items_per_ex) return;
+  if (MODE == 3) {
+    // an (atom, channel) pair without weight contributes nothing: leave before any other load
+    int ea = item / G.T;
+    if (G.type_vector[((size_t)b * G.N + ea) * G.T + (item - ea * G.T)] == 0.f) return;
+  }
   ColBufD& buf = bufs[wid];
   ZTabs& zt = ztabs[wid];
 
@@ -1494,6 +1519,11 @@ __global__ void __launch_bounds__(SCAT_WARPS * 32) k_gradgrad_quads(BwdArgs G) {
   int bl = blockIdx.y;
   int b = G.b0 + bl;
   if (item >= G.N * G.T) return;
+  if (true) {
+    // an (atom, channel) pair without weight contributes nothing: leave before any other load
+    int ea = item / G.T;
+    if (G.type_vector[((size_t)b * G.N + ea) * G.T + (item - ea * G.T)] == 0.f) return;
+  }
   ColBufD& buf = bufs[wid];
   ZTabs& zt = ztabs[wid];
 

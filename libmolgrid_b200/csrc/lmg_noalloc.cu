@@ -150,6 +150,7 @@ int lmg_backward_static(const lmg_gridmaker* g, const lmg_atoms* a, const float*
   B.recs = E.recs;
   B.diff = diff;
   B.atom_gradients = atom_gradients;
+  B.quads = 1;  // the aligned-quad kernel where the grid allows it (the launcher checks)
   e = lmg::launch_backward(B, 0, st);
   if (e != cudaSuccess) return fail(LMG_ERR_CUDA, std::string("CUDA Error: backward: ") + cudaGetErrorString(e));
   return LMG_OK;

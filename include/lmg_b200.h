@@ -193,6 +193,14 @@ int lmg_interpolate(const lmg_interpolater* gi, int batch, int nchannels, const 
                     const lmg_transform* transforms, const float* in_centers,
                     const float* out_centers, float* out, void* stream);
 
+/* Adjoint of lmg_interpolate: grad_in[batch][nchannels][Din]^3 (fully overwritten) from
+ * grad_out[batch][nchannels][Dout]^3 with the same transforms and centres.  The reference has no
+ * backward pass for GridInterpolater ("TODO: backwards", include/libmolgrid/grid_interpolater.h:179);
+ * this is the transpose of the forward pass's trilinear weights. */
+int lmg_interpolate_backward(const lmg_interpolater* gi, int batch, int nchannels, const float* grad_out,
+                             const lmg_transform* transforms, const float* in_centers,
+                             const float* out_centers, float* grad_in, void* stream);
+
 /* ---- batch assembly from pre-typed atom records --------------------------------------------
  * A record is the 16-byte {float x, y, z; int type} of the reference's .gninatypes / .molcache2 files
  * (src/coord_cache.cpp:82-148).  One call turns the records of a whole batch into the padded batch

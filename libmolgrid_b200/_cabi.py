@@ -81,6 +81,8 @@ SYMBOLS = [
                                              ctypes.c_float]),
     ("lmg_interpolate", ctypes.c_int, [_GI, ctypes.c_int, ctypes.c_int, _VP, _TR, c_float_p, c_float_p,
                                        _VP, _VP]),
+    ("lmg_interpolate_backward", ctypes.c_int, [_GI, ctypes.c_int, ctypes.c_int, _VP, _TR, c_float_p, c_float_p,
+                                                _VP, _VP]),
     ("lmg_decode_records", ctypes.c_int, [_VP, _VP, ctypes.c_int, _VP, _VP, ctypes.c_int, ctypes.c_int,
                                           ctypes.c_int, _VP, _VP, _VP, _VP, _VP, _VP, _VP]),
     ("lmg_check_status", ctypes.c_int, [_VP, _VP]),

@@ -762,6 +762,16 @@ class GridInterpolater(object):
         ``in``/``out`` are (K,D,D,D) grids with one Transform, or batched (B,K,D,D,D) grids with a
         list of B Transforms (and (B,3) centres in the five-argument form).
         """
+        self._run(args, backward=False)
+
+    def backward(self, *args):
+        """backward(grad_out, transform, grad_in) or backward(in_center, grad_out, transform, out_center,
+        grad_in): the gradient with respect to the forward pass's input from the gradient with respect
+        to its output, for the same transform(s) and centres.  Not in the reference, which leaves the
+        backward pass open (include/libmolgrid/grid_interpolater.h:179)."""
+        self._run(args, backward=True)
+
+    def _run(self, args, backward):
         if len(args) == 3:
             inp, transform, out = args
             in_center = out_center = None
@@ -781,6 +791,8 @@ class GridInterpolater(object):
             raise ValueError("need one transform per example")
         ish = tuple(i.t.shape[1:] if batched else i.t.shape)
         osh = tuple(o.t.shape[1:] if batched else o.t.shape)
+        if backward:
+            ish, osh = osh, ish   # the first grid is the output's gradient, the last the input's
         # GridInterpolater::checkGrids, src/grid_interpolater.cpp:55-76
         if i.t.data_ptr() == o.t.data_ptr():
             raise ValueError("Input and output grid can not be the same in GridInterpolator.")
@@ -807,6 +819,6 @@ class GridInterpolater(object):
             return arr
 
         ic, oc = centers(in_center), centers(out_center)
-        check(_cabi.lib().lmg_interpolate(ctypes.byref(self.s), B, int(ish[0]), i.ptr, T, ic, oc, o.ptr,
-                                          _stream_ptr(dev)))
+        fn = _cabi.lib().lmg_interpolate_backward if backward else _cabi.lib().lmg_interpolate
+        check(fn(ctypes.byref(self.s), B, int(ish[0]), i.ptr, T, ic, oc, o.ptr, _stream_ptr(dev)))
         o.finish()

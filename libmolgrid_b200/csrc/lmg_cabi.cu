@@ -713,4 +713,45 @@ int lmg_interpolate(const lmg_interpolater* gi, int batch, int nchannels, const 
   return LMG_OK;
 }
 
+int lmg_interpolate_backward(const lmg_interpolater* gi, int batch, int nchannels, const float* grad_out,
+                             const lmg_transform* transforms, const float* in_centers,
+                             const float* out_centers, float* grad_in, void* stream) {
+  if (gi == nullptr || transforms == nullptr || in_centers == nullptr || out_centers == nullptr)
+    return fail(LMG_ERR_INVALID_ARGUMENT, "null interpolater arguments");
+  if (batch < 0 || nchannels < 0) return fail(LMG_ERR_INVALID_ARGUMENT, "negative size");
+  if (grad_out == grad_in && grad_out != nullptr)
+    return fail(LMG_ERR_INVALID_ARGUMENT, "Input and output grid can not be the same in GridInterpolator.");
+  if (grad_out == nullptr) return fail(LMG_ERR_INVALID_ARGUMENT, "Output gradient grid not allocated");
+  if (grad_in == nullptr) return fail(LMG_ERR_INVALID_ARGUMENT, "Input gradient grid not allocated");
+  cudaStream_t st = (cudaStream_t)stream;
+  size_t in_elems = (size_t)nchannels * gi->in_dim * gi->in_dim * gi->in_dim;
+  cudaError_t e = cudaMemsetAsync(grad_in, 0, in_elems * batch * sizeof(float), st);
+  if (e != cudaSuccess) return cuda_fail(e, "zeroing the input gradient");
+  lmg::InterpArgs I;
+  I.in_res = gi->in_resolution;
+  I.out_res = gi->out_resolution;
+  I.in_half = (float)(gi->in_dimension / 2.0);
+  I.out_half = (float)(gi->out_dimension / 2.0);
+  I.in_dim = gi->in_dim;
+  I.out_dim = gi->out_dim;
+  I.K = nchannels;
+  I.in = grad_out;
+  I.out = grad_in;
+  for (int b0 = 0; b0 < batch; b0 += lmg::INTERP_MAX_EX) {
+    int nb = std::min(lmg::INTERP_MAX_EX, batch - b0);
+    I.b0 = b0;
+    for (int i = 0; i < nb; i++) {
+      I.ex[i].X = to_xform(&transforms[b0 + i]);
+      for (int k = 0; k < 3; k++) {
+        I.ex[i].in_center[k] = in_centers[(size_t)(b0 + i) * 3 + k];
+        I.ex[i].out_center[k] = out_centers[(size_t)(b0 + i) * 3 + k];
+      }
+    }
+    e = lmg::launch_interpolate_backward(I, nb, st);
+    g_launches += 1;
+    if (e != cudaSuccess) return cuda_fail(e, "interpolate backward");
+  }
+  return LMG_OK;
+}
+
 }  // extern "C"

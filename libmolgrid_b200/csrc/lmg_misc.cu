@@ -349,6 +349,57 @@ cudaError_t read_tma_timeouts(unsigned* count) {
   return cudaMemcpyFromSymbol(count, g_tma_timeouts, sizeof(unsigned));
 }
 
+// Adjoint of the interpolation (the reference leaves it as a TODO, include/libmolgrid/
+// grid_interpolater.h:179): every output voxel hands its gradient to the eight input voxels it was
+// blended from, with the forward pass's weights; contributions outside the input grid are dropped,
+// as their values were zeros in the forward pass.  I.in is the gradient with respect to the output
+// (read), I.out the gradient with respect to the input (zero-filled by the caller, accumulated here).
+__global__ void __launch_bounds__(256) k_interpolate_backward(InterpArgs I) {
+  int bl = blockIdx.y;
+  const InterpExample& E = I.ex[bl];
+  unsigned od = I.out_dim;
+  unsigned v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= od * od * od) return;
+  unsigned k = v % od, j = (v / od) % od, i = v / (od * od);
+  InterpFrame F = interp_frame(I, E);
+  float gx, gy, gz;
+  interp_point(I, F, i, j, k, gx, gy, gz);
+  InterpCell C = interp_cell(gx, gy, gz);
+  int id = (int)I.in_dim;
+  if (C.xh < 0 || C.xl >= id || C.yh < 0 || C.yl >= id || C.zh < 0 || C.zl >= id) return;
+  size_t ichan = (size_t)id * id * id, ochan = (size_t)od * od * od;
+  size_t b = (size_t)I.b0 + bl;
+  const float* gout = I.in + b * I.K * ochan + v;
+  float* gin = I.out + b * I.K * ichan;
+  // corner (a,b,c) has weight wx[a]*wy[b]*wz[c], the factors of interp_blend
+  int xs[2] = {C.xl, C.xh}, ys[2] = {C.yl, C.yh}, zs[2] = {C.zl, C.zh};
+  float wx[2] = {C.xm, C.xd}, wy[2] = {C.ym, C.yd}, wz[2] = {C.zm, C.zd};
+  for (int c = 0; c < I.K; c++) {
+    float g = __ldg(gout + c * ochan);
+    if (g == 0.f) continue;
+    float* gc = gin + c * ichan;
+#pragma unroll
+    for (int a = 0; a < 2; a++)
+#pragma unroll
+      for (int bb = 0; bb < 2; bb++)
+#pragma unroll
+        for (int cc = 0; cc < 2; cc++) {
+          int x = xs[a], y = ys[bb], z = zs[cc];
+          float w = wx[a] * wy[bb] * wz[cc];
+          if (w != 0.f && x >= 0 && x < id && y >= 0 && y < id && z >= 0 && z < id)
+            atomicAdd(gc + ((size_t)x * id + y) * id + z, w * g);
+        }
+  }
+}
+
+cudaError_t launch_interpolate_backward(const InterpArgs& I, int nb, cudaStream_t st) {
+  unsigned nv = I.out_dim * I.out_dim * I.out_dim;
+  if (nv == 0 || nb == 0 || I.K == 0) return cudaSuccess;
+  dim3 grid((nv + 255) / 256, nb);
+  k_interpolate_backward<<<grid, 256, 0, st>>>(I);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_interpolate(const InterpArgs& I, int nb, cudaStream_t st) {
   unsigned nv = I.out_dim * I.out_dim * I.out_dim;
   if (nv == 0 || nb == 0 || I.K == 0) return cudaSuccess;

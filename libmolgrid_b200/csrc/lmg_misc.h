@@ -29,6 +29,8 @@ struct InterpArgs {
 cudaError_t launch_transform(const Xform& X, int n, const float* in, float* out, int dotranslate,
                              bool forward, cudaStream_t st);
 cudaError_t launch_interpolate(const InterpArgs& I, int nb, cudaStream_t st);
+// adjoint: I.in = gradient of the output grid (read), I.out = gradient of the input grid (accumulated)
+cudaError_t launch_interpolate_backward(const InterpArgs& I, int nb, cudaStream_t st);
 
 // Tiled kernel: output tiles of ITILE^3 voxels read a staged box of the input of at most
 // ITILE_BX x ITILE_BY x ITILE_BZ voxels (z is the contiguous axis; the box starts on a multiple of four).

@@ -60,6 +60,21 @@ class GridInterpolater {
     forward(c, in, transform, c, out);
   }
 
+  // Gradient with respect to forward's input from the gradient with respect to its output, for the
+  // same transform and centres (the reference leaves the backward pass open).
+  void backward(float3 in_center, const Grid<float, 4, true>& grad_out, const Transform& transform,
+                float3 out_center, Grid<float, 4, true>& grad_in) const {
+    check_grids(grad_in, grad_out);
+    lmg_transform t = transform.c_struct();
+    float ic[3] = {in_center.x, in_center.y, in_center.z}, oc[3] = {out_center.x, out_center.y, out_center.z};
+    detail::check(lmg_interpolate_backward(&s_, 1, (int)grad_out.dimension(0), grad_out.data(), &t, ic, oc,
+                                           grad_in.data(), nullptr));
+  }
+  void backward(const Grid<float, 4, true>& grad_out, const Transform& transform, Grid<float, 4, true>& grad_in) const {
+    float3 c = transform.get_rotation_center();
+    backward(c, grad_out, transform, c, grad_in);
+  }
+
  private:
   void check_grids(const Grid<float, 4, true>& in, const Grid<float, 4, true>& out) const {
     if (in.data() == out.data()) throw std::invalid_argument("Input and output grid can not be the same in GridInterpolator.");

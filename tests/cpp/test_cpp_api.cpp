@@ -161,6 +161,19 @@ int main(int argc, char** argv) {
     EXPECT_THROW(gi.forward(same, t, same), std::invalid_argument);
   }
   write_grid(out, dst);
+  {
+    // backward is the adjoint of forward: <forward(src), dst> == <src, backward(dst)>
+    MGrid4f back(K, D, D, D);
+    Grid4fCUDA gb = back.gpu();
+    gi.backward(dst.gpu(), t, gb);
+    double lhs = 0, rhs = 0;
+    Grid4f hs = src.cpu(), hd = dst.cpu(), hb = back.cpu();
+    for (size_t i = 0; i < hs.size(); i++) {
+      lhs += (double)hd.data()[i] * hd.data()[i];
+      rhs += (double)hs.data()[i] * hb.data()[i];
+    }
+    EXPECT(lhs > 1.0 && std::fabs(lhs - rhs) <= 1e-4 * lhs);
+  }
 
   // ---- 8. argument errors carry the reference's exception types
   {

@@ -45,7 +45,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--ops", default="forward,forward_binary,backward,relevance,forward_vector,"
-                                      "backward_vector,backward_gradients,onehot_forward,onehot_backward,interpolate,provider")
+                                      "backward_vector,backward_gradients,onehot_forward,onehot_backward,onehot_gradgrad,interpolate,"
+                                      "provider")
     ap.add_argument("--interp-batch", type=int, default=48)
     args = ap.parse_args()
     import torch
@@ -148,7 +149,7 @@ def main():
         del grid, diff, dd
 
     # ---- vector types with per-atom radii (the autograd bindings' layout), 48^3 -------------------
-    if set(ops) & {"onehot_forward", "onehot_backward"}:
+    if set(ops) & {"onehot_forward", "onehot_backward", "onehot_gradgrad"}:
         B = 50
         coords, types, radii, ns, tr = cases.blob_batch(1001, B, 2000, 4000, T)
         tv = np.zeros(types.shape + (T,), np.float32)
@@ -176,6 +177,14 @@ def main():
                    timeit(lambda: g.backward_arrays(cen, dc, dtv, dr, diff, ag, transforms=dtr, n_atoms=dn,
                                                     want_type_gradients=False)),
                    B, gb + natoms * (28 + 4 * T))
+        if "onehot_gradgrad" in ops:
+            g.backward(cen, dc, dtv, dr, diff, ag, tg, transforms=dtr, n_atoms=dn)
+            dd, add, tdd = torch.empty_like(grid), torch.empty_like(ag), torch.empty_like(tg)
+            report("onehot_gradgrad", wl,
+                   timeit(lambda: g.backward_gradients(cen, dc, dtv, dr, diff, ag, tg, dd, add, tdd,
+                                                       transforms=dtr, n_atoms=dn)),
+                   B, 2 * gb + natoms * (40 + 12 * T))
+            del dd
         del grid, diff
 
     # ---- interpolation --------------------------------------------------------------------------

@@ -1948,6 +1948,235 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads_atom_ag(BwdA
   }
 }
 
+// backward_gradients for the same layout (vector types, per-atom radii), one warp per atom.  Only
+// channels in which the atom carries weight take part (src/grid_maker.cpp:573).
+// Grid term, per voxel and such channel t:  density * tgrad_t  -  w_t * s * (delta . agrad), with
+// s = (d density/d dist)/dist: the two voxel-dependent factors are shared by the channels.
+__global__ void __launch_bounds__(SCAT_WARPS * 32) k_gradgrad_quads_atom(BwdArgs G) {
+  __shared__ ColBufD bufs[SCAT_WARPS];
+  __shared__ ZTabs ztabs[SCAT_WARPS];
+  __shared__ int nz_t[SCAT_WARPS][VA_CH];
+  __shared__ float nz_w[SCAT_WARPS][VA_CH], nz_g[SCAT_WARPS][VA_CH];
+  const GMParams& gm = G.gm;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int item = blockIdx.x * SCAT_WARPS + wid;
+  int bl = blockIdx.y;
+  int b = G.b0 + bl;
+  if (item >= G.N) return;
+  ColBufD& buf = bufs[wid];
+  ZTabs& zt = ztabs[wid];
+
+  float cx, cy, cz;
+  if (G.centers != nullptr) {
+    cx = G.centers[b * 3]; cy = G.centers[b * 3 + 1]; cz = G.centers[b * 3 + 2];
+  } else {
+    cx = G.center_host[0]; cy = G.center_host[1]; cz = G.center_host[2];
+  }
+  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
+  ItemParams P = load_item<false>(G, bl, b, item, ox, oy, oz);
+  if (!P.valid) return;
+
+  size_t dim = gm.dim;
+  const size_t chan_stride = dim * dim * dim;
+  float* outb = G.out_grid + (size_t)b * G.T * chan_stride;
+  const size_t ai = (size_t)b * G.N + item;
+  const float* wrow = G.type_vector + ai * G.T;
+  const float* grow = G.tg_in + ai * G.T;
+  const float inx = G.ag_in[ai * 3], iny = G.ag_in[ai * 3 + 1], inz = G.ag_in[ai * 3 + 2];
+  const float kexp = P.inv_ar2 * NEG2_LOG2E;
+  const float k4 = 4.f * P.inv_ar2, kD = -gm.D * P.inv_ar2, kE = -gm.E * P.inv_ar;
+  const float ta = gm.ta, ntb = -gm.tb;
+
+  unsigned nx = P.hix - P.lox, ny = P.hiy - P.loy;
+  unsigned ncols = nx * ny;
+  float inv_ny = 1.f / (float)ny;
+  for (int tb = 0; tb < G.T; tb += VA_CH) {
+    int t = tb + lane;
+    float w = t < G.T ? wrow[t] : 0.f;
+    unsigned m = __ballot_sync(0xffffffffu, w != 0.f);
+    int nnz = __popc(m);
+    if (nnz == 0) continue;
+    __syncwarp();
+    if (w != 0.f) {
+      int slot = __popc(m & ((1u << lane) - 1u));
+      nz_t[wid][slot] = t;
+      nz_w[wid][slot] = w;
+      nz_g[wid][slot] = grow[t];
+    }
+    __syncwarp();
+    for (unsigned cbase = 0; cbase < ncols;) {
+      unsigned nkept = compact_columns<ColBufD, true>(buf, P, cbase, ncols, ny, inv_ny, P.Tcut, ox, oy,
+                                                      gm.res, gm.dim, lane);
+      for (unsigned zc = P.loz & ~3u; zc < P.hiz; zc += 4 * QPASS) {
+        __syncwarp();
+        fill_ztabs(zt, zc, P, oz, gm.res, kexp, lane);
+        __syncwarp();
+        unsigned nq = min((unsigned)QPASS, (P.hiz - zc + 3) >> 2);
+        for (unsigned c0 = 0; c0 < nkept; c0 += 32) {
+          unsigned i = c0 + lane;
+          bool have = i < nkept;
+          float dxy2 = have ? buf.dxy2[i] : CUDART_NAN_F;
+          float dotxy = have ? fmaf(buf.dx[i], inx, buf.dy[i] * iny) : 0.f;
+          float* row = outb + (size_t)(have ? buf.row[i] : 0u) * dim + zc;
+          float exy = ex2_approx(dxy2 * kexp);
+          for (unsigned q = 0; q < nq; q++) {
+            float4 d2 = zt.dz2[q], e = zt.ez[q], dz = zt.dz[q];
+            float d2v[4] = {d2.x, d2.y, d2.z, d2.w}, ev[4] = {e.x, e.y, e.z, e.w};
+            float dzv[4] = {dz.x, dz.y, dz.z, dz.w}, val[4], sd[4];
+            bool any = false;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              float rsq = __fadd_rn(dxy2, d2v[j]);
+              float g = exy * ev[j];
+              float tq = fminf(fmaf(ta, sqrt_approx(rsq * P.inv_ar2), ntb), 0.f);
+              bool gauss = rsq <= P.Tg, in = rsq <= P.Tcut;
+              float sg = gauss ? k4 * g : fmaf(kE, rsqrt_approx(rsq), kD);
+              float dot = rsq > 0.f ? fmaf(dzv[j], inz, dotxy) : 0.f;
+              val[j] = in ? (gauss ? g : tq * tq) : 0.f;
+              sd[j] = in ? sg * dot : 0.f;
+              any = any || in;
+            }
+            if (any) {
+              for (int k = 0; k < nnz; k++) {
+                float wk = nz_w[wid][k], gk = nz_g[wid][k];
+                red_add_v4(row + (size_t)nz_t[wid][k] * chan_stride + 4 * q, fmaf(val[0], gk, sd[0] * wk),
+                           fmaf(val[1], gk, sd[1] * wk), fmaf(val[2], gk, sd[2] * wk),
+                           fmaf(val[3], gk, sd[3] * wk));
+              }
+            }
+          }
+        }
+      }
+      __syncwarp();
+    }
+  }
+}
+
+// Atom term (src/grid_maker.cpp:636-662, second derivatives of src/grid_maker.cu:812-878): per voxel
+//   sum_t dv_t [ w_t (alpha (delta.agrad) delta_a + beta agrad_a) + tgrad_t (alpha delta_a^2 + beta) ]
+// = (alpha (delta.agrad) delta_a + beta agrad_a) S1 + (alpha delta_a^2 + beta) S2
+// with S1 = sum_t w_t dv_t and S2 = sum_t tgrad_t dv_t over the weighted channels.
+__global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads_atom_gg(BwdArgs G) {
+  __shared__ ColBufD bufs[BWD2_WARPS];
+  __shared__ ZTabs ztabs[BWD2_WARPS];
+  __shared__ int nz_t[BWD2_WARPS][VA_CH];
+  __shared__ float nz_w[BWD2_WARPS][VA_CH], nz_g[BWD2_WARPS][VA_CH];
+  const GMParams& gm = G.gm;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int item = blockIdx.x * BWD2_WARPS + wid;
+  int bl = blockIdx.y;
+  int b = G.b0 + bl;
+  if (item >= G.N) return;
+  ColBufD& buf = bufs[wid];
+  ZTabs& zt = ztabs[wid];
+
+  float cx, cy, cz;
+  if (G.centers != nullptr) {
+    cx = G.centers[b * 3]; cy = G.centers[b * 3 + 1]; cz = G.centers[b * 3 + 2];
+  } else {
+    cx = G.center_host[0]; cy = G.center_host[1]; cz = G.center_host[2];
+  }
+  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
+  ItemParams P = load_item<false>(G, bl, b, item, ox, oy, oz);
+
+  size_t dim = gm.dim;
+  const size_t chan_stride = dim * dim * dim;
+  const float* diffb = G.diff + (size_t)b * G.T * chan_stride;
+  const size_t ai = (size_t)b * G.N + item;
+  const float* wrow = G.type_vector + ai * G.T;
+  const float* grow = G.tg_in + ai * G.T;
+  const float inx = G.ag_in[ai * 3], iny = G.ag_in[ai * 3 + 1], inz = G.ag_in[ai * 3 + 2];
+  const float kexp = P.inv_ar2 * NEG2_LOG2E;
+  float agx = 0.f, agy = 0.f, agz = 0.f;
+
+  for (int tb = 0; P.valid && tb < G.T; tb += VA_CH) {
+    int t = tb + lane;
+    float w = t < G.T ? wrow[t] : 0.f;
+    unsigned m = __ballot_sync(0xffffffffu, w != 0.f);
+    int nnz = __popc(m);
+    if (nnz == 0) continue;
+    __syncwarp();
+    if (w != 0.f) {
+      int slot = __popc(m & ((1u << lane) - 1u));
+      nz_t[wid][slot] = t;
+      nz_w[wid][slot] = w;
+      nz_g[wid][slot] = grow[t];
+    }
+    __syncwarp();
+    unsigned nx = P.hix - P.lox, ny = P.hiy - P.loy;
+    unsigned ncols = nx * ny;
+    float inv_ny = 1.f / (float)ny;
+    for (unsigned cbase = 0; cbase < ncols;) {
+      unsigned nkept = compact_columns<ColBufD, true>(buf, P, cbase, ncols, ny, inv_ny, P.Tcut, ox, oy,
+                                                      gm.res, gm.dim, lane);
+      for (unsigned zc = P.loz & ~3u; zc < P.hiz; zc += 4 * QPASS) {
+        __syncwarp();
+        fill_ztabs(zt, zc, P, oz, gm.res, kexp, lane);
+        __syncwarp();
+        unsigned nq = min((unsigned)QPASS, (P.hiz - zc + 3) >> 2);
+        for (unsigned c0 = 0; c0 < nkept; c0 += 32) {
+          unsigned i = c0 + lane;
+          bool have = i < nkept;
+          float dxy2 = have ? buf.dxy2[i] : CUDART_NAN_F;
+          float dx = have ? buf.dx[i] : 0.f, dy = have ? buf.dy[i] : 0.f;
+          const float4* row = reinterpret_cast<const float4*>(diffb + (size_t)(have ? buf.row[i] : 0u) * dim + zc);
+          float exy = ex2_approx(dxy2 * kexp);
+          float dotxy = fmaf(dx, inx, dy * iny);
+          for (unsigned q = 0; q < nq; q++) {
+            float4 d2 = zt.dz2[q], e = zt.ez[q], dz = zt.dz[q];
+            float lo = fminf(fminf(d2.x, d2.y), fminf(d2.z, d2.w));  // fminf skips the NaN entries
+            if (!(__fadd_rn(dxy2, lo) <= P.Tcut)) continue;
+            float s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int k = 0; k < nnz; k++) {
+              float wk = nz_w[wid][k], gk = nz_g[wid][k];
+              float4 dv = __ldg(row + q + (size_t)nz_t[wid][k] * (chan_stride / 4));
+              s1[0] = fmaf(wk, dv.x, s1[0]); s1[1] = fmaf(wk, dv.y, s1[1]);
+              s1[2] = fmaf(wk, dv.z, s1[2]); s1[3] = fmaf(wk, dv.w, s1[3]);
+              s2[0] = fmaf(gk, dv.x, s2[0]); s2[1] = fmaf(gk, dv.y, s2[1]);
+              s2[2] = fmaf(gk, dv.z, s2[2]); s2[3] = fmaf(gk, dv.w, s2[3]);
+            }
+            float d2v[4] = {d2.x, d2.y, d2.z, d2.w}, ev[4] = {e.x, e.y, e.z, e.w}, dzv[4] = {dz.x, dz.y, dz.z, dz.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              float rsq = __fadd_rn(dxy2, d2v[j]);
+              if (rsq <= P.Tcut) {
+                float alpha, beta;
+                if (rsq <= P.Tg) {
+                  float g = exy * ev[j];
+                  alpha = 16.f * g * P.inv_ar2 * P.inv_ar2;
+                  beta = -4.f * g * P.inv_ar2;
+                } else {
+                  float id = rsqrt_approx(rsq);
+                  float S = fmaf(gm.D * P.inv_ar, rsq * id, gm.E);
+                  beta = S * id * P.inv_ar;
+                  alpha = fmaf(gm.D * P.inv_ar2, id * id, -beta * id * id);
+                }
+                float dzj = dzv[j];
+                float ad = alpha * fmaf(dzj, inz, dotxy);
+                agx += fmaf(ad, dx, beta * inx) * s1[j] + fmaf(alpha, dx * dx, beta) * s2[j];
+                agy += fmaf(ad, dy, beta * iny) * s1[j] + fmaf(alpha, dy * dy, beta) * s2[j];
+                agz += fmaf(ad, dzj, beta * inz) * s1[j] + fmaf(alpha, dzj * dzj, beta) * s2[j];
+              }
+            }
+          }
+        }
+      }
+      __syncwarp();
+    }
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) {
+    agx += __shfl_xor_sync(0xffffffffu, agx, o);
+    agy += __shfl_xor_sync(0xffffffffu, agy, o);
+    agz += __shfl_xor_sync(0xffffffffu, agz, o);
+  }
+  if (lane == 0) {
+    G.atom_gradients[ai * 3] = agx;
+    G.atom_gradients[ai * 3 + 1] = agy;
+    G.atom_gradients[ai * 3 + 2] = agz;
+  }
+}
+
 // atom_gradients[a] = sum over channels in ascending order of partial[a][t] * w[a][t] for w != 0
 // (src/grid_maker.cpp:508-515)
 __global__ void __launch_bounds__(256) k_reduce_types(BwdArgs G) {
@@ -2046,6 +2275,9 @@ cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st) {
     else k_backward_warp<1, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
     int n = G.nb * G.N;
     k_reduce_types<<<(n + 255) / 256, 256, 0, st>>>(G);
+  } else if (mode == 3 && quads && !G.gm.rti) {
+    dim3 ga((unsigned)((G.N + BWD2_WARPS - 1) / BWD2_WARPS), G.nb);
+    k_backward_quads_atom_gg<<<ga, BWD2_WARPS * 32, 0, st>>>(G);
   } else if (mode == 3) {
     if (quads) k_backward_quads<3, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
     else k_backward_warp<3, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
@@ -2064,7 +2296,10 @@ cudaError_t launch_gradgrad_scatter(const BwdArgs& G, cudaStream_t st) {
   long items = (long)G.N * G.T;
   if (items == 0 || G.nb == 0) return cudaSuccess;
   dim3 grid((unsigned)((items + SCAT_WARPS - 1) / SCAT_WARPS), G.nb);
-  if (G.quads && G.gm.dim % 4 == 0 && (uintptr_t)G.out_grid % 16 == 0)
+  if (G.quads && !G.gm.rti && G.gm.dim % 4 == 0 && (uintptr_t)G.out_grid % 16 == 0) {
+    dim3 ga((unsigned)((G.N + SCAT_WARPS - 1) / SCAT_WARPS), G.nb);
+    k_gradgrad_quads_atom<<<ga, SCAT_WARPS * 32, 0, st>>>(G);
+  } else if (G.quads && G.gm.dim % 4 == 0 && (uintptr_t)G.out_grid % 16 == 0)
     k_gradgrad_quads<<<grid, SCAT_WARPS * 32, 0, st>>>(G);
   else
     k_gradgrad_scatter<<<grid, SCAT_WARPS * 32, 0, st>>>(G);

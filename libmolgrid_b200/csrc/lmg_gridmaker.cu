@@ -878,7 +878,7 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_warp(BwdArgs G) {
   int bl = blockIdx.y;
   int b = G.b0 + bl;
   if (item >= items_per_ex) return;
-  if (MODE == 3) {
+  if (MODE == 3 || (MODE == 1 && G.type_gradients == nullptr)) {
     // an (atom, channel) pair without weight contributes nothing: leave before any other load
     int ea = item / G.T;
     if (G.type_vector[((size_t)b * G.N + ea) * G.T + (item - ea * G.T)] == 0.f) return;
@@ -1246,24 +1246,17 @@ __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, 
                : "memory");
 }
 
+// One work item (an atom, or an (atom, channel) pair with VEC) of the forward pass on aligned quads.
 template <bool VEC>
-__global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads(BwdArgs G) {
-  __shared__ ColBuf bufs[SCAT_WARPS];
-  __shared__ ZTabs ztabs[SCAT_WARPS];
+__device__ __forceinline__ void forward_quads_item(const BwdArgs& G, int item, int bl, ColBuf& buf, ZTabs& zt,
+                                                   int lane) {
   const GMParams& gm = G.gm;
-  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  int items_per_ex = VEC ? G.N * G.T : G.N;
-  int item = blockIdx.x * SCAT_WARPS + wid;
-  int bl = blockIdx.y;
   int b = G.b0 + bl;
-  if (item >= items_per_ex) return;
   if (VEC) {
     // an (atom, channel) pair without weight contributes nothing: leave before any other load
     int ea = item / G.T;
     if (G.type_vector[((size_t)b * G.N + ea) * G.T + (item - ea * G.T)] == 0.f) return;
   }
-  ColBuf& buf = bufs[wid];
-  ZTabs& zt = ztabs[wid];
 
   float cx, cy, cz;
   if (G.centers != nullptr) {
@@ -1318,26 +1311,57 @@ __global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads(BwdArgs G) {
   }
 }
 
+template <bool VEC>
+__global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads(BwdArgs G) {
+  __shared__ ColBuf bufs[SCAT_WARPS];
+  __shared__ ZTabs ztabs[SCAT_WARPS];
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int item = blockIdx.x * SCAT_WARPS + wid;
+  if (item >= (VEC ? G.N * G.T : G.N)) return;
+  forward_quads_item<VEC>(G, item, blockIdx.y, bufs[wid], ztabs[wid], lane);
+}
+
+// Vector types whose radii differ by channel: one warp takes a group of NZ_GROUP consecutive channels
+// of an atom and runs the (atom, channel) item of every channel of the group in which the atom
+// carries weight - no work item, and no block, per channel without weight (27 of 28 with one-hot
+// types), and still several warps per atom when every channel is weighted.
+constexpr int NZ_GROUP = 8;
+__host__ __device__ inline int nz_groups(int T) { return (T + NZ_GROUP - 1) / NZ_GROUP; }
+
+#define LMG_FOR_EACH_WEIGHTED_CHANNEL(G, b, unit, lane, atom, t)                                        \
+  if (int atom = (unit) / nz_groups((G).T); true)                                                       \
+    if (int t0_ = ((unit) - atom * nz_groups((G).T)) * NZ_GROUP; true)                                  \
+      for (unsigned m_ = __ballot_sync(                                                                 \
+               0xffffffffu, (lane) < NZ_GROUP && t0_ + (lane) < (G).T &&                                \
+                                (G).type_vector[((size_t)(b) * (G).N + atom) * (G).T + t0_ + (lane)] != 0.f); \
+           m_ != 0u; m_ &= m_ - 1u)                                                                     \
+        if (int t = t0_ + __ffs(m_) - 1; true)
+
+__global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads_nz(BwdArgs G) {
+  __shared__ ColBuf bufs[SCAT_WARPS];
+  __shared__ ZTabs ztabs[SCAT_WARPS];
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int unit = blockIdx.x * SCAT_WARPS + wid;
+  if (unit >= G.N * nz_groups(G.T)) return;
+  int b = G.b0 + blockIdx.y;
+  LMG_FOR_EACH_WEIGHTED_CHANNEL(G, b, unit, lane, atom, t) {
+    forward_quads_item<true>(G, atom * G.T + t, blockIdx.y, bufs[wid], ztabs[wid], lane);
+    __syncwarp();
+  }
+}
+
 // The backward passes (modes as in k_backward_warp) on aligned quads.
 template <int MODE, bool BINARY>
-__global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads(BwdArgs G) {
+__device__ __forceinline__ void backward_quads_item(const BwdArgs& G, int item, int bl, ColBufD& buf, ZTabs& zt,
+                                                    int lane) {
   constexpr bool VEC = MODE == 1 || MODE == 3;
-  __shared__ ColBufD bufs[BWD2_WARPS];
-  __shared__ ZTabs ztabs[BWD2_WARPS];
   const GMParams& gm = G.gm;
-  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  int items_per_ex = VEC ? G.N * G.T : G.N;
-  int item = blockIdx.x * BWD2_WARPS + wid;
-  int bl = blockIdx.y;
   int b = G.b0 + bl;
-  if (item >= items_per_ex) return;
-  if (MODE == 3) {
+  if (MODE == 3 || (MODE == 1 && G.type_gradients == nullptr)) {
     // an (atom, channel) pair without weight contributes nothing: leave before any other load
     int ea = item / G.T;
     if (G.type_vector[((size_t)b * G.N + ea) * G.T + (item - ea * G.T)] == 0.f) return;
   }
-  ColBufD& buf = bufs[wid];
-  ZTabs& zt = ztabs[wid];
 
   float cx, cy, cz;
   if (G.centers != nullptr) {
@@ -1509,23 +1533,43 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads(BwdArgs G) {
   }
 }
 
-// Grid term of backward_gradients on aligned quads (see k_gradgrad_scatter).
-__global__ void __launch_bounds__(SCAT_WARPS * 32) k_gradgrad_quads(BwdArgs G) {
-  __shared__ ColBufD bufs[SCAT_WARPS];
-  __shared__ ZTabs ztabs[SCAT_WARPS];
-  const GMParams& gm = G.gm;
+template <int MODE, bool BINARY>
+__global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads(BwdArgs G) {
+  constexpr bool VEC = MODE == 1 || MODE == 3;
+  __shared__ ColBufD bufs[BWD2_WARPS];
+  __shared__ ZTabs ztabs[BWD2_WARPS];
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  int item = blockIdx.x * SCAT_WARPS + wid;
-  int bl = blockIdx.y;
+  int item = blockIdx.x * BWD2_WARPS + wid;
+  if (item >= (VEC ? G.N * G.T : G.N)) return;
+  backward_quads_item<MODE, BINARY>(G, item, blockIdx.y, bufs[wid], ztabs[wid], lane);
+}
+
+// The (atom, channel) items of the weighted channels of one atom, by one warp: modes that need
+// nothing from channels without weight (MODE 1 when no type gradients are wanted, MODE 3).
+template <int MODE, bool BINARY>
+__global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads_nz(BwdArgs G) {
+  __shared__ ColBufD bufs[BWD2_WARPS];
+  __shared__ ZTabs ztabs[BWD2_WARPS];
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int unit = blockIdx.x * BWD2_WARPS + wid;
+  if (unit >= G.N * nz_groups(G.T)) return;
+  int b = G.b0 + blockIdx.y;
+  LMG_FOR_EACH_WEIGHTED_CHANNEL(G, b, unit, lane, atom, t) {
+    backward_quads_item<MODE, BINARY>(G, atom * G.T + t, blockIdx.y, bufs[wid], ztabs[wid], lane);
+    __syncwarp();
+  }
+}
+
+// Grid term of backward_gradients on aligned quads (see k_gradgrad_scatter).
+__device__ __forceinline__ void gradgrad_quads_item(const BwdArgs& G, int item, int bl, ColBufD& buf, ZTabs& zt,
+                                                    int lane) {
+  const GMParams& gm = G.gm;
   int b = G.b0 + bl;
-  if (item >= G.N * G.T) return;
   if (true) {
     // an (atom, channel) pair without weight contributes nothing: leave before any other load
     int ea = item / G.T;
     if (G.type_vector[((size_t)b * G.N + ea) * G.T + (item - ea * G.T)] == 0.f) return;
   }
-  ColBufD& buf = bufs[wid];
-  ZTabs& zt = ztabs[wid];
 
   float cx, cy, cz;
   if (G.centers != nullptr) {
@@ -1586,6 +1630,19 @@ __global__ void __launch_bounds__(SCAT_WARPS * 32) k_gradgrad_quads(BwdArgs G) {
         }
       }
     }
+    __syncwarp();
+  }
+}
+
+__global__ void __launch_bounds__(SCAT_WARPS * 32) k_gradgrad_quads_nz(BwdArgs G) {
+  __shared__ ColBufD bufs[SCAT_WARPS];
+  __shared__ ZTabs ztabs[SCAT_WARPS];
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int unit = blockIdx.x * SCAT_WARPS + wid;
+  if (unit >= G.N * nz_groups(G.T)) return;
+  int b = G.b0 + blockIdx.y;
+  LMG_FOR_EACH_WEIGHTED_CHANNEL(G, b, unit, lane, atom, t) {
+    gradgrad_quads_item(G, atom * G.T + t, blockIdx.y, bufs[wid], ztabs[wid], lane);
     __syncwarp();
   }
 }
@@ -2268,6 +2325,13 @@ cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st) {
     if (G.type_gradients == nullptr) k_backward_quads_atom_ag<<<ga, BWD2_WARPS * 32, 0, st>>>(G);
     else if (bin) k_backward_quads_atom<true><<<ga, BWD2_WARPS * 32, 0, st>>>(G);
     else k_backward_quads_atom<false><<<ga, BWD2_WARPS * 32, 0, st>>>(G);
+  } else if (mode == 1 && quads && G.type_gradients == nullptr) {
+    // radii by channel, no type gradients wanted: only the weighted channels of each atom
+    dim3 ga((unsigned)(((long)G.N * nz_groups(G.T) + BWD2_WARPS - 1) / BWD2_WARPS), G.nb);
+    if (bin) k_backward_quads_nz<1, true><<<ga, BWD2_WARPS * 32, 0, st>>>(G);
+    else k_backward_quads_nz<1, false><<<ga, BWD2_WARPS * 32, 0, st>>>(G);
+    int n = G.nb * G.N;
+    k_reduce_types<<<(n + 255) / 256, 256, 0, st>>>(G);
   } else if (mode == 1) {
     if (quads && bin) k_backward_quads<1, true><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
     else if (quads) k_backward_quads<1, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
@@ -2279,7 +2343,8 @@ cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st) {
     dim3 ga((unsigned)((G.N + BWD2_WARPS - 1) / BWD2_WARPS), G.nb);
     k_backward_quads_atom_gg<<<ga, BWD2_WARPS * 32, 0, st>>>(G);
   } else if (mode == 3) {
-    if (quads) k_backward_quads<3, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
+    dim3 ga((unsigned)(((long)G.N * nz_groups(G.T) + BWD2_WARPS - 1) / BWD2_WARPS), G.nb);
+    if (quads) k_backward_quads_nz<3, false><<<ga, BWD2_WARPS * 32, 0, st>>>(G);
     else k_backward_warp<3, false><<<grid, BWD2_WARPS * 32, 0, st>>>(G);
     int n = G.nb * G.N;
     k_reduce_types<<<(n + 255) / 256, 256, 0, st>>>(G);
@@ -2299,8 +2364,10 @@ cudaError_t launch_gradgrad_scatter(const BwdArgs& G, cudaStream_t st) {
   if (G.quads && !G.gm.rti && G.gm.dim % 4 == 0 && (uintptr_t)G.out_grid % 16 == 0) {
     dim3 ga((unsigned)((G.N + SCAT_WARPS - 1) / SCAT_WARPS), G.nb);
     k_gradgrad_quads_atom<<<ga, SCAT_WARPS * 32, 0, st>>>(G);
-  } else if (G.quads && G.gm.dim % 4 == 0 && (uintptr_t)G.out_grid % 16 == 0)
-    k_gradgrad_quads<<<grid, SCAT_WARPS * 32, 0, st>>>(G);
+  } else if (G.quads && G.gm.dim % 4 == 0 && (uintptr_t)G.out_grid % 16 == 0) {
+    dim3 ga((unsigned)(((long)G.N * nz_groups(G.T) + SCAT_WARPS - 1) / SCAT_WARPS), G.nb);
+    k_gradgrad_quads_nz<<<ga, SCAT_WARPS * 32, 0, st>>>(G);
+  }
   else
     k_gradgrad_scatter<<<grid, SCAT_WARPS * 32, 0, st>>>(G);
   return cudaGetLastError();
@@ -2321,8 +2388,13 @@ cudaError_t launch_forward_scatter(const BwdArgs& G, bool vec, cudaStream_t st) 
     return cudaGetLastError();
   }
   if (G.quads && !bin && !G.precise && G.gm.dim % 4 == 0 && (uintptr_t)G.out_grid % 16 == 0) {
-    if (vec) k_forward_quads<true><<<grid, SCAT_WARPS * 32, 0, st>>>(G);
-    else k_forward_quads<false><<<grid, SCAT_WARPS * 32, 0, st>>>(G);
+    if (vec) {
+      // radii by channel: one warp per atom runs the items of its weighted channels
+      dim3 ga((unsigned)(((long)G.N * nz_groups(G.T) + SCAT_WARPS - 1) / SCAT_WARPS), G.nb);
+      k_forward_quads_nz<<<ga, SCAT_WARPS * 32, 0, st>>>(G);
+      return cudaGetLastError();
+    }
+    k_forward_quads<false><<<grid, SCAT_WARPS * 32, 0, st>>>(G);
     return cudaGetLastError();
   }
   if (vec) {

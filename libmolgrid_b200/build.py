@@ -48,5 +48,36 @@ def build_library(force=False, verbose=False):
     return LIB
 
 
+NATIVE_SRC = os.path.join(HERE, "cpp", "bindings.cpp")
+
+
+def native_module_path():
+    import sysconfig
+    return os.path.join(HERE, "molgrid_native" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_native_module(force=False):
+    """Compile the pybind11 module over the C++ host layer (g++; links liblmg_b200.so by $ORIGIN)."""
+    import pybind11
+    import sysconfig
+    out = native_module_path()
+    deps = [NATIVE_SRC, LIB] + [os.path.join(HERE, "cpp", "include", "libmolgrid", f)
+                                for f in os.listdir(os.path.join(HERE, "cpp", "include", "libmolgrid"))]
+    if not force and os.path.exists(out) and all(os.path.getmtime(d) <= os.path.getmtime(out) for d in deps):
+        return out
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden",
+           "-I" + pybind11.get_include(), "-I" + sysconfig.get_paths()["include"],
+           "-I" + os.path.join(HERE, "cpp", "include"), "-I" + os.path.join(HERE, "..", "include"),
+           "-I" + os.path.join(cuda, "include"), NATIVE_SRC, "-o", out,
+           "-L" + HERE, "-llmg_b200", "-L" + os.path.join(cuda, "lib64"), "-lcudart",
+           "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(cuda, "lib64")]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)
+    return out
+
+
 if __name__ == "__main__":
     print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_native_module(force="--force" in sys.argv))

@@ -93,9 +93,9 @@ class GridMaker {
   }
 
   void forward(float3 grid_center, const CoordinateSet& in, Grid<float, 4, true>& out, const Transform* transform = nullptr) const {
-    if (in.has_indexed_types()) forward(grid_center, in.coords.gpu(), in.type_index.gpu(), in.radii.gpu(), out, transform);
-    else if (in.has_vector_types()) forward(grid_center, in.coords.gpu(), in.type_vector.gpu(), in.radii.gpu(), out, transform);
-    else throw std::invalid_argument("Type information missing from coordinate set");
+    // vector types win when the set has both (include/libmolgrid/grid_maker.h:132-153 of the reference)
+    if (in.has_vector_types() && in.size() > 0) forward(grid_center, in.coords.gpu(), in.type_vector.gpu(), in.radii.gpu(), out, transform);
+    else forward(grid_center, in.coords.gpu(), in.type_index.gpu(), in.radii.gpu(), out, transform);
   }
 
   // The Transform is applied inside the gridding kernels; the grid stays centred on the

@@ -195,13 +195,14 @@ def test_backward_known_answer(port):
         assert ag[0, 0].item() == pytest.approx(-0.60653066, rel=1e-4)
 
 
+@pytest.mark.parametrize("dimension", [11.5, 11.0])   # 24 points, and 23: rows not 16-byte aligned
 @pytest.mark.parametrize("rti", [False, True])
 @pytest.mark.parametrize("binary", [False, True])
-def test_backward_vector(port, rti, binary):
-    kw = dict(resolution=0.5, dimension=11.5, binary=binary, radius_type_indexed=rti)
+def test_backward_vector(port, rti, binary, dimension):
+    kw = dict(resolution=0.5, dimension=dimension, binary=binary, radius_type_indexed=rti)
     g, og = gm_pair(port, **kw)
     T = 6
-    coords, tv, radii = cases.vector_case(13, 150, T, 6.5, rti=rti)
+    coords, tv, radii = cases.vector_case(13, 150, T, dimension / 2 + 0.75, rti=rti)
     rng = np.random.default_rng(6)
     diff = rng.normal(size=g.grid_dimensions(T)).astype(np.float32)
     wag, wtg = port.backward_vector(og, (0, 0, 0), coords, tv, radii, diff)
@@ -312,6 +313,7 @@ def test_atoms_larger_than_the_radius_hint(port, binary):
 
 @pytest.mark.parametrize("rti", [False, True])
 @pytest.mark.parametrize("kw", [dict(resolution=0.5, dimension=11.5),
+                                dict(resolution=0.5, dimension=6.0),   # 13 points: rows not 16-byte aligned
                                 dict(resolution=0.25, dimension=5.75, gaussian_radius_multiple=-2.0)])
 def test_backward_gradients(port, kw, rti):
     """Second-order pass against the oracle; also batched with per-example transforms."""

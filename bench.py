@@ -185,7 +185,7 @@ def run_gpu_arm(args, rank, world, local_rank):
         cores = os.cpu_count() or 1
         per_core = 8   # about 0.1 s of CPU work per example
         rate, wall = cpu_examples_per_s(kind, cores, per_core)
-        cpu = {"value": rate, "unit": "examples/s", "cores": cores, "kind": kind,
+        cpu = {"value": rate, "unit": "examples/s", "cores": cores, "kind": kind, "per_core": rate / cores,
                "sample": "%d examples of the same workload (%d per core, one process per core), %.1f s wall"
                          % (cores * per_core, per_core, wall)}
 

@@ -50,6 +50,25 @@ class GridMaker {
   }
   const lmg_gridmaker& settings() const { return s_; }
 
+  // double grids: the signatures of the reference exist so that code written for them compiles, but
+  // the path computes in fp32 only (the reference's own CUDA vector backward and second-order
+  // kernels are float-only too, src/grid_maker.cu:645-649,805-809)
+  template <size_t N, bool G>
+  void forward(float3, const Grid<float, 2, G>&, const Grid<float, N, G>&, const Grid<float, 1, G>&,
+               Grid<double, 4, G>&) const {
+    throw std::invalid_argument("double grids are not supported on the GPU path: use float grids");
+  }
+  template <size_t N, bool G>
+  void backward(float3, const Grid<float, 2, G>&, const Grid<float, N, G>&, const Grid<float, 1, G>&,
+                const Grid<double, 4, G>&, Grid<double, 2, G>&) const {
+    throw std::invalid_argument("double grids are not supported on the GPU path: use float grids");
+  }
+  template <bool G>
+  void backward(float3, const Grid<float, 2, G>&, const Grid<float, 2, G>&, const Grid<float, 1, G>&,
+                const Grid<double, 4, G>&, Grid<double, 2, G>&, Grid<double, 2, G>&) const {
+    throw std::invalid_argument("double grids are not supported on the GPU path: use float grids");
+  }
+
   // ------------------------------------------------------------------ forward, device grids
   void forward(float3 grid_center, const Grid<float, 2, true>& coords, const Grid<float, 1, true>& type_index,
                const Grid<float, 1, true>& radii, Grid<float, 4, true>& out, const Transform* transform = nullptr) const {

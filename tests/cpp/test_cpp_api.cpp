@@ -193,6 +193,13 @@ int main(int argc, char** argv) {
     EXPECT_THROW(gm.check_types(), std::out_of_range);
   }
 
+  {
+    // double grids keep their signatures and throw
+    MGrid4d dgrid(T, D, D, D);
+    Grid4dCUDA dg = dgrid.gpu();
+    EXPECT_THROW(gm.forward(center, mc.gpu(), mt.gpu(), mr.gpu(), dg), std::invalid_argument);
+  }
+
   // ---- 9. managed grids: shared storage, slices, clone, resize
   {
     MGrid2f m(3, 4);

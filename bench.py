@@ -265,20 +265,31 @@ def run_gpu_arm(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
+    per_rank = {}
+
+    def timed(fn, steps, tag):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
+        h0 = time.perf_counter()
         for _ in range(steps):
             fn()
+        host_ms = (time.perf_counter() - h0) * 1e3                 # time the host needed to issue the steps
         torch.cuda.current_stream(dev).wait_stream(copy_stream)   # the last download belongs to the region
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
+        mine = torch.tensor([ms, host_ms, float(ns.sum())], device=dev, dtype=torch.float64)
         if world > 1:
+            every = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(every, mine)
             t = torch.tensor([ms], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
+        else:
+            every = [mine]
+        per_rank[tag] = [{"device_ms": round(float(x[0]), 3), "host_issue_ms": round(float(x[1]), 3),
+                          "atoms": int(x[2])} for x in every]
         return ms
 
     for _ in range(max(args.warmup, 3)):
@@ -288,7 +299,7 @@ def run_gpu_arm(args, rank, world, local_rank):
     lib.lmg_profile_enable(3 * args.steps + 8)
     sampler = ClockSampler(local_rank)
     sampler.start()
-    ms = timed(step, args.steps)
+    ms = timed(step, args.steps, "resident")
     clocks = sampler.stop()
     launches = lib.lmg_launch_count() - launches0
     kms = (ctypes.c_double * 3)()
@@ -298,7 +309,7 @@ def run_gpu_arm(args, rank, world, local_rank):
 
     for _ in range(2):
         step_e2e()
-    ms_e2e = timed(step_e2e, args.steps)
+    ms_e2e = timed(step_e2e, args.steps, "e2e")
 
     # sanity: the timed kernels did the work (cheap property checks, outside the timed region)
     assert torch.isfinite(ag).all() and float(grid.sum()) > 0
@@ -354,6 +365,7 @@ def run_gpu_arm(args, rank, world, local_rank):
                 "note": "every step uploads its atoms from pinned host memory and downloads its atom "
                         "gradients to pinned host memory; the copies run on a second stream one step ahead "
                         "of the kernels; grids and their gradients stay on the device as in a training loop"},
+        "per_rank": per_rank,
         "gpu_launches": int(launches),
         "clocks": clocks,
     }

@@ -59,6 +59,10 @@ class GridInterpolater {
     float3 c = transform.get_rotation_center();
     forward(c, in, transform, c, out);
   }
+  void forward(const Grid<float, 4, false>& in, Grid<float, 4, false>& out, float random_translation = 0, bool random_rotation = false) const {
+    Transform t(make_float3(0, 0, 0), random_translation, random_rotation);
+    forward(in, t, out);
+  }
 
   // Gradient with respect to forward's input from the gradient with respect to its output, for the
   // same transform and centres (the reference leaves the backward pass open).

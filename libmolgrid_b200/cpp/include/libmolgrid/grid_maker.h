@@ -283,6 +283,98 @@ class GridMaker {
     detail::check(lmg_backward_relevance(&s_, &a, density.data(), diff.data(), relevance.data(), detail::workspace(bytes), bytes, nullptr));
   }
 
+  // ------------------------------------------------------------------ host grids and coordinate sets
+  // The reference's host-grid overloads (include/libmolgrid/grid_maker.h:392-445,463-485,598-612)
+  // run its CPU code; here the arrays are staged through device memory and the GPU path computes.
+  void backward(float3 grid_center, const Grid<float, 2, false>& coords, const Grid<float, 1, false>& type_index,
+                const Grid<float, 1, false>& radii, const Grid<float, 4, false>& diff, Grid<float, 2, false>& atom_gradients) const {
+    detail::Staged<float> c(coords.data(), coords.size(), true, false), t(type_index.data(), type_index.size(), true, false),
+        r(radii.data(), radii.size(), true, false), d(diff.data(), diff.size(), true, false),
+        g(atom_gradients.data(), atom_gradients.size(), false, true);
+    Grid2fCUDA gg(g.get(), atom_gradients.dimension(0), atom_gradients.dimension(1));
+    backward(grid_center, Grid2fCUDA(c.get(), coords.dimension(0), coords.dimension(1)), Grid1fCUDA(t.get(), type_index.size()),
+             Grid1fCUDA(r.get(), radii.size()), dev4(d, diff), gg);
+    g.finish();
+  }
+  void backward(float3 grid_center, const Grid<float, 2, false>& coords, const Grid<float, 2, false>& type_vector,
+                const Grid<float, 1, false>& radii, const Grid<float, 4, false>& diff, Grid<float, 2, false>& atom_gradients,
+                Grid<float, 2, false>& type_gradients) const {
+    detail::Staged<float> c(coords.data(), coords.size(), true, false), t(type_vector.data(), type_vector.size(), true, false),
+        r(radii.data(), radii.size(), true, false), d(diff.data(), diff.size(), true, false),
+        g(atom_gradients.data(), atom_gradients.size(), false, true), tg(type_gradients.data(), type_gradients.size(), false, true);
+    Grid2fCUDA gg(g.get(), atom_gradients.dimension(0), atom_gradients.dimension(1));
+    Grid2fCUDA tgg(tg.get(), type_gradients.dimension(0), type_gradients.dimension(1));
+    backward(grid_center, Grid2fCUDA(c.get(), coords.dimension(0), coords.dimension(1)),
+             Grid2fCUDA(t.get(), type_vector.dimension(0), type_vector.dimension(1)), Grid1fCUDA(r.get(), radii.size()),
+             dev4(d, diff), gg, tgg);
+    g.finish();
+    tg.finish();
+  }
+  void backward_gradients(float3 grid_center, const Grid<float, 2, false>& coords, const Grid<float, 2, false>& type_vector,
+                          const Grid<float, 1, false>& radii, const Grid<float, 4, false>& diff,
+                          const Grid<float, 2, false>& atom_gradients, const Grid<float, 2, false>& type_gradients,
+                          Grid<float, 4, false>& diffdiff, Grid<float, 2, false>& atom_diffdiff, Grid<float, 2, false>& type_diffdiff) {
+    detail::Staged<float> c(coords.data(), coords.size(), true, false), t(type_vector.data(), type_vector.size(), true, false),
+        r(radii.data(), radii.size(), true, false), d(diff.data(), diff.size(), true, false),
+        ag(atom_gradients.data(), atom_gradients.size(), true, false), tg(type_gradients.data(), type_gradients.size(), true, false),
+        dd(diffdiff.data(), diffdiff.size(), false, true), add(atom_diffdiff.data(), atom_diffdiff.size(), false, true),
+        tdd(type_diffdiff.data(), type_diffdiff.size(), false, true);
+    Grid4fCUDA ddg = dev4(dd, diffdiff);
+    Grid2fCUDA addg(add.get(), atom_diffdiff.dimension(0), atom_diffdiff.dimension(1));
+    Grid2fCUDA tddg(tdd.get(), type_diffdiff.dimension(0), type_diffdiff.dimension(1));
+    backward_gradients(grid_center, Grid2fCUDA(c.get(), coords.dimension(0), coords.dimension(1)),
+                       Grid2fCUDA(t.get(), type_vector.dimension(0), type_vector.dimension(1)), Grid1fCUDA(r.get(), radii.size()),
+                       dev4(d, diff), Grid2fCUDA(ag.get(), atom_gradients.dimension(0), atom_gradients.dimension(1)),
+                       Grid2fCUDA(tg.get(), type_gradients.dimension(0), type_gradients.dimension(1)), ddg, addg, tddg);
+    dd.finish();
+    add.finish();
+    tdd.finish();
+  }
+  void backward_relevance(float3 grid_center, const Grid<float, 2, false>& coords, const Grid<float, 1, false>& type_index,
+                          const Grid<float, 1, false>& radii, const Grid<float, 4, false>& density,
+                          const Grid<float, 4, false>& diff, Grid<float, 1, false>& relevance) const {
+    detail::Staged<float> c(coords.data(), coords.size(), true, false), t(type_index.data(), type_index.size(), true, false),
+        r(radii.data(), radii.size(), true, false), de(density.data(), density.size(), true, false),
+        d(diff.data(), diff.size(), true, false), rel(relevance.data(), relevance.size(), false, true);
+    Grid1fCUDA relg(rel.get(), relevance.size());
+    backward_relevance(grid_center, Grid2fCUDA(c.get(), coords.dimension(0), coords.dimension(1)), Grid1fCUDA(t.get(), type_index.size()),
+                       Grid1fCUDA(r.get(), radii.size()), dev4(de, density), dev4(d, diff), relg);
+    rel.finish();
+  }
+
+  // Coordinate sets with host grids (include/libmolgrid/grid_maker.h:131-143,314-350): the set's own
+  // arrays are used on whichever side the result lives
+  void forward(float3 grid_center, const CoordinateSet& in, Grid<float, 4, false>& out) const {
+    if (in.has_vector_types() && in.size() > 0) forward(grid_center, in.coords.cpu(), in.type_vector.cpu(), in.radii.cpu(), out);
+    else if (in.has_indexed_types()) forward(grid_center, in.coords.cpu(), in.type_index.cpu(), in.radii.cpu(), out);
+    else throw std::invalid_argument("Type information missing from coordinate set");
+  }
+  void backward(float3 grid_center, const CoordinateSet& in, const Grid<float, 4, false>& diff, Grid<float, 2, false>& atomic_gradients) const {
+    if (!in.has_indexed_types()) throw std::invalid_argument("Index types missing from coordinate set");
+    backward(grid_center, in.coords.cpu(), in.type_index.cpu(), in.radii.cpu(), diff, atomic_gradients);
+  }
+  void backward(float3 grid_center, const CoordinateSet& in, const Grid<float, 4, false>& diff, Grid<float, 2, false>& atomic_gradients,
+                Grid<float, 2, false>& type_gradients) const {
+    if (!in.has_vector_types()) throw std::invalid_argument("Vector types missing from coordinate set");
+    backward(grid_center, in.coords.cpu(), in.type_vector.cpu(), in.radii.cpu(), diff, atomic_gradients, type_gradients);
+  }
+  // include/libmolgrid/grid_maker.h:508-547
+  template <bool G>
+  void backward_gradients(float3 grid_center, const CoordinateSet& in, const Grid<float, 4, G>& diff,
+                          const Grid<float, 2, G>& atom_gradients, const Grid<float, 2, G>& type_gradients,
+                          Grid<float, 4, G>& diffdiff, Grid<float, 2, G>& atom_diffdiff, Grid<float, 2, G>& type_diffdiff) {
+    if (!in.has_vector_types()) throw std::invalid_argument("Vector types missing from coordinate set");
+    backward_gradients(grid_center, side<G>(in.coords), side<G>(in.type_vector), side<G>(in.radii), diff, atom_gradients,
+                       type_gradients, diffdiff, atom_diffdiff, type_diffdiff);
+  }
+  // include/libmolgrid/grid_maker.h:558-596
+  template <bool G>
+  void backward_relevance(float3 grid_center, const CoordinateSet& in, const Grid<float, 4, G>& density,
+                          const Grid<float, 4, G>& diff, Grid<float, 1, G>& relevance) const {
+    if (!in.has_indexed_types()) throw std::invalid_argument("Index types missing from coordinate set");
+    backward_relevance(grid_center, side<G>(in.coords), side<G>(in.type_index), side<G>(in.radii), density, diff, relevance);
+  }
+
   // Synchronises and throws std::out_of_range / std::invalid_argument if the last call on this
   // thread met a type index >= the number of channels (the reference checks this while looping
   // over atoms on the host, src/grid_maker.cpp:172,458-460).
@@ -291,6 +383,14 @@ class GridMaker {
   }
 
  private:
+  static Grid4fCUDA dev4(const detail::Staged<float>& st, const Grid<float, 4, false>& g) {
+    return Grid4fCUDA(st.get(), g.dimension(0), g.dimension(1), g.dimension(2), g.dimension(3));
+  }
+  // the view of a managed grid on the side (device or host) that G names
+  template <bool G, size_t N>
+  static Grid<float, N, G> side(const ManagedGrid<float, N>& m) {
+    return m;  // ManagedGrid converts to either view, migrating its block
+  }
   static void batch_check(size_t got, size_t B) {
     if (got != B) throw std::invalid_argument("Mismatched batch sizes: " + itoa(got) + " vs " + itoa(B));
   }

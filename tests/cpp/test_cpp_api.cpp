@@ -162,6 +162,20 @@ int main(int argc, char** argv) {
   }
   write_grid(out, dst);
   {
+    // host grids, and the overload that draws its own transform (identity when nothing is random)
+    std::vector<float> hout(ingrid.size(), -1.f), hout2(ingrid.size(), -1.f);
+    Grid4f hin(ingrid.data(), K, D, D, D), ho(hout.data(), K, D, D, D), ho2(hout2.data(), K, D, D, D);
+    gi.forward(hin, t, ho);
+    Grid4f hd = dst.cpu();
+    bool same = true;
+    for (size_t i = 0; i < hout.size(); i++) same = same && hout[i] == hd.data()[i];
+    EXPECT(same);
+    gi.forward(hin, ho2);
+    same = true;
+    for (size_t i = 0; i < hout2.size(); i++) same = same && hout2[i] == ingrid[i];
+    EXPECT(same);
+  }
+  {
     // backward is the adjoint of forward: <forward(src), dst> == <src, backward(dst)>
     MGrid4f back(K, D, D, D);
     Grid4fCUDA gb = back.gpu();
@@ -198,6 +212,90 @@ int main(int argc, char** argv) {
     MGrid4d dgrid(T, D, D, D);
     Grid4dCUDA dg = dgrid.gpu();
     EXPECT_THROW(gm.forward(center, mc.gpu(), mt.gpu(), mr.gpu(), dg), std::invalid_argument);
+  }
+
+  // ---- 10. host-grid overloads of the backward passes agree with the device overloads
+  {
+    auto close = [](const float* a, const float* b, size_t n, float scale) {
+      for (size_t i = 0; i < n; i++) {
+        float d = a[i] - b[i];
+        if ((d < 0 ? -d : d) > 1e-5f * scale + 1e-4f * (a[i] < 0 ? -a[i] : a[i])) return false;
+      }
+      return true;
+    };
+    Grid2f hc(coords.data(), N, 3); Grid1f ht(types.data(), N), hr(radii.data(), N);
+    Grid4f hd(diffv.data(), T, D, D, D);
+    std::vector<float> hagv(N * 3, -1.f);
+    Grid2f hag(hagv.data(), N, 3);
+    gm.backward(center, hc, ht, hr, hd, hag);
+    EXPECT(close(hagv.data(), ag.cpu().data(), hagv.size(), 10.f));
+
+    // index-typed coordinate set, host grids: forward, backward, relevance
+    CoordinateSet cs(rc, types, radii, T);
+    MGrid4f csgrid(T, D, D, D);
+    Grid4f csg = csgrid.cpu();
+    gm.forward(center, cs, csg);
+    {
+      Grid4fCUDA g = grid.gpu();   // section 8 left another case in it
+      gm.forward(center, mc.gpu(), mt.gpu(), mr.gpu(), g);
+    }
+    EXPECT(close(csg.data(), grid.cpu().data(), csg.size(), 1.f));
+    std::vector<float> hag2(N * 3, -1.f);
+    Grid2f hag2g(hag2.data(), N, 3);
+    gm.backward(center, cs, hd, hag2g);
+    EXPECT(close(hag2.data(), hagv.data(), hag2.size(), 10.f));
+    std::vector<float> relh(N, -1.f);
+    Grid1f relhg(relh.data(), N);
+    gm.backward_relevance(center, cs, csg, hd, relhg);
+    MGrid1f reld(N);
+    {
+      Grid1fCUDA g = reld.gpu();
+      gm.backward_relevance(center, mc.gpu(), mt.gpu(), mr.gpu(), grid.gpu(), diff.gpu(), g);
+    }
+    EXPECT(close(relh.data(), reld.cpu().data(), relh.size(), 10.f));
+
+    // vector types: host and device overloads of backward and backward_gradients, arrays and sets
+    std::vector<float> tv((size_t)N * T, 0.f);
+    for (int i = 0; i < N; i++) {
+      tv[(size_t)i * T + ((int)types[i] % T + T) % T] = 0.75f;
+      tv[(size_t)i * T + (i % T)] += 0.25f;
+    }
+    Grid2f htv(tv.data(), N, T);
+    std::vector<float> vag(N * 3), vtg((size_t)N * T);
+    Grid2f vagg(vag.data(), N, 3), vtgg(vtg.data(), N, T);
+    gm.backward(center, hc, htv, hr, hd, vagg, vtgg);
+    MGrid2f mtv(N, T), dag(N, 3), dtg(N, T);
+    std::memcpy(mtv.cpu().data(), tv.data(), tv.size() * 4);
+    {
+      Grid2fCUDA a = dag.gpu(), b = dtg.gpu();
+      gm.backward(center, mc.gpu(), mtv.gpu(), mr.gpu(), diff.gpu(), a, b);
+    }
+    EXPECT(close(vag.data(), dag.cpu().data(), vag.size(), 10.f));
+    EXPECT(close(vtg.data(), dtg.cpu().data(), vtg.size(), 10.f));
+    CoordinateSet vs(hc, htv, hr);
+    EXPECT(vs.has_vector_types() && vs.num_types() == (unsigned)T);
+    std::vector<float> sag(N * 3), stg((size_t)N * T);
+    Grid2f sagg(sag.data(), N, 3), stgg(stg.data(), N, T);
+    gm.backward(center, vs, hd, sagg, stgg);
+    EXPECT(close(sag.data(), vag.data(), sag.size(), 10.f));
+    EXPECT_THROW(gm.backward(center, cs, hd, sagg, stgg), std::invalid_argument);   // no vector types
+
+    std::vector<float> ddh((size_t)T * D * D * D), addh(N * 3), tddh((size_t)N * T, 1.f);
+    Grid4f ddhg(ddh.data(), T, D, D, D);
+    Grid2f addhg(addh.data(), N, 3), tddhg(tddh.data(), N, T);
+    gm.backward_gradients(center, hc, htv, hr, hd, vagg, vtgg, ddhg, addhg, tddhg);
+    MGrid4f ddd(T, D, D, D);
+    MGrid2f addd(N, 3), tddd(N, T);
+    {
+      Grid4fCUDA a = ddd.gpu();
+      Grid2fCUDA b = addd.gpu(), c = tddd.gpu();
+      gm.backward_gradients(center, vs, diff.gpu(), dag.gpu(), dtg.gpu(), a, b, c);
+    }
+    EXPECT(close(ddh.data(), ddd.cpu().data(), ddh.size(), 100.f));
+    EXPECT(close(addh.data(), addd.cpu().data(), addh.size(), 1000.f));
+    bool zero = true;
+    for (float v : tddh) zero = zero && v == 0.f;
+    EXPECT(zero);   // the reference leaves type_diffdiff at zero
   }
 
   // ---- 9. managed grids: shared storage, slices, clone, resize

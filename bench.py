@@ -194,8 +194,10 @@ def run_gpu_arm(args, rank, world, local_rank):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    # each rank grids its own batch of the same statistics: examples are independent, no collective
-    coords, types, radii, ns, tr = cases.blob_batch(SEED + rank, BATCH, NMIN, NMAX, NTYPES)
+    # each rank grids its own batch: examples are independent, no collective.  Atom counts and
+    # per-type radii are those of rank 0's batch on every rank (fixed work per GPU, weak scaling);
+    # coordinates, types and transforms are the rank's own
+    coords, types, radii, ns, tr = cases.blob_batch(SEED + rank, BATCH, NMIN, NMAX, NTYPES, layout_seed=SEED)
     nmax = coords.shape[1]
     g = lmg.GridMaker(RES, DIMENSION)
     gen = torch.Generator(device=dev)
@@ -351,7 +353,8 @@ def run_gpu_arm(args, rank, world, local_rank):
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "batch_per_gpu": BATCH, "global_batch": BATCH * world,
-                   "parallelism": "examples sharded over %d GPU(s), no collective" % world,
+                   "parallelism": "examples sharded over %d GPU(s), no collective; every rank grids its own "
+                                  "coordinates with the atom counts and per-type radii of rank 0's batch" % world,
                    "l2": "inputs larger than L2: each step writes 619 MB of grids and reads 619 MB of gradients"},
         "roofline": roof,
         "roofline_step": {"bound": "hbm", "achieved": step_bytes * world / (ms / args.steps * 1e-3) / 1e9 / world,

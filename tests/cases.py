@@ -45,16 +45,26 @@ def vector_case(seed, n, ntypes, extent, alpha=0.3, rti=False):
     return coords, tv, radii
 
 
-def blob_batch(seed, batch, nmin, nmax, ntypes=28):
+def blob_batch(seed, batch, nmin, nmax, ntypes=28, layout_seed=None):
     """The benchmark's batch: 30% of atoms uniform in a 12 A ball, 70% in a 4 A blob whose centre
-    is uniform in a 6 A ball; per-type radii U[1.2,2.2]; random rotation and +-2 A translation."""
+    is uniform in a 6 A ball; per-type radii U[1.2,2.2]; random rotation and +-2 A translation.
+
+    With ``layout_seed`` the atom counts and the per-type radii come from that seed and only the
+    coordinates, types and transforms from ``seed``: batches of equal size for weak scaling.  A batch
+    whose two seeds are equal is the batch of ``seed`` alone."""
     rng = np.random.default_rng(seed)
     ns = rng.integers(nmin, nmax + 1, batch)
+    if layout_seed is not None:
+        ns = np.random.default_rng(layout_seed).integers(nmin, nmax + 1, batch)
     nmaxa = int(ns.max())
     coords = np.zeros((batch, nmaxa, 3), np.float32)
     types = np.zeros((batch, nmaxa), np.float32)
     radii = np.zeros((batch, nmaxa), np.float32)
     R = rng.uniform(1.2, 2.2, ntypes).astype(np.float32)
+    if layout_seed is not None:
+        lrng = np.random.default_rng(layout_seed)
+        lrng.integers(nmin, nmax + 1, batch)
+        R = lrng.uniform(1.2, 2.2, ntypes).astype(np.float32)
     for b in range(batch):
         n = int(ns[b])
         nblob = int(0.7 * n)

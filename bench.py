@@ -381,7 +381,8 @@ def main():
     global BATCH
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=None,
+                    help="timed steps (default: 1000 on the GPU, 20 for --impl reference)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -392,8 +393,12 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
+        if args.steps is None:
+            args.steps = 20
         run_reference_arm(args, rank)
         return
+    if args.steps is None:
+        args.steps = 1000
     BATCH = args.batch
     run_gpu_arm(args, rank, world, local_rank)
 

@@ -1220,7 +1220,11 @@ __global__ void __launch_bounds__(SCAT_WARPS * 32) k_gradgrad_scatter(BwdArgs G)
 // voxels: the forward adds a quad with one red.global.add.v4.f32, the backward reads it with one
 // 16-byte load, so a warp has 32 columns x 4 quads in flight per round trip to memory instead of
 // 8 columns x 4 voxels.  What depends on z alone sits in a small shared table per warp (one pass
-// covers 32 z positions from the aligned start of the footprint).
+// covers 32 z positions from the aligned start of the footprint).  This lane-per-column layout
+// serves the backward passes and the per-atom vector kernels, which spend their time issuing
+// instructions and amortise the per-column terms over the quads of a column; the forward pass of
+// index types and of (atom, channel) items is bound by the lines its reductions touch and uses
+// the (column, z-quad) layout of qlane_sweep instead.
 // ---------------------------------------------------------------------------------------------
 constexpr int QPASS = 8;  // quads per pass
 
@@ -1246,10 +1250,46 @@ __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, 
                : "memory");
 }
 
+// Sweep over the compacted columns of a footprint with the lanes laid out as (column, z-quad): ZQ
+// lanes along z hold one aligned quad each, 32/ZQ columns per step.  A lane's z terms live in
+// registers for the whole item, and the lanes of a column touch neighbouring 16-byte pieces of one
+// line, so a warp's reduction reaches 32/ZQ rows instead of 32 (the scatter kernels are bound by the
+// number of distinct lines their reductions touch).  `quad(i, dxy2, exy, d2v, ev, dzv, off)` is called
+// by every lane whose quad can hold a voxel of the item: i = column slot, off = row*dim + z of the quad.
+template <int ZQ, class BUF, class QuadFn>
+__device__ __forceinline__ void qlane_sweep(const ItemParams& P, const BUF& buf, unsigned nkept, size_t dim,
+                                            float oz, float res, float kexp, float Tcull, int lane,
+                                            QuadFn quad) {
+  constexpr int CPI = 32 / ZQ;
+  const int zq = lane % ZQ, cl = lane / ZQ;
+  for (unsigned zc = P.loz & ~3u; zc < P.hiz; zc += 4 * ZQ) {
+    float d2v[4], ev[4], dzv[4];
+    float lo = CUDART_INF_F;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      unsigned zz = zc + 4 * zq + j;
+      dzv[j] = __fsub_rn(voxel_coord(oz, zz, res), P.z);
+      bool in = zz >= P.loz && zz < P.hiz;
+      d2v[j] = in ? __fmul_rn(dzv[j], dzv[j]) : CUDART_NAN_F;
+      ev[j] = ex2_approx(d2v[j] * kexp);
+      lo = fminf(lo, d2v[j]);  // fminf skips the NaN entries
+    }
+    const size_t zoff = zc + 4 * zq;
+    for (unsigned c0 = 0; c0 < nkept; c0 += CPI) {
+      unsigned i = c0 + cl;
+      float dxy2 = i < nkept ? buf.dxy2[i] : CUDART_NAN_F;
+      if (!(__fadd_rn(dxy2, lo) <= Tcull)) continue;  // also false for NaN: no column, or no z in range
+      quad(i, dxy2, ex2_approx(dxy2 * kexp), d2v, ev, dzv, (size_t)buf.row[i] * dim + zoff);
+    }
+  }
+}
+
+// number of aligned quads between the first and the last z of a footprint
+__device__ __forceinline__ unsigned quad_span(const ItemParams& P) { return (P.hiz - (P.loz & ~3u) + 3) >> 2; }
+
 // One work item (an atom, or an (atom, channel) pair with VEC) of the forward pass on aligned quads.
 template <bool VEC>
-__device__ __forceinline__ void forward_quads_item(const BwdArgs& G, int item, int bl, ColBuf& buf, ZTabs& zt,
-                                                   int lane) {
+__device__ __forceinline__ void forward_quads_item(const BwdArgs& G, int item, int bl, ColBuf& buf, int lane) {
   const GMParams& gm = G.gm;
   int b = G.b0 + bl;
   if (VEC) {
@@ -1279,34 +1319,22 @@ __device__ __forceinline__ void forward_quads_item(const BwdArgs& G, int item, i
   for (unsigned cbase = 0; cbase < ncols;) {
     unsigned nkept = compact_columns<ColBuf, false>(buf, P, cbase, ncols, ny, inv_ny, P.Tcut, ox, oy,
                                                     gm.res, gm.dim, lane);
-    for (unsigned zc = P.loz & ~3u; zc < P.hiz; zc += 4 * QPASS) {
-      __syncwarp();
-      fill_ztabs(zt, zc, P, oz, gm.res, kexp, lane);
-      __syncwarp();
-      unsigned nq = min((unsigned)QPASS, (P.hiz - zc + 3) >> 2);
-      for (unsigned c0 = 0; c0 < nkept; c0 += 32) {
-        unsigned i = c0 + lane;
-        bool have = i < nkept;
-        float dxy2 = have ? buf.dxy2[i] : CUDART_NAN_F;  // NaN fails every test below
-        float* row = out + (size_t)(have ? buf.row[i] : 0u) * dim + zc;
-        float exy = ex2_approx(dxy2 * kexp);
-        for (unsigned q = 0; q < nq; q++) {
-          float4 d2 = zt.dz2[q], e = zt.ez[q];
-          float d2v[4] = {d2.x, d2.y, d2.z, d2.w}, ev[4] = {e.x, e.y, e.z, e.w}, v[4];
+    __syncwarp();
+    auto quad = [&](unsigned, float dxy2, float exy, const float (&d2v)[4], const float (&ev)[4],
+                    const float (&)[4], size_t off) {
+      float v[4];
 #pragma unroll
-          for (int j = 0; j < 4; j++) {
-            float rsq = __fadd_rn(dxy2, d2v[j]);
-            // tail (ta*dr - tb)^2 clamped to zero beyond the cut-off; a NaN rsq gives zero too
-            float tq = fminf(fmaf(ta, sqrt_approx(rsq * P.inv_ar2), ntb), 0.f);
-            float val = rsq <= P.Tg ? exy * ev[j] : tq * tq;
-            v[j] = VEC ? val * P.w : val;
-          }
-          unsigned any = __float_as_uint(v[0]) | __float_as_uint(v[1]) | __float_as_uint(v[2]) |
-                         __float_as_uint(v[3]);
-          if (any != 0u) red_add_v4(row + 4 * q, v[0], v[1], v[2], v[3]);
-        }
+      for (int j = 0; j < 4; j++) {
+        float rsq = __fadd_rn(dxy2, d2v[j]);
+        // tail (ta*dr - tb)^2 clamped to zero beyond the cut-off; a NaN rsq gives zero too
+        float tq = fminf(fmaf(ta, sqrt_approx(rsq * P.inv_ar2), ntb), 0.f);
+        float val = rsq <= P.Tg ? exy * ev[j] : tq * tq;
+        v[j] = VEC ? val * P.w : val;
       }
-    }
+      red_add_v4(out + off, v[0], v[1], v[2], v[3]);
+    };
+    if (quad_span(P) <= 4) qlane_sweep<4>(P, buf, nkept, dim, oz, gm.res, kexp, P.Tcut, lane, quad);
+    else qlane_sweep<8>(P, buf, nkept, dim, oz, gm.res, kexp, P.Tcut, lane, quad);
     __syncwarp();
   }
 }
@@ -1314,11 +1342,10 @@ __device__ __forceinline__ void forward_quads_item(const BwdArgs& G, int item, i
 template <bool VEC>
 __global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads(BwdArgs G) {
   __shared__ ColBuf bufs[SCAT_WARPS];
-  __shared__ ZTabs ztabs[SCAT_WARPS];
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   int item = blockIdx.x * SCAT_WARPS + wid;
   if (item >= (VEC ? G.N * G.T : G.N)) return;
-  forward_quads_item<VEC>(G, item, blockIdx.y, bufs[wid], ztabs[wid], lane);
+  forward_quads_item<VEC>(G, item, blockIdx.y, bufs[wid], lane);
 }
 
 // Vector types whose radii differ by channel: one warp takes a group of NZ_GROUP consecutive channels
@@ -1329,8 +1356,8 @@ constexpr int NZ_GROUP = 8;
 __host__ __device__ inline int nz_groups(int T) { return (T + NZ_GROUP - 1) / NZ_GROUP; }
 
 #define LMG_FOR_EACH_WEIGHTED_CHANNEL(G, b, unit, lane, atom, t)                                        \
-  if (int atom = (unit) / nz_groups((G).T); true)                                                       \
-    if (int t0_ = ((unit) - atom * nz_groups((G).T)) * NZ_GROUP; true)                                  \
+  if (int atom = (unit) % (G).N; true)                                                                  \
+    if (int t0_ = ((unit) / (G).N) * NZ_GROUP; true)                                                    \
       for (unsigned m_ = __ballot_sync(                                                                 \
                0xffffffffu, (lane) < NZ_GROUP && t0_ + (lane) < (G).T &&                                \
                                 (G).type_vector[((size_t)(b) * (G).N + atom) * (G).T + t0_ + (lane)] != 0.f); \
@@ -1339,13 +1366,12 @@ __host__ __device__ inline int nz_groups(int T) { return (T + NZ_GROUP - 1) / NZ
 
 __global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads_nz(BwdArgs G) {
   __shared__ ColBuf bufs[SCAT_WARPS];
-  __shared__ ZTabs ztabs[SCAT_WARPS];
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   int unit = blockIdx.x * SCAT_WARPS + wid;
   if (unit >= G.N * nz_groups(G.T)) return;
   int b = G.b0 + blockIdx.y;
   LMG_FOR_EACH_WEIGHTED_CHANNEL(G, b, unit, lane, atom, t) {
-    forward_quads_item<true>(G, atom * G.T + t, blockIdx.y, bufs[wid], ztabs[wid], lane);
+    forward_quads_item<true>(G, atom * G.T + t, blockIdx.y, bufs[wid], lane);
     __syncwarp();
   }
 }

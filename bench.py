@@ -42,9 +42,9 @@ WORKLOAD = ("batch 50 x [2000,4000] index-typed atoms (70% in a 4A blob), 28x48^
             "forward with fused per-example rotation+translation, then backward with N(0,1) grid gradient")
 # dram bytes per example from the ncu captures summarised under profiles/ (batch 12, scaled per
 # example: every example's grids are separate and larger than what L2 keeps, so traffic grows in
-# proportion).  forward = the fill's own 12,386,304 B + the scatter kernel's 6.46 MB of read-modify-
+# proportion).  forward = the fill's own 12,386,304 B + the scatter kernel's 6.40 MB of read-modify-
 # write on the sectors atoms touch; backward = the touched part of the grid gradient.
-NCU_TRAFFIC_PER_EXAMPLE = {"forward": 12386304 + 6.46e6, "backward": 6.85e6}
+NCU_TRAFFIC_PER_EXAMPLE = {"forward": 12386304 + 6.40e6, "backward": 6.85e6}
 
 
 # ------------------------------------------------------------------------------------------------

@@ -1,16 +1,22 @@
-// sm_100a kernels for GridMaker forward / backward / backward_relevance.
+// sm_100a kernels for GridMaker forward / backward / backward_gradients / backward_relevance.
 //
-// Pipeline of one forward pass over a batch:
-//   emit   : one thread per atom - fused Transform, exact footprint bounds and distance thresholds
-//            -> 64-byte atom record; counts the atom into every voxel region its footprint touches
+// Every pass starts with emit: one thread per atom - fused Transform, exact footprint bounds and
+// distance thresholds -> 64-byte atom record.
+//
+// Default forward: the output is zero-filled, then one warp per atom (per (atom, channel) with vector
+// types) compacts the columns of the atom's footprint that lie inside the cut-off circle and adds
+// the density into the grid with red.global.add (k_forward_quads*, k_forward_scatter).
+// Backward passes: one warp per atom reads the grid gradient under the footprint and reduces with
+// shuffles, so no global atomics are needed (k_backward_quads*, k_backward_warp).
+//
+// Alternative gather forward (forward mode 0, and the grid term of backward_gradients on grids that
+// are not 16-byte aligned): emit also counts the atom into every voxel region its footprint touches;
 //   scan   : per-example exclusive scan of the (region, channel) counts
 //   fill   : writes atom indices into per-(region, channel) lists
 //   forward: one warp per 4x8x4-voxel region; per channel the warp turns its list into a per-lane
 //            bit mask of atoms whose footprint crosses the lane's z-column, then every lane walks
 //            its own mask and accumulates 4 voxels in registers; each output voxel is written
 //            exactly once with a 16-byte store (no memset, no read-modify-write of the grid).
-// Backward passes read the atom records directly: one warp per atom sweeps the footprint (four
-// lanes along z, eight columns at a time) and reduces with shuffles, so no global atomics are needed.
 #include "lmg_device.cuh"
 #include "lmg_launch.h"
 

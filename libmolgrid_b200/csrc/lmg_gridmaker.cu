@@ -9,8 +9,8 @@
 // Backward passes: one warp per atom reads the grid gradient under the footprint and reduces with
 // shuffles, so no global atomics are needed (k_backward_quads*, k_backward_warp).
 //
-// Alternative gather forward (forward mode 0, and the grid term of backward_gradients on grids that
-// are not 16-byte aligned): emit also counts the atom into every voxel region its footprint touches;
+// Alternative gather forward (forward mode 0, also for the grid term of backward_gradients in that
+// mode): emit also counts the atom into every voxel region its footprint touches;
 //   scan   : per-example exclusive scan of the (region, channel) counts
 //   fill   : writes atom indices into per-(region, channel) lists
 //   forward: one warp per 4x8x4-voxel region; per channel the warp turns its list into a per-lane

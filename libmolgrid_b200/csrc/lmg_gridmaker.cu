@@ -1687,6 +1687,7 @@ __global__ void __launch_bounds__(SCAT_WARPS * 32) k_gradgrad_quads_nz(BwdArgs G
 // one work item per (atom, channel).  Channels are handled in rounds of VA_CH.
 // ---------------------------------------------------------------------------------------------
 constexpr int VA_CH = 32;  // channels per round
+constexpr int VA_SPARSE = 2;  // rounds with at most this many weighted channels sweep once per channel
 
 template <bool BINARY, bool PRECISE>
 __global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads_atom(BwdArgs G) {
@@ -1741,6 +1742,30 @@ __global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads_atom(BwdArgs 
     for (unsigned cbase = 0; cbase < ncols;) {
       unsigned nkept = compact_columns<ColBuf, false>(buf, P, cbase, ncols, ny, inv_ny, Tcull, ox, oy,
                                                       gm.res, gm.dim, lane);
+      if (!BINARY && !PRECISE && nnz <= VA_SPARSE) {
+        // few weighted channels (one-hot types): one sweep per channel in the lane layout of the
+        // index-typed forward, whose reductions touch a quarter of the rows
+        __syncwarp();
+        for (int k = 0; k < nnz; k++) {
+          float* out = outb + (size_t)nz_t[wid][k] * chan_stride;
+          const float wk = nz_w[wid][k];
+          auto quad = [&](unsigned, float dxy2, float exy, const float (&d2v)[4], const float (&ev)[4],
+                          const float (&)[4], size_t off) {
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              float rsq = __fadd_rn(dxy2, d2v[j]);
+              float tq = fminf(fmaf(ta, sqrt_approx(rsq * P.inv_ar2), ntb), 0.f);
+              v[j] = (rsq <= P.Tg ? exy * ev[j] : tq * tq) * wk;
+            }
+            red_add_v4(out + off, v[0], v[1], v[2], v[3]);
+          };
+          if (quad_span(P) <= 4) qlane_sweep<4>(P, buf, nkept, dim, oz, gm.res, kexp, Tcull, lane, quad);
+          else qlane_sweep<8>(P, buf, nkept, dim, oz, gm.res, kexp, Tcull, lane, quad);
+        }
+        __syncwarp();
+        continue;
+      }
       for (unsigned zc = P.loz & ~3u; zc < P.hiz; zc += 4 * QPASS) {
         __syncwarp();
         fill_ztabs(zt, zc, P, oz, gm.res, kexp, lane);

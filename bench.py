@@ -28,7 +28,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-from tests import cases  # noqa: E402
+from libmolgrid_b200 import synthetic as cases  # noqa: E402
 
 BATCH = 50
 NTYPES = 28

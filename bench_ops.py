@@ -28,7 +28,7 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
-from tests import cases  # noqa: E402
+from libmolgrid_b200 import synthetic as cases  # noqa: E402
 
 T = 28
 

@@ -160,10 +160,16 @@ int lmg_backward_relevance(const lmg_gridmaker* g, const lmg_atoms* atoms, const
  *    the caller.
  *  - The first call on each device resolves the array's device address; make it outside any stream
  *    capture.
- * Results are those of lmg_backward. */
+ *  - A type index >= ntypes is not an error of the call itself (the data lives on the device): the
+ *    atom's gradient stays zero and a status word is set in the fixed array.
+ *    lmg_static_check_status(stream) waits for the stream, reads that word (a 4-byte copy, nothing
+ *    allocated) and returns LMG_ERR_INVALID_ARGUMENT for it, as lmg_check_status does for
+ *    lmg_backward.  It reports the last lmg_backward_static call on the current device.
+ * Results are those of lmg_backward, bit for bit (the same kernels run). */
 int lmg_backward_static(const lmg_gridmaker* g, const lmg_atoms* atoms, const float* diff,
                         float* atom_gradients, void* stream);
 size_t lmg_static_max_atoms(void);
+int lmg_static_check_status(void* stream);
 
 /* out[n][3] = transform applied to in[n][3]; in-place is allowed; `t` is a host struct.
  * dotranslate == 0 rotates about the centre only.

@@ -75,6 +75,7 @@ SYMBOLS = [
     ("lmg_backward_relevance", ctypes.c_int, [_GM, _AT, _VP, _VP, _VP, _VP, ctypes.c_size_t, _VP]),
     ("lmg_backward_static", ctypes.c_int, [_GM, _AT, _VP, _VP, _VP]),
     ("lmg_static_max_atoms", ctypes.c_size_t, []),
+    ("lmg_static_check_status", ctypes.c_int, [_VP]),
     ("lmg_transform_forward", ctypes.c_int, [_TR, ctypes.c_int, _VP, _VP, ctypes.c_int, _VP]),
     ("lmg_transform_backward", ctypes.c_int, [_TR, ctypes.c_int, _VP, _VP, ctypes.c_int, _VP]),
     ("lmg_interpolater_init", ctypes.c_int, [_GI, ctypes.c_float, ctypes.c_float, ctypes.c_float,

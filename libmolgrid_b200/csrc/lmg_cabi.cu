@@ -78,8 +78,12 @@ bool make_input_map(CUtensorMap* map, const float* in, unsigned dim, size_t ncha
   return r == CUDA_SUCCESS;
 }
 
-lmg::GMParams to_params(const lmg_gridmaker* g) {
-  lmg::GMParams p;
+}  // namespace
+
+namespace lmg {
+
+GMParams to_params(const lmg_gridmaker* g) {
+  GMParams p;
   p.res = g->resolution;
   p.half = (float)(g->dimension / 2.0);  // src/grid_maker.cpp:101
   p.rscale = g->radius_scale;
@@ -98,12 +102,43 @@ lmg::GMParams to_params(const lmg_gridmaker* g) {
   return p;
 }
 
-lmg::Xform to_xform(const lmg_transform* t) {
-  lmg::Xform X;
+Xform to_xform(const lmg_transform* t) {
+  Xform X;
   for (int i = 0; i < 4; i++) X.q[i] = t->q[i];
   for (int i = 0; i < 3; i++) { X.c[i] = t->center[i]; X.t[i] = t->translate[i]; }
   return X;
 }
+
+void fill_emit(EmitArgs& E, const lmg_gridmaker* g, const lmg_atoms* a) {
+  std::memset(&E, 0, sizeof E);
+  E.gm = to_params(g);
+  E.N = a->max_atoms;
+  E.T = a->ntypes;
+  E.vec = a->type_vector != nullptr;
+  E.n_atoms = a->n_atoms;
+  E.coords = a->coords;
+  E.type_index = a->type_index;
+  E.type_vector = a->type_vector;
+  E.radii = a->radii;
+  E.centers = a->centers;
+  for (int i = 0; i < 3; i++) E.center_host[i] = a->center_host[i];
+  E.transforms = reinterpret_cast<const Xform*>(a->transforms);
+  if (a->transforms == nullptr && a->transform_host != nullptr) {
+    E.xform_host = to_xform(a->transform_host);
+    E.has_xform_host = 1;
+  }
+  E.check_types = 1;
+}
+
+int quads_setting() { return g_quads; }
+
+}  // namespace lmg
+
+namespace {
+
+using lmg::fill_emit;
+using lmg::to_params;
+using lmg::to_xform;
 
 int regions_touched(int nvox, int s) { return (nvox + s - 2) / s + 1; }
 
@@ -181,27 +216,6 @@ int check_common(const lmg_gridmaker* g, const lmg_atoms* a, const void* ws) {
     return fail(LMG_ERR_INVALID_ARGUMENT, "Type indexed radii not supported with index types.");
   if (ws == nullptr) return fail(LMG_ERR_WORKSPACE, "workspace missing");
   return LMG_OK;
-}
-
-void fill_emit(lmg::EmitArgs& E, const lmg_gridmaker* g, const lmg_atoms* a) {
-  std::memset(&E, 0, sizeof E);
-  E.gm = to_params(g);
-  E.N = a->max_atoms;
-  E.T = a->ntypes;
-  E.vec = a->type_vector != nullptr;
-  E.n_atoms = a->n_atoms;
-  E.coords = a->coords;
-  E.type_index = a->type_index;
-  E.type_vector = a->type_vector;
-  E.radii = a->radii;
-  E.centers = a->centers;
-  for (int i = 0; i < 3; i++) E.center_host[i] = a->center_host[i];
-  E.transforms = reinterpret_cast<const lmg::Xform*>(a->transforms);
-  if (a->transforms == nullptr && a->transform_host != nullptr) {
-    E.xform_host = to_xform(a->transform_host);
-    E.has_xform_host = 1;
-  }
-  E.check_types = 1;
 }
 
 void carve(lmg::EmitArgs& E, const Layout& L, char* ws, int nb) {

@@ -88,3 +88,15 @@ cudaError_t launch_forward_scatter(const BwdArgs& G, bool vec, cudaStream_t st);
 cudaError_t launch_gradgrad_scatter(const BwdArgs& G, cudaStream_t st);
 
 }  // namespace lmg
+
+// Host-side helpers shared by the entry points (defined with the C ABI).
+struct lmg_gridmaker;
+struct lmg_atoms;
+struct lmg_transform;
+namespace lmg {
+GMParams to_params(const lmg_gridmaker* g);
+Xform to_xform(const lmg_transform* t);
+// input side of a pass: settings, sizes, the caller's arrays, per-example or single transform
+void fill_emit(EmitArgs& E, const lmg_gridmaker* g, const lmg_atoms* a);
+int quads_setting();  // current value of the aligned-quad kernel switch
+}  // namespace lmg

@@ -17,6 +17,9 @@
 //     calls issued one after another on the same stream are independent; calls that can overlap on
 //     the GPU (different streams, different host threads) race on it and must be serialised by the
 //     caller.
+//   * A type index >= ntypes leaves that atom's gradient at zero and sets a status word in the
+//     array; lmg_static_check_status(stream) reads it back (the counterpart of lmg_check_status,
+//     which needs a workspace pointer this path does not have).
 //   * The first call on each device looks up the array's device address (cudaGetSymbolAddress).
 //     Make that first call outside any stream capture; later calls only launch work.
 //   * Nothing here calls cudaMalloc, cudaFree or any other allocating routine.
@@ -100,41 +103,11 @@ int lmg_backward_static(const lmg_gridmaker* g, const lmg_atoms* a, const float*
   cudaError_t e = cudaMemsetAsync(ws, 0, STATIC_STATUS_BYTES, st);
   if (e != cudaSuccess) return fail(LMG_ERR_CUDA, std::string("CUDA Error: ") + cudaGetErrorString(e));
 
-  lmg::GMParams p;
-  p.res = g->resolution;
-  p.half = (float)(g->dimension / 2.0);
-  p.rscale = g->radius_scale;
-  p.G = g->gaussian_radius_multiple;
-  p.finalm = g->final_radius_multiple;
-  p.A = g->A; p.B = g->B; p.C = g->C; p.D = g->D; p.E = g->E;
-  {
-    double G = g->gaussian_radius_multiple, eg = std::exp(-G * G);
-    bool truncated = g->final_radius_multiple == g->gaussian_radius_multiple;
-    p.ta = truncated ? 0.f : (float)(2.0 * G * eg);
-    p.tb = truncated ? 0.f : (float)((1.0 + 2.0 * G * G) * eg);
-  }
-  p.dim = g->dim;
-  p.binary = g->binary;
-  p.rti = 0;
-
   lmg::EmitArgs E;
-  std::memset(&E, 0, sizeof E);
-  E.gm = p;
-  E.b0 = 0; E.nb = a->batch; E.N = a->max_atoms; E.T = a->ntypes;
-  E.vec = 0; E.round_types = 1; E.check_types = 1;
-  E.n_atoms = a->n_atoms;
-  E.coords = a->coords; E.type_index = a->type_index; E.radii = a->radii;
-  E.centers = a->centers;
-  for (int i = 0; i < 3; i++) E.center_host[i] = a->center_host[i];
-  E.transforms = reinterpret_cast<const lmg::Xform*>(a->transforms);
-  if (a->transforms == nullptr && a->transform_host != nullptr) {
-    for (int i = 0; i < 4; i++) E.xform_host.q[i] = a->transform_host->q[i];
-    for (int i = 0; i < 3; i++) {
-      E.xform_host.c[i] = a->transform_host->center[i];
-      E.xform_host.t[i] = a->transform_host->translate[i];
-    }
-    E.has_xform_host = 1;
-  }
+  lmg::fill_emit(E, g, a);
+  E.gm.rti = 0;
+  E.b0 = 0; E.nb = a->batch;
+  E.round_types = 1;
   E.status = reinterpret_cast<int*>(ws);
   E.recs = reinterpret_cast<lmg::Rec*>(ws + STATIC_STATUS_BYTES);
   E.cnt = nullptr;  // no region lists are needed by the backward kernel
@@ -143,16 +116,32 @@ int lmg_backward_static(const lmg_gridmaker* g, const lmg_atoms* a, const float*
 
   lmg::BwdArgs B;
   std::memset(&B, 0, sizeof B);
-  B.gm = p;
+  B.gm = E.gm;
   B.b0 = 0; B.nb = a->batch; B.N = a->max_atoms; B.T = a->ntypes;
   B.centers = a->centers;
   for (int i = 0; i < 3; i++) B.center_host[i] = a->center_host[i];
   B.recs = E.recs;
   B.diff = diff;
   B.atom_gradients = atom_gradients;
-  B.quads = 1;  // the aligned-quad kernel where the grid allows it (the launcher checks)
+  B.quads = lmg::quads_setting();  // the aligned-quad kernel where the grid allows it (the launcher checks)
   e = lmg::launch_backward(B, 0, st);
   if (e != cudaSuccess) return fail(LMG_ERR_CUDA, std::string("CUDA Error: backward: ") + cudaGetErrorString(e));
+  return LMG_OK;
+}
+
+// The data-dependent check of lmg_backward (a type index >= ntypes) for the static entry point:
+// reads the status word that the last lmg_backward_static call on this device and stream left in
+// the fixed array.  A 4-byte device-to-host copy and a stream synchronisation; allocates nothing.
+int lmg_static_check_status(void* stream) {
+  char* ws = nullptr;
+  int rc = scratch_for_current_device(&ws);
+  if (rc != LMG_OK) return rc;
+  int st = 0;
+  cudaError_t e = cudaMemcpyAsync(&st, ws, sizeof st, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(LMG_ERR_CUDA, std::string("CUDA Error: reading status: ") + cudaGetErrorString(e));
+  if (st == 1) return fail(LMG_ERR_OUT_OF_RANGE, "Type index larger than allowed");
+  if (st == 2) return fail(LMG_ERR_INVALID_ARGUMENT, "Incorrect channel size for diff");
   return LMG_OK;
 }
 

@@ -1,7 +1,8 @@
 """lmg_backward_static: the backward pass for hosts that cannot allocate device memory.
 
 Called through the C ABI directly (ctypes), twice in a row, and compared with lmg_backward, the
-entry point that takes a caller-provided workspace.  Kept in a file that pytest collects last so
+entry point that takes a caller-provided workspace (the same kernels run, so bit for bit), and with
+the CPU checker.  Kept in a file that pytest collects last so
 that a run stopping at the first failure has already exercised everything else.
 """
 import ctypes
@@ -24,7 +25,7 @@ def _atoms(coords, types, radii, center, T):
     return a
 
 
-def test_static_backward_matches_workspace_backward(lib):
+def test_static_backward_matches_workspace_backward(lib, port):
     from libmolgrid_b200 import _cabi
     torch.cuda.set_device(0)
     s = _cabi.GridMakerStruct()
@@ -53,10 +54,44 @@ def test_static_backward_matches_workspace_backward(lib):
         rc = lib.lmg_backward_static(ctypes.byref(s), ctypes.byref(a), diff.data_ptr(), got.data_ptr(), stream)
         assert rc == 0, lib.lmg_last_error()
         torch.cuda.synchronize()
+        assert lib.lmg_static_check_status(stream) == 0, lib.lmg_last_error()
+        assert torch.equal(got, want)
         w, g = want.cpu().numpy(), got.cpu().numpy()
-        scale = max(1.0, float(np.abs(w).max()))
-        assert np.allclose(g, w, rtol=1e-4, atol=1e-5 * scale), np.abs(g - w).max()
         assert np.abs(w).max() > 0.1
+        og = port.gm(0.5, 11.5)
+        dh = diff.cpu().numpy()
+        for b in range(B):
+            ref = port.backward_index(og, center, data[b][0], data[b][1], data[b][2], dh[b])
+            scale = max(1.0, float(np.abs(ref).max()))
+            assert np.allclose(g[b], ref, rtol=1e-4, atol=1e-5 * scale), np.abs(g[b] - ref).max()
+
+
+def test_static_backward_reports_out_of_range_types(lib):
+    """A type index >= ntypes is dropped by the kernel and reported by lmg_static_check_status,
+    as lmg_check_status does for the workspace entry point; the next clean call reports nothing."""
+    from libmolgrid_b200 import _cabi
+    torch.cuda.set_device(0)
+    s = _cabi.GridMakerStruct()
+    assert lib.lmg_gridmaker_init(ctypes.byref(s), 0.5, 5.5, 0, 0, 1.0, 1.0) == 0
+    T, N, d = 3, 8, int(s.dim)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    coords = torch.zeros((1, N, 3), device="cuda")
+    radii = torch.ones((1, N), device="cuda")
+    diff = torch.ones((1, T, d, d, d), device="cuda")
+    for bad in (True, False):
+        types = torch.zeros((1, N), device="cuda")
+        if bad:
+            types[0, 3] = float(T)
+        a = _atoms(coords, types, radii, (0, 0, 0), T)
+        got = torch.full((1, N, 3), -7.0, device="cuda")
+        rc = lib.lmg_backward_static(ctypes.byref(s), ctypes.byref(a), diff.data_ptr(), got.data_ptr(), stream)
+        assert rc == 0, lib.lmg_last_error()
+        rc = lib.lmg_static_check_status(stream)
+        if bad:
+            assert rc == _cabi.LMG_ERR_INVALID_ARGUMENT, rc
+            assert float(got[0, 3].abs().sum()) == 0.0
+        else:
+            assert rc == 0, lib.lmg_last_error()
 
 
 def test_static_backward_refuses_oversized_batches(lib):

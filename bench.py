@@ -38,8 +38,10 @@ DIM = 48
 GRID_BYTES = NTYPES * DIM ** 3 * 4          # 12,386,304
 SEED = 1001
 METRIC = "examples/s gridded (28x48^3 fp32) fwd+bwd"
-WORKLOAD = ("batch 50 x [2000,4000] index-typed atoms (70% in a 4A blob), 28x48^3 @0.5A, "
+WORKLOAD = ("batch 50 per GPU x [2000,4000] index-typed atoms (70% in a 4A blob), 28x48^3 @0.5A, "
             "forward with fused per-example rotation+translation, then backward with N(0,1) grid gradient")
+WORKLOAD_C4A = ("one batch of 1024 x [2000,4000] index-typed atoms (70% in a 4A blob), 28x48^3 @0.5A, cut by "
+                "example over the GPUs; forward with fused rotation+translation, then backward")
 # dram bytes per example from the ncu captures summarised under profiles/ (batch 12, scaled per
 # example: every example's grids are separate and larger than what L2 keeps, so traffic grows in
 # proportion).  forward = the fill's own 12,386,304 B + the scatter kernel's 6.40 MB of read-modify-
@@ -91,6 +93,9 @@ def run_reference_arm(args, rank):
     if rank != 0:
         return
     kind = _cpu_kind()
+    # the parent loads the checker library and grids one small example itself, so that the library
+    # shows among the files this process has mapped; the timed work runs in forked workers
+    _cpu_worker((kind, SEED + 5, 1))
     cores = os.cpu_count() or 1
     per_core = 1
     times = []
@@ -171,6 +176,22 @@ def measured_peak():
         return 6650.0, "fallback"
 
 
+def make_workload(args, rank, world):
+    """The rank's slice of the global batch, cut by example with the sharding helper.
+
+    headline: 50 examples per GPU (global batch 50 x world, weak scaling); c4a: ONE batch of 1024
+    (strong scaling).  Every example has its own atom count; the cut balances atoms, so ranks hold
+    slightly different numbers of examples."""
+    from libmolgrid_b200.sharding import shard_bounds
+    global_batch = 1024 if args.config == "c4a" else args.batch * world
+    seed = 1004 if args.config == "c4a" else SEED
+    counts = cases.blob_counts(seed, global_batch, NMIN, NMAX)
+    R = cases.type_radii(seed, NTYPES)
+    bounds = shard_bounds(counts, world, per_example_cost=args.example_cost)
+    start, end = bounds[rank]
+    return cases.blob_slice(seed, start, end, counts, R), global_batch, bounds
+
+
 def run_gpu_arm(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -194,10 +215,9 @@ def run_gpu_arm(args, rank, world, local_rank):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    # each rank grids its own batch: examples are independent, no collective.  Atom counts and
-    # per-type radii are those of rank 0's batch on every rank (fixed work per GPU, weak scaling);
-    # coordinates, types and transforms are the rank's own
-    coords, types, radii, ns, tr = cases.blob_batch(SEED + rank, BATCH, NMIN, NMAX, NTYPES, layout_seed=SEED)
+    # examples are independent: every rank grids its own slice of the global batch, no collective
+    (coords, types, radii, ns, tr), global_batch, bounds = make_workload(args, rank, world)
+    nex = coords.shape[0]
     nmax = coords.shape[1]
     g = lmg.GridMaker(RES, DIMENSION)
     gen = torch.Generator(device=dev)
@@ -207,10 +227,10 @@ def run_gpu_arm(args, rank, world, local_rank):
         return torch.from_numpy(a).to(dev)
 
     dc, dt, dr, dtr, dn = d(coords), d(types), d(radii), d(tr), d(ns)
-    cen = torch.zeros((BATCH, 3), device=dev)
-    grid = torch.empty((BATCH,) + g.grid_dimensions(NTYPES), device=dev)
+    cen = torch.zeros((nex, 3), device=dev)
+    grid = torch.empty((nex,) + g.grid_dimensions(NTYPES), device=dev)
     diff = torch.randn(grid.shape, device=dev, generator=gen)
-    ag = torch.empty((BATCH, nmax, 3), device=dev)
+    ag = torch.empty((nex, nmax, 3), device=dev)
 
     def step():
         g.forward(cen, dc, dt, dr, grid, transforms=dtr, n_atoms=dn)
@@ -221,8 +241,8 @@ def run_gpu_arm(args, rank, world, local_rank):
     # ahead of the kernels (two sets of device input buffers); the kernels of step i wait on the
     # upload of step i, the download of step i waits on its backward kernel.
     hc, ht, hr, htr = (torch.from_numpy(x).pin_memory() for x in (coords, types, radii, tr))
-    hcen = torch.zeros((BATCH, 3)).pin_memory()
-    hag = [torch.empty((BATCH, nmax, 3)).pin_memory() for _ in range(2)]
+    hcen = torch.zeros((nex, 3)).pin_memory()
+    hag = [torch.empty((nex, nmax, 3)).pin_memory() for _ in range(2)]
     host_in = (hc, ht, hr, htr, hcen)
     h2d = sum(x.numel() * x.element_size() for x in host_in)
     d2h = hag[0].numel() * hag[0].element_size()
@@ -262,6 +282,15 @@ def run_gpu_arm(args, rank, world, local_rank):
             downloaded[slot].record(copy_stream)
         e2e_state["i"] = i + 1
 
+    # The same step with the host buffers handed straight to the API: the call stages them itself
+    # (host-to-device copies of the atoms, device-to-host copy of the gradients) on the calling
+    # stream, nothing overlapped.
+    htr_rows = htr
+
+    def step_host_api():
+        g.forward(hcen, hc, ht, hr, grid, transforms=htr_rows, n_atoms=dn)
+        g.backward(hcen, hc, ht, hr, diff, hag[0], transforms=htr_rows, n_atoms=dn)
+
     def barrier():
         if world > 1:
             dist.barrier()
@@ -281,7 +310,7 @@ def run_gpu_arm(args, rank, world, local_rank):
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
-        mine = torch.tensor([ms, host_ms, float(ns.sum())], device=dev, dtype=torch.float64)
+        mine = torch.tensor([ms, host_ms, float(ns.sum()), float(nex)], device=dev, dtype=torch.float64)
         if world > 1:
             every = [torch.empty_like(mine) for _ in range(world)]
             dist.all_gather(every, mine)
@@ -291,19 +320,25 @@ def run_gpu_arm(args, rank, world, local_rank):
         else:
             every = [mine]
         per_rank[tag] = [{"device_ms": round(float(x[0]), 3), "host_issue_ms": round(float(x[1]), 3),
-                          "atoms": int(x[2])} for x in every]
+                          "atoms": int(x[2]), "examples": int(x[3])} for x in every]
         return ms
 
-    for _ in range(max(args.warmup, 3)):
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
         step()
     lib = _cabi.lib()
+    lib.lmg_profile_enable(0)
     launches0 = lib.lmg_launch_count()
-    lib.lmg_profile_enable(3 * args.steps + 8)
     sampler = ClockSampler(local_rank)
     sampler.start()
-    ms = timed(step, args.steps, "resident")
+    ms = timed(step, args.steps, "resident")       # the headline: no timing hooks inside the library
     clocks = sampler.stop()
     launches = lib.lmg_launch_count() - launches0
+
+    # per-kernel durations in a pass of their own (CUDA events around each launch, on its stream)
+    ksteps = min(args.steps, 200)
+    lib.lmg_profile_enable(4 * ksteps + 8)
+    timed(step, ksteps, "kernels")
     kms = (ctypes.c_double * 3)()
     kcount = (ctypes.c_int * 3)()
     lib.lmg_profile_collect(kms, kcount)
@@ -312,6 +347,10 @@ def run_gpu_arm(args, rank, world, local_rank):
     for _ in range(2):
         step_e2e()
     ms_e2e = timed(step_e2e, args.steps, "e2e")
+    hsteps = min(args.steps, 50)
+    for _ in range(2):
+        step_host_api()
+    ms_host = timed(step_host_api, hsteps, "host_api")
 
     # sanity: the timed kernels did the work (cheap property checks, outside the timed region)
     assert torch.isfinite(ag).all() and float(grid.sum()) > 0
@@ -320,45 +359,48 @@ def run_gpu_arm(args, rank, world, local_rank):
         if world > 1:
             dist.destroy_process_group()
         return
-    total_examples = BATCH * world * args.steps
+    total_examples = global_batch * args.steps
     value = total_examples / (ms * 1e-3)
     peak, peak_kind = measured_peak()
     natoms = float(ns.sum())
-    fwd_bytes = BATCH * GRID_BYTES + 20.0 * natoms           # write grid once + read atoms
-    bwd_bytes = BATCH * GRID_BYTES + 32.0 * natoms           # read diff once + read atoms + write gradients
+    fwd_bytes = nex * GRID_BYTES + 20.0 * natoms           # write grid once + read atoms
+    bwd_bytes = nex * GRID_BYTES + 32.0 * natoms           # read diff once + read atoms + write gradients
     kern = []
     # the forward pass is a zero fill of the grids plus the scatter kernel that adds the densities
     # into them; its algorithmic bytes (one write of every grid) are charged to the pair
     fill_ms = kms[2] / kcount[2] if kcount[2] else 0.0
-    for k, name, nbytes in ((0, "forward (zero fill + k_forward_quads)", fwd_bytes),
-                            (1, "backward (k_backward_quads)", bwd_bytes)):
+    for k, name, nbytes in ((0, "forward (zero fill + k_emit + k_forward_quads)", fwd_bytes),
+                            (1, "backward (k_emit + k_backward_quads)", bwd_bytes)):
         if kcount[k]:
             avg_ms = kms[k] / kcount[k] + (fill_ms if k == 0 else 0.0)
             kern.append({"kernel": name, "launches": int(kcount[k]), "avg_ms": avg_ms,
                          "achieved": nbytes / (avg_ms * 1e-3) / 1e9, "bytes_per_launch": nbytes})
     if kcount[2]:
         kern.append({"kernel": "zero fill alone", "launches": int(kcount[2]), "avg_ms": fill_ms,
-                     "achieved": BATCH * GRID_BYTES / (fill_ms * 1e-3) / 1e9, "bytes_per_launch": BATCH * GRID_BYTES})
+                     "achieved": nex * GRID_BYTES / (fill_ms * 1e-3) / 1e9, "bytes_per_launch": nex * GRID_BYTES})
     dom = max(kern[:2], key=lambda x: x["avg_ms"] * x["launches"]) if kern else None
     roof = None
     if dom:
         traffic = NCU_TRAFFIC_PER_EXAMPLE.get(dom["kernel"].split()[0])
         roof = {"bound": "hbm", "kernel": dom["kernel"], "achieved": dom["achieved"], "peak": peak,
                 "unit": "GB/s", "frac": dom["achieved"] / peak, "peak_kind": peak_kind,
-                "traffic": traffic * BATCH if traffic else None,
+                "traffic": traffic * nex if traffic else None,
                 "avg_launch_ms": dom["avg_ms"], "algorithmic_bytes_per_launch": dom["bytes_per_launch"]}
     step_bytes = fwd_bytes + bwd_bytes
+    strong = args.config == "c4a"
     line = {
         "metric": METRIC, "value": value, "unit": "examples/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "batch_per_gpu": BATCH, "global_batch": BATCH * world,
-                   "parallelism": "examples sharded over %d GPU(s), no collective; every rank grids its own "
-                                  "coordinates with the atom counts and per-type radii of rank 0's batch" % world,
-                   "l2": "inputs larger than L2: each step writes 619 MB of grids and reads 619 MB of gradients"},
+        "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD_C4A if strong else WORKLOAD, "global_batch": global_batch,
+                   "examples_per_rank": [e - s0 for s0, e in bounds],
+                   "parallelism": "one global batch cut by example over %d GPU(s) with the atom-balancing "
+                                  "sharding helper, no collective; every example has its own atom count" % world,
+                   "l2": "inputs larger than L2: each step writes %d MB of grids and reads as much of gradients per GPU"
+                         % (nex * GRID_BYTES // 1000000)},
         "roofline": roof,
-        "roofline_step": {"bound": "hbm", "achieved": step_bytes * world / (ms / args.steps * 1e-3) / 1e9 / world,
-                          "peak": peak, "unit": "GB/s per GPU",
+        "roofline_step": {"bound": "hbm", "achieved": step_bytes / (ms / args.steps * 1e-3) / 1e9,
+                          "peak": peak, "unit": "GB/s per GPU (rank 0)",
                           "frac": step_bytes / (ms / args.steps * 1e-3) / 1e9 / peak,
                           "note": "whole step (all kernels) vs 24.77 MB + 52 B/atom per example"},
         "kernels": kern,
@@ -368,6 +410,9 @@ def run_gpu_arm(args, rank, world, local_rank):
                 "note": "every step uploads its atoms from pinned host memory and downloads its atom "
                         "gradients to pinned host memory; the copies run on a second stream one step ahead "
                         "of the kernels; grids and their gradients stay on the device as in a training loop"},
+        "e2e_host_arrays": {"value": global_batch * hsteps / (ms_host * 1e-3), "unit": "examples/s", "steps": hsteps,
+                            "note": "pinned host arrays handed to GridMaker.forward/backward themselves: the "
+                                    "calls copy atoms in and gradients out on the calling stream, no overlap"},
         "per_rank": per_rank,
         "gpu_launches": int(launches),
         "clocks": clocks,
@@ -378,7 +423,6 @@ def run_gpu_arm(args, rank, world, local_rank):
 
 
 def main():
-    global BATCH
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None,
@@ -388,6 +432,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=BATCH,
                     help="examples per GPU per step (the headline workload uses 50; smaller values are for profiler captures)")
+    ap.add_argument("--config", default="headline", choices=["headline", "c4a"],
+                    help="headline: 50 examples per GPU; c4a: one batch of 1024 examples cut over the GPUs")
+    ap.add_argument("--example-cost", type=float, default=1200.0,
+                    help="cost of one example's grids in atom-equivalents, for the balanced cut")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -399,7 +447,6 @@ def main():
         return
     if args.steps is None:
         args.steps = 1000
-    BATCH = args.batch
     run_gpu_arm(args, rank, world, local_rank)
 
 

@@ -7,14 +7,9 @@
 extern "C" {
 #endif
 
-/* Largest radius * radius_scale * final_radius_multiple (Angstrom) the per-region atom lists of the
- * gather path are sized for; larger atoms stay correct through an overflow list.  Default 3.5. */
-void lmg_set_max_radius_hint(float angstroms);
 /* -1 (default): the reference's own operation order for the density when gaussian_radius_multiple > 2,
  * the fast form otherwise; 0 / 1 force the fast / exact form. */
 void lmg_set_precise(int mode);
-/* 1 (default): forward = zero fill + scatter with reductions; 0: gather through per-region lists. */
-void lmg_set_forward_mode(int mode);
 /* 1 (default): kernels that walk rows in aligned quads of four voxels (16-byte loads,
  * red.global.add.v4.f32) where dim % 4 == 0 and the grid is 16-byte aligned; 0: never. */
 void lmg_set_quads(int on);

@@ -92,9 +92,7 @@ SYMBOLS = [
 ]
 # tuning knobs outside the reference interface
 EXTRA_SYMBOLS = [
-    ("lmg_set_max_radius_hint", None, [ctypes.c_float]),
     ("lmg_set_precise", None, [ctypes.c_int]),
-    ("lmg_set_forward_mode", None, [ctypes.c_int]),
     ("lmg_set_quads", None, [ctypes.c_int]),
     ("lmg_set_interp_tiled", None, [ctypes.c_int]),
     ("lmg_tma_timeouts", ctypes.c_uint, []),

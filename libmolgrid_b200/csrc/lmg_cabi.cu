@@ -15,11 +15,9 @@ namespace {
 
 thread_local std::string g_err;
 std::default_random_engine g_engine;  // same engine type as libmolgrid::random_engine
-float g_radius_hint = 3.5f;           // largest radius*radius_scale*final_radius_multiple expected
 int g_precise = -1;                   // -1 auto, 0 fast density, 1 reference-order density
 int g_interp_tiled = 1;               // tensor-copy staged interpolation where the input allows it
 int g_quads = 1;                      // aligned-quad kernels where the grid allows them
-int g_forward_mode = 1;               // 0: gather through region lists, 1: zero-fill + scatter
 
 // ---- optional per-kernel timing (bench support; off by default) --------------------------------
 // When enabled, the forward and backward kernels of each pass are bracketed by CUDA events on the
@@ -140,33 +138,10 @@ using lmg::fill_emit;
 using lmg::to_params;
 using lmg::to_xform;
 
-int regions_touched(int nvox, int s) { return (nvox + s - 2) / s + 1; }
-
-struct Geometry {
-  int nrx, nry, nrz, nreg, cap;
-};
-
-Geometry geometry(const lmg_gridmaker* g) {
-  Geometry G;
-  int d = (int)g->dim;
-  G.nrx = (d + lmg::REG_X - 1) / lmg::REG_X;
-  G.nry = (d + lmg::REG_Y - 1) / lmg::REG_Y;
-  G.nrz = (d + lmg::REG_Z - 1) / lmg::REG_Z;
-  G.nreg = G.nrx * G.nry * G.nrz;
-  int nvox = (int)std::floor(2.0f * g_radius_hint / g->resolution) + 2;
-  if (nvox < 2) nvox = 2;
-  long cap = (long)std::min(regions_touched(nvox, lmg::REG_X), G.nrx) *
-             std::min(regions_touched(nvox, lmg::REG_Y), G.nry) *
-             std::min(regions_touched(nvox, lmg::REG_Z), G.nrz);
-  G.cap = (int)std::min<long>(cap, 1 << 20);
-  return G;
-}
-
 // Scratch layout of one pass over nb examples.
 struct Layout {
-  size_t status, recs, chanp, cnt, bigcount, biglist, list, partial, total;
+  size_t status, recs, chanp, partial, total;
   size_t per_example;
-  size_t M, listcap;
 };
 
 constexpr size_t STATUS_BYTES = 256;
@@ -174,28 +149,15 @@ constexpr size_t STATUS_BYTES = 256;
 Layout layout(const lmg_gridmaker* g, int op, int nb, int N, int T, int vec) {
   Layout L;
   std::memset(&L, 0, sizeof L);
-  Geometry G = geometry(g);
   size_t recs = align_up((size_t)N * sizeof(lmg::Rec));
   size_t chanp = (vec && g->radii_type_indexed) ? align_up((size_t)T * sizeof(lmg::ChanParam)) : 0;
-  bool lists = op == LMG_OP_FORWARD || op == LMG_OP_BACKWARD_GRADIENTS;
-  L.M = lists ? (size_t)G.nreg * (vec ? 1 : T) : 0;
-  L.listcap = lists ? (size_t)N * G.cap : 0;
-  size_t cnt = align_up(L.M * 4);
-  size_t bigcount = lists ? 256 : 0;
-  size_t biglist = lists ? align_up((size_t)N * 4) : 0;
-  size_t list = align_up(L.listcap * 4);
   size_t partial = (vec && (op == LMG_OP_BACKWARD || op == LMG_OP_BACKWARD_GRADIENTS))
                        ? align_up((size_t)N * T * 3 * 4) : 0;
-  L.per_example = recs + chanp + cnt + bigcount + biglist + list + partial;
+  L.per_example = recs + chanp + partial;
   size_t o = STATUS_BYTES;
   L.status = 0;
   L.recs = o; o += recs * nb;
   L.chanp = o; o += chanp * nb;
-  // counters and big-list counters are adjacent so that one memset clears both
-  L.cnt = o; o += cnt * nb;
-  L.bigcount = o; o += bigcount * nb;
-  L.biglist = o; o += biglist * nb;
-  L.list = o; o += list * nb;
   L.partial = o; o += partial * nb;
   L.total = o;
   return L;
@@ -218,17 +180,10 @@ int check_common(const lmg_gridmaker* g, const lmg_atoms* a, const void* ws) {
   return LMG_OK;
 }
 
-void carve(lmg::EmitArgs& E, const Layout& L, char* ws, int nb) {
-  (void)nb;
+void carve(lmg::EmitArgs& E, const Layout& L, char* ws) {
   E.status = reinterpret_cast<int*>(ws + L.status);
   E.recs = reinterpret_cast<lmg::Rec*>(ws + L.recs);
   E.chanp = reinterpret_cast<lmg::ChanParam*>(ws + L.chanp);
-  E.cnt = L.M ? reinterpret_cast<unsigned*>(ws + L.cnt) : nullptr;
-  E.bigcount = reinterpret_cast<unsigned*>(ws + L.bigcount);
-  E.biglist = reinterpret_cast<unsigned*>(ws + L.biglist);
-  E.list = reinterpret_cast<unsigned*>(ws + L.list);
-  E.M = (int)L.M;
-  E.listcap = L.listcap;
 }
 
 // number of examples per pass that fit the workspace; 0 if none
@@ -291,9 +246,7 @@ int lmg_profile_collect(double* ms, int* count) {
 long lmg_launch_count(void) { return g_launches; }
 
 // Tuning knobs (not part of the reference interface).
-void lmg_set_max_radius_hint(float angstroms) { g_radius_hint = angstroms > 0 ? angstroms : 3.5f; }
 void lmg_set_precise(int mode) { g_precise = mode; }
-void lmg_set_forward_mode(int mode) { g_forward_mode = mode; }
 void lmg_set_quads(int on) { g_quads = on; }
 
 int lmg_gridmaker_init(lmg_gridmaker* g, float res, float d, int bin, int rti, float rscale, float grm) {
@@ -403,73 +356,40 @@ int lmg_forward(const lmg_gridmaker* g, const lmg_atoms* a, float* out, void* wo
   if (per_pass == 0)
     return fail(LMG_ERR_WORKSPACE, "workspace too small for one example: need " +
                                        std::to_string(STATUS_BYTES + one.per_example) + " bytes");
-  Geometry G = geometry(g);
-  // Scatter forward: one zero fill of the whole output, then per pass one emit and one scatter
-  // launch.  (Measured and dropped: filling on an auxiliary stream one chunk ahead of the scatter -
-  // the library's fill kernels occupy every SM, so the scatter blocks merely queue behind them; and
-  // letting each scatter launch clear the next chunk of examples - ten small launches lose more in
-  // ramp-up and tail than the overlap gains.)
-  ProfRec* pr_fill = nullptr;
-  if (g_forward_mode == 1) {
-    pr_fill = prof_begin(2, st);
-    e = cudaMemsetAsync(out, 0, grid_elems * a->batch * sizeof(float), st);
-    prof_end(pr_fill, st);
-    if (e != cudaSuccess) return cuda_fail(e, "zeroing output");
-  }
+  // One zero fill of the whole output, then per pass one emit and one scatter launch.  (Measured
+  // and dropped: filling on an auxiliary stream one chunk ahead of the scatter - the library's fill
+  // kernels occupy every SM, so the scatter blocks merely queue behind them; and letting each
+  // scatter launch clear the next chunk of examples - ten small launches lose more in ramp-up and
+  // tail than the overlap gains.)
+  ProfRec* pr_fill = prof_begin(2, st);
+  e = cudaMemsetAsync(out, 0, grid_elems * a->batch * sizeof(float), st);
+  prof_end(pr_fill, st);
+  if (e != cudaSuccess) return cuda_fail(e, "zeroing output");
   for (int b0 = 0; b0 < a->batch; b0 += per_pass) {
     int nb = std::min(per_pass, a->batch - b0);
     Layout L = layout(g, LMG_OP_FORWARD, nb, a->max_atoms, a->ntypes, vec);
     lmg::EmitArgs E;
     fill_emit(E, g, a);
-    carve(E, L, ws, nb);
+    carve(E, L, ws);
     E.b0 = b0; E.nb = nb;
     E.round_types = 0;
-    if (g_forward_mode == 1) {
-      E.cnt = nullptr;  // no lists
-      e = lmg::launch_emit(E, st);
-      if (e != cudaSuccess) return cuda_fail(e, "emit");
-      lmg::BwdArgs S;
-      std::memset(&S, 0, sizeof S);
-      S.gm = E.gm; S.b0 = b0; S.nb = nb; S.N = E.N; S.T = E.T;
-      S.type_vector = a->type_vector;
-      S.centers = a->centers;
-      for (int i = 0; i < 3; i++) S.center_host[i] = a->center_host[i];
-      S.recs = E.recs; S.chanp = E.chanp;
-      S.out_grid = out;
-      S.precise = use_precise(g);
-      S.quads = g_quads;
-      ProfRec* pr = prof_begin(0, st);
-      e = lmg::launch_forward_scatter(S, vec != 0, st);
-      prof_end(pr, st);
-      g_launches += 2 + ((vec && g->radii_type_indexed) ? 1 : 0);
-      if (e != cudaSuccess) return cuda_fail(e, "forward scatter");
-      continue;
-    }
-    E.nrx = G.nrx; E.nry = G.nry; E.nrz = G.nrz; E.cap = G.cap;
-    e = cudaMemsetAsync(ws + L.cnt, 0, L.biglist - L.cnt, st);
-    if (e != cudaSuccess) return cuda_fail(e, "clearing counters");
     e = lmg::launch_emit(E, st);
     if (e != cudaSuccess) return cuda_fail(e, "emit");
-    e = lmg::launch_scan_fill(E, st);
-    if (e != cudaSuccess) return cuda_fail(e, "scan/fill");
-    g_launches += 3 + ((vec && g->radii_type_indexed) ? 1 : 0);
-    lmg::FwdArgs F;
-    std::memset(&F, 0, sizeof F);
-    F.gm = E.gm; F.b0 = b0; F.nb = nb; F.N = E.N; F.T = E.T;
-    F.vec = vec; F.precise = use_precise(g);
-    F.vec4_ok = (g->dim % 4 == 0) && ((uintptr_t)out % 16 == 0);
-    F.type_vector = a->type_vector;
-    F.centers = a->centers;
-    for (int i = 0; i < 3; i++) F.center_host[i] = a->center_host[i];
-    F.recs = E.recs; F.chanp = E.chanp; F.cnt = E.cnt; F.list = E.list;
-    F.bigcount = E.bigcount; F.biglist = E.biglist;
-    F.nrx = G.nrx; F.nry = G.nry; F.nrz = G.nrz; F.M = E.M; F.listcap = E.listcap;
-    F.out = out;
+    lmg::BwdArgs S;
+    std::memset(&S, 0, sizeof S);
+    S.gm = E.gm; S.b0 = b0; S.nb = nb; S.N = E.N; S.T = E.T;
+    S.type_vector = a->type_vector;
+    S.centers = a->centers;
+    for (int i = 0; i < 3; i++) S.center_host[i] = a->center_host[i];
+    S.recs = E.recs; S.chanp = E.chanp;
+    S.out_grid = out;
+    S.precise = use_precise(g);
+    S.quads = g_quads;
     ProfRec* pr = prof_begin(0, st);
-    e = lmg::launch_forward(F, st);
+    e = lmg::launch_forward_scatter(S, vec != 0, st);
     prof_end(pr, st);
-    g_launches += vec ? 1 : 2;
-    if (e != cudaSuccess) return cuda_fail(e, "forward");
+    g_launches += 2 + ((vec && g->radii_type_indexed) ? 1 : 0);
+    if (e != cudaSuccess) return cuda_fail(e, "forward scatter");
   }
   return LMG_OK;
 }
@@ -494,10 +414,9 @@ static int backward_common(const lmg_gridmaker* g, const lmg_atoms* a, int op, i
     Layout L = layout(g, op, nb, a->max_atoms, a->ntypes, vec);
     lmg::EmitArgs E;
     fill_emit(E, g, a);
-    carve(E, L, ws, nb);
+    carve(E, L, ws);
     E.b0 = b0; E.nb = nb;
     E.round_types = 1;
-    E.cnt = nullptr;
     e = lmg::launch_emit(E, st);
     if (e != cudaSuccess) return cuda_fail(e, "emit");
     lmg::BwdArgs B;
@@ -580,17 +499,14 @@ int lmg_backward_gradients(const lmg_gridmaker* g, const lmg_atoms* a, const flo
   if (per_pass == 0)
     return fail(LMG_ERR_WORKSPACE, "workspace too small for one example: need " +
                                        std::to_string(STATUS_BYTES + one.per_example) + " bytes");
-  Geometry G = geometry(g);
-  if (g_forward_mode == 1) {
-    e = cudaMemsetAsync(diffdiff, 0, grid_elems * a->batch * sizeof(float), st);
-    if (e != cudaSuccess) return cuda_fail(e, "zeroing output");
-  }
+  e = cudaMemsetAsync(diffdiff, 0, grid_elems * a->batch * sizeof(float), st);
+  if (e != cudaSuccess) return cuda_fail(e, "zeroing output");
   for (int b0 = 0; b0 < a->batch; b0 += per_pass) {
     int nb = std::min(per_pass, a->batch - b0);
     Layout L = layout(g, LMG_OP_BACKWARD_GRADIENTS, nb, a->max_atoms, a->ntypes, 1);
     lmg::EmitArgs E;
     fill_emit(E, g, a);
-    carve(E, L, ws, nb);
+    carve(E, L, ws);
     E.b0 = b0; E.nb = nb;
     E.round_types = 0;
     // atom part (atom_diffdiff) and, by scatter, the grid part (diffdiff)
@@ -608,44 +524,13 @@ int lmg_backward_gradients(const lmg_gridmaker* g, const lmg_atoms* a, const flo
     B.partial = reinterpret_cast<float*>(ws + L.partial);
     B.out_grid = diffdiff;
     B.quads = g_quads;
-    if (g_forward_mode == 1) {
-      E.cnt = nullptr;  // no lists
-      e = lmg::launch_emit(E, st);
-      if (e != cudaSuccess) return cuda_fail(e, "emit");
-      e = lmg::launch_gradgrad_scatter(B, st);
-      if (e != cudaSuccess) return cuda_fail(e, "backward_gradients grid");
-      e = lmg::launch_backward(B, 3, st);
-      if (e != cudaSuccess) return cuda_fail(e, "backward_gradients atoms");
-      g_launches += 4 + (g->radii_type_indexed ? 1 : 0);
-      continue;
-    }
-    E.nrx = G.nrx; E.nry = G.nry; E.nrz = G.nrz; E.cap = G.cap;
-    e = cudaMemsetAsync(ws + L.cnt, 0, L.biglist - L.cnt, st);
-    if (e != cudaSuccess) return cuda_fail(e, "clearing counters");
     e = lmg::launch_emit(E, st);
     if (e != cudaSuccess) return cuda_fail(e, "emit");
-    e = lmg::launch_scan_fill(E, st);
-    if (e != cudaSuccess) return cuda_fail(e, "scan/fill");
-    g_launches += 3 + (g->radii_type_indexed ? 1 : 0);
-    // grid part: diffdiff
-    lmg::FwdArgs F;
-    std::memset(&F, 0, sizeof F);
-    F.gm = E.gm; F.b0 = b0; F.nb = nb; F.N = E.N; F.T = E.T;
-    F.vec = 1; F.gradgrad = 1;
-    F.vec4_ok = (g->dim % 4 == 0) && ((uintptr_t)diffdiff % 16 == 0);
-    F.atom_gradients = atom_gradients; F.type_gradients = type_gradients;
-    F.type_vector = a->type_vector;
-    F.centers = a->centers;
-    for (int i = 0; i < 3; i++) F.center_host[i] = a->center_host[i];
-    F.recs = E.recs; F.chanp = E.chanp; F.cnt = E.cnt; F.list = E.list;
-    F.bigcount = E.bigcount; F.biglist = E.biglist;
-    F.nrx = G.nrx; F.nry = G.nry; F.nrz = G.nrz; F.M = E.M; F.listcap = E.listcap;
-    F.out = diffdiff;
-    e = lmg::launch_forward(F, st);
+    e = lmg::launch_gradgrad_scatter(B, st);
     if (e != cudaSuccess) return cuda_fail(e, "backward_gradients grid");
     e = lmg::launch_backward(B, 3, st);
     if (e != cudaSuccess) return cuda_fail(e, "backward_gradients atoms");
-    g_launches += 3;
+    g_launches += 4 + (g->radii_type_indexed ? 1 : 0);
   }
   return LMG_OK;
 }

@@ -17,12 +17,6 @@
 
 namespace lmg {
 
-// Region of voxels owned by one warp of the forward kernel: lane -> (x = lane>>3, y = lane&7),
-// each lane keeps REG_Z consecutive z voxels in registers.
-constexpr int REG_X = 4;
-constexpr int REG_Y = 8;
-constexpr int REG_Z = 4;
-
 struct GMParams {
   float res, half, rscale, G, finalm;
   float A, B, C, D, E;
@@ -55,8 +49,6 @@ struct __align__(16) Rec {
 };
 
 constexpr unsigned REC_VALID = 1u;     // contributes to some voxel
-constexpr unsigned REC_BIG = 2u;       // footprint spans more regions than the list capacity
-constexpr unsigned REC_ZFREE = 4u;     // no voxel outside [lo.z, hi.z) can pass the radial test
 
 // Per (example, channel) radius constants for type-indexed radii.
 struct __align__(16) ChanParam {

@@ -8,15 +8,6 @@
 // the density into the grid with red.global.add (k_forward_quads*, k_forward_scatter).
 // Backward passes: one warp per atom reads the grid gradient under the footprint and reduces with
 // shuffles, so no global atomics are needed (k_backward_quads*, k_backward_warp).
-//
-// Alternative gather forward (forward mode 0, also for the grid term of backward_gradients in that
-// mode): emit also counts the atom into every voxel region its footprint touches;
-//   scan   : per-example exclusive scan of the (region, channel) counts
-//   fill   : writes atom indices into per-(region, channel) lists
-//   forward: one warp per 4x8x4-voxel region; per channel the warp turns its list into a per-lane
-//            bit mask of atoms whose footprint crosses the lane's z-column, then every lane walks
-//            its own mask and accumulates 4 voxels in registers; each output voxel is written
-//            exactly once with a 16-byte store (no memset, no read-modify-write of the grid).
 #include "lmg_device.cuh"
 #include "lmg_launch.h"
 
@@ -25,32 +16,6 @@ namespace lmg {
 // ---------------------------------------------------------------------------------------------
 // emit
 // ---------------------------------------------------------------------------------------------
-
-__device__ __forceinline__ void region_box(const uint4& c, int& rx0, int& rx1, int& ry0, int& ry1,
-                                           int& rz0, int& rz1) {
-  unsigned lox = lo16(c.x), loy = hi16(c.x), hix = lo16(c.y), hiy = hi16(c.y);
-  unsigned loz = lo16(c.z), hiz = hi16(c.z);
-  rx0 = lox / REG_X; rx1 = (hix - 1) / REG_X;
-  ry0 = loy / REG_Y; ry1 = (hiy - 1) / REG_Y;
-  rz0 = loz / REG_Z; rz1 = (hiz - 1) / REG_Z;
-}
-
-// True when the axis-aligned box of region (rx,ry,rz) can hold a voxel within sqrt(Tcull) of the
-// atom.  Conservative (the threshold is widened by a few ulps' worth), and a pure function of its
-// arguments so that the counting and the filling pass agree.
-__device__ __forceinline__ bool region_in_reach(const GMParams& gm, float ox, float oy, float oz,
-                                                float ax, float ay, float az, float Tcull,
-                                                int rx, int ry, int rz) {
-  unsigned last = gm.dim - 1;
-  float x0 = voxel_coord(ox, rx * REG_X, gm.res), x1 = voxel_coord(ox, min((unsigned)(rx * REG_X + REG_X - 1), last), gm.res);
-  float y0 = voxel_coord(oy, ry * REG_Y, gm.res), y1 = voxel_coord(oy, min((unsigned)(ry * REG_Y + REG_Y - 1), last), gm.res);
-  float z0 = voxel_coord(oz, rz * REG_Z, gm.res), z1 = voxel_coord(oz, min((unsigned)(rz * REG_Z + REG_Z - 1), last), gm.res);
-  float dx = fmaxf(fmaxf(x0 - ax, ax - x1), 0.f);
-  float dy = fmaxf(fmaxf(y0 - ay, ay - y1), 0.f);
-  float dz = fmaxf(fmaxf(z0 - az, az - z1), 0.f);
-  float d2 = dx * dx + dy * dy + dz * dz;
-  return d2 <= Tcull * 1.0001f + 1e-12f;
-}
 
 // Type-indexed radii: constants of channel t of example b.
 __device__ __forceinline__ void make_chan_param(const GMParams& gm, float radius, ChanParam& cp) {
@@ -144,613 +109,14 @@ __global__ void __launch_bounds__(256) k_emit(EmitArgs A) {
     if (any) {
       r.a = make_float4(x, y, z, cp.q.w);
       r.b = make_float4(1.f, cp.p.x, cp.p.y, cp.p.z);
-      // If even the nearest voxel layers outside [lo.z, hi.z) are farther than the cut-off by
-      // their z distance alone, the z test of the footprint can never decide anything.
-      bool zfree = true;
-      if (loz > 0) {
-        float dzl = __fsub_rn(voxel_coord(oz, loz - 1, gm.res), z);
-        zfree = zfree && dzl <= 0.f && __fmul_rn(dzl, dzl) > cp.q.w;
-      }
-      if (hiz < gm.dim) {
-        float dzh = __fsub_rn(voxel_coord(oz, hiz, gm.res), z);
-        zfree = zfree && dzh >= 0.f && __fmul_rn(dzh, dzh) > cp.q.w;
-      }
       r.c = make_uint4(lox | (loy << 16), hix | (hiy << 16), loz | (hiz << 16),
-                       (unsigned)chan | ((REC_VALID | (zfree ? REC_ZFREE : 0u)) << 16));
+                       (unsigned)chan | (REC_VALID << 16));
       r.d = make_float4(cp.p.w, cp.q.x, cp.q.y, cp.q.z);
     }
     valid = any;
   }
 
-  if (valid && A.cnt != nullptr) {
-    int rx0, rx1, ry0, ry1, rz0, rz1;
-    region_box(r.c, rx0, rx1, ry0, ry1, rz0, rz1);
-    int nslots = (rx1 - rx0 + 1) * (ry1 - ry0 + 1) * (rz1 - rz0 + 1);
-    if (nslots > A.cap) {
-      r.c.w |= REC_BIG << 16;
-      unsigned p = atomicAdd(&A.bigcount[bl], 1u);
-      A.biglist[(size_t)bl * A.N + p] = (unsigned)a;
-    } else {
-      unsigned* cnt = A.cnt + (size_t)bl * A.M;
-      int tb = A.vec ? 1 : A.T;
-      int ch = A.vec ? 0 : chan;
-      for (int rx = rx0; rx <= rx1; rx++)
-        for (int ry = ry0; ry <= ry1; ry++)
-          for (int rz = rz0; rz <= rz1; rz++) {
-            if (!region_in_reach(gm, ox, oy, oz, r.a.x, r.a.y, r.a.z, r.a.w, rx, ry, rz)) continue;
-            int reg = (rx * A.nry + ry) * A.nrz + rz;
-            atomicAdd(&cnt[(size_t)reg * tb + ch], 1u);
-          }
-    }
-  }
   A.recs[i] = r;
-}
-
-// ---------------------------------------------------------------------------------------------
-// scan: in-place exclusive prefix sum of the M counters of each example
-// ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024) k_scan(unsigned* cnt, int M) {
-  __shared__ unsigned warp_tot[32];
-  __shared__ unsigned carry_s;
-  unsigned* c = cnt + (size_t)blockIdx.x * M;
-  int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-  if (tid == 0) carry_s = 0;
-  __syncthreads();
-  const int per = 8;
-  for (int base = 0; base < M; base += 1024 * per) {
-    unsigned v[per];
-    unsigned sum = 0;
-    int i0 = base + tid * per;
-#pragma unroll
-    for (int k = 0; k < per; k++) {
-      v[k] = (i0 + k < M) ? c[i0 + k] : 0u;
-      sum += v[k];
-    }
-    unsigned inc = sum;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      unsigned n = __shfl_up_sync(0xffffffffu, inc, o);
-      if (lane >= o) inc += n;
-    }
-    if (lane == 31) warp_tot[wid] = inc;
-    __syncthreads();
-    if (wid == 0) {
-      unsigned w = warp_tot[lane];
-      unsigned winc = w;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        unsigned n = __shfl_up_sync(0xffffffffu, winc, o);
-        if (lane >= o) winc += n;
-      }
-      warp_tot[lane] = winc - w;  // exclusive
-    }
-    __syncthreads();
-    unsigned carry = carry_s;
-    unsigned excl = carry + warp_tot[wid] + inc - sum;
-#pragma unroll
-    for (int k = 0; k < per; k++) {
-      if (i0 + k < M) c[i0 + k] = excl;
-      excl += v[k];
-    }
-    __syncthreads();
-    if (tid == 1023) carry_s = excl;
-    __syncthreads();
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
-// fill: after this kernel cnt[bin] holds the END offset of the bin (begin = end of the bin before)
-// ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) k_fill(EmitArgs A) {
-  int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= A.nb * A.N) return;
-  int bl = i / A.N, a = i - bl * A.N;
-  uint4 c = A.recs[i].c;
-  unsigned flags = c.w >> 16;
-  if (!(flags & REC_VALID) || (flags & REC_BIG)) return;
-  float4 ra = A.recs[i].a;
-  int b = A.b0 + bl;
-  float cx, cy, cz;
-  if (A.centers != nullptr) {
-    cx = A.centers[b * 3]; cy = A.centers[b * 3 + 1]; cz = A.centers[b * 3 + 2];
-  } else {
-    cx = A.center_host[0]; cy = A.center_host[1]; cz = A.center_host[2];
-  }
-  float ox = __fsub_rn(cx, A.gm.half), oy = __fsub_rn(cy, A.gm.half), oz = __fsub_rn(cz, A.gm.half);
-  int rx0, rx1, ry0, ry1, rz0, rz1;
-  region_box(c, rx0, rx1, ry0, ry1, rz0, rz1);
-  unsigned* cnt = A.cnt + (size_t)bl * A.M;
-  unsigned* list = A.list + (size_t)bl * A.listcap;
-  int tb = A.vec ? 1 : A.T;
-  int ch = A.vec ? 0 : (int)(c.w & 0xffffu);
-  for (int rx = rx0; rx <= rx1; rx++)
-    for (int ry = ry0; ry <= ry1; ry++)
-      for (int rzb = rz0; rzb <= rz1; rzb += 4) {
-        // four regions per step: their atomics are issued before any result is consumed
-        bool in[4];
-        unsigned p[4];
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-          int rz = rzb + k;
-          in[k] = rz <= rz1 && region_in_reach(A.gm, ox, oy, oz, ra.x, ra.y, ra.z, ra.w, rx, ry, rz);
-        }
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-          int reg = (rx * A.nry + ry) * A.nrz + rzb + k;
-          p[k] = in[k] ? atomicAdd(&cnt[(size_t)reg * tb + ch], 1u) : 0u;
-        }
-#pragma unroll
-        for (int k = 0; k < 4; k++)
-          if (in[k]) list[p[k]] = (unsigned)a;
-      }
-}
-
-// ---------------------------------------------------------------------------------------------
-// forward
-// ---------------------------------------------------------------------------------------------
-
-constexpr int FWD_WARPS = 4;        // warps per block of the vector-typed kernel (one region each)
-constexpr int FWD_INDEX_WARPS = 8;  // warps sharing one region in the index-typed kernel
-
-// ---------------------------------------------------------------------------------------------
-// forward, vector types (and the grid part of backward_gradients)
-//
-// One warp per region; the region's atom list is shared by all channels, so the warp loops over
-// the channels and, for each, stages the atoms that carry weight in that channel.  With
-// type-indexed radii the footprint and thresholds of an (atom, channel) pair are built here.
-// GRADGRAD evaluates, instead of the density, the derivative of the backward pass with respect
-// to the grid gradient (src/grid_maker.cpp:618-634).
-// ---------------------------------------------------------------------------------------------
-
-struct __align__(16) Cand {
-  float4 a;  // x, y, z, Tcull
-  float4 b;  // w, inv_ar2 (or ar when PRECISE), Tg, Tcut (Tbin when BINARY)
-  uint4 c;   // lo.x|lo.y<<16, hi.x|hi.y<<16, lo.z|hi.z<<16, bits of 1/ar
-  float4 g;  // GRADGRAD: incoming atom gradient x, y, z and type gradient of this channel
-};
-
-template <bool BINARY, bool PRECISE, bool GRADGRAD>
-__global__ void __launch_bounds__(FWD_WARPS * 32) k_forward_vector(FwdArgs F) {
-  __shared__ Cand cand_s[FWD_WARPS][32];
-  const GMParams& gm = F.gm;
-  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  int reg = blockIdx.x * FWD_WARPS + wid;
-  int bl = blockIdx.y;
-  int b = F.b0 + bl;
-  int nreg = F.nrx * F.nry * F.nrz;
-  if (reg >= nreg) return;
-  Cand* cs = cand_s[wid];
-
-  int rz = reg % F.nrz;
-  int ry = (reg / F.nrz) % F.nry;
-  int rx = reg / (F.nrz * F.nry);
-  unsigned vx = rx * REG_X + (lane >> 3), vy = ry * REG_Y + (lane & 7), vz0 = rz * REG_Z;
-  bool col_ok = vx < gm.dim && vy < gm.dim;
-
-  float cx, cy, cz;
-  if (F.centers != nullptr) {
-    cx = F.centers[b * 3]; cy = F.centers[b * 3 + 1]; cz = F.centers[b * 3 + 2];
-  } else {
-    cx = F.center_host[0]; cy = F.center_host[1]; cz = F.center_host[2];
-  }
-  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
-  float gx = voxel_coord(ox, vx, gm.res), gy = voxel_coord(oy, vy, gm.res);
-  float gz[REG_Z];
-#pragma unroll
-  for (int k = 0; k < REG_Z; k++) gz[k] = voxel_coord(oz, vz0 + k, gm.res);
-
-  const Rec* recs = F.recs + (size_t)bl * F.N;
-  const unsigned* cnt = F.cnt + (size_t)bl * F.M;
-  const unsigned* list = F.list + (size_t)bl * F.listcap;
-  unsigned nbig = F.bigcount[bl];
-  const unsigned* biglist = F.biglist + (size_t)bl * F.N;
-  size_t dim = gm.dim;
-  float* outb = F.out + (size_t)b * F.T * dim * dim * dim;
-  bool vec4_ok = F.vec4_ok;
-  unsigned beg = reg == 0 ? 0u : cnt[reg - 1];
-  unsigned nlist = cnt[reg] - beg;
-  unsigned total = nlist + nbig;  // atoms too large for the lists are visited by every region
-
-  for (int chan = 0; chan < F.T; chan++) {
-    float acc[REG_Z];
-#pragma unroll
-    for (int k = 0; k < REG_Z; k++) acc[k] = 0.f;
-    ChanParam cp;
-    if (gm.rti) cp = F.chanp[(size_t)bl * F.T + chan];
-
-    for (unsigned base = 0; base < total; base += 32) {
-      unsigned n = min(32u, total - base);
-      // ---- stage up to 32 candidates ----
-      bool have = false;
-      if (lane < n) {
-        unsigned e = base + lane;
-        unsigned ai = e < nlist ? list[beg + e] : biglist[e - nlist];
-        const Rec* rp = recs + ai;
-        float4 ra = rp->a, rb = rp->b;
-        uint4 rc = rp->c;
-        Cand cd;
-        size_t gi = (size_t)b * F.N + ai;
-        float w = F.type_vector[gi * F.T + chan];
-        bool use = w != 0.f;
-        if (!gm.rti) {
-          cd.a = ra;
-          cd.b = make_float4(w, PRECISE ? rp->d.z : rb.y, rb.z, BINARY ? rp->d.y : rp->d.x);
-          cd.c = make_uint4(rc.x, rc.y, rc.z, __float_as_uint(rb.w));
-        } else {
-          // per-channel radius: footprint and thresholds of this (atom, channel)
-          unsigned lox, hix, loy, hiy, loz, hiz;
-          bounds_1d(ox, ra.x, cp.q.z, gm.res, gm.dim, lox, hix);
-          bounds_1d(oy, ra.y, cp.q.z, gm.res, gm.dim, loy, hiy);
-          bounds_1d(oz, ra.z, cp.q.z, gm.res, gm.dim, loz, hiz);
-          cd.a = make_float4(ra.x, ra.y, ra.z, cp.q.w);
-          cd.b = make_float4(w, PRECISE ? cp.q.y : cp.p.x, cp.p.y, BINARY ? cp.q.x : cp.p.w);
-          cd.c = make_uint4(lox | (loy << 16), hix | (hiy << 16), loz | (hiz << 16),
-                            __float_as_uint(cp.p.z));
-          use = use && cp.q.y > 0.f;
-        }
-        if (GRADGRAD) {
-          cd.g = make_float4(F.atom_gradients[gi * 3], F.atom_gradients[gi * 3 + 1],
-                             F.atom_gradients[gi * 3 + 2], F.type_gradients[gi * F.T + chan]);
-        } else {
-          cd.g = make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-        if (!use) cd.a.w = -1.f;  // nothing passes a negative threshold
-        cs[lane] = cd;
-        have = use;
-      }
-      __syncwarp();
-      // ---- column test: bit i set when candidate i can touch this lane's z-column ----
-      unsigned mask = 0;
-      if (__any_sync(0xffffffffu, have)) {
-        for (unsigned i = 0; i < n; i++) {
-          float4 a = cs[i].a;
-          uint2 bb = *reinterpret_cast<const uint2*>(&cs[i].c);
-          float dx = __fsub_rn(gx, a.x), dy = __fsub_rn(gy, a.y);
-          float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
-          bool p = dxy2 <= a.w;
-          p = p && (vx - lo16(bb.x)) < (lo16(bb.y) - lo16(bb.x));
-          p = p && (vy - hi16(bb.x)) < (hi16(bb.y) - hi16(bb.x));
-          mask |= (p ? 1u : 0u) << i;
-        }
-      }
-      if (!col_ok) mask = 0;
-      // ---- each lane walks its own candidates ----
-      while (mask) {
-        int i = __ffs(mask) - 1;
-        mask &= mask - 1;
-        float4 a = cs[i].a, bq = cs[i].b;
-        uint4 cc = cs[i].c;
-        float dx = __fsub_rn(gx, a.x), dy = __fsub_rn(gy, a.y);
-        float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
-        unsigned loz = lo16(cc.z), nz = hi16(cc.z) - loz;
-        float4 gg = make_float4(0.f, 0.f, 0.f, 0.f);
-        float kD = 0.f, kE = 0.f, k4 = 0.f, dotxy = 0.f;
-        if (GRADGRAD) {
-          gg = cs[i].g;
-          float inv_ar = __uint_as_float(cc.w);
-          k4 = -4.f * bq.y; kD = gm.D * bq.y; kE = gm.E * inv_ar;
-          dotxy = fmaf(dx, gg.x, dy * gg.y);
-        }
-#pragma unroll
-        for (int k = 0; k < REG_Z; k++) {
-          float dz = __fsub_rn(gz[k], a.z);
-          float rsq = __fadd_rn(dxy2, __fmul_rn(dz, dz));
-          bool inz = (vz0 + k - loz) < nz;
-          if (GRADGRAD) {
-            // -(w * (d density/d dist)/dist) * (delta . atom gradient) + density * type gradient,
-            // only where the voxel is within the cut-off (the reference's isfinite test)
-            float e = ex2_approx(rsq * bq.y * NEG2_LOG2E);
-            float sq = sqrt_approx(rsq * bq.y);
-            float q = fmaxf(fmaf(fmaf(gm.A, sq, gm.B), sq, gm.C), 0.f);
-            bool gauss = rsq <= bq.z;
-            float val = gauss ? e : q;
-            float s = gauss ? k4 * e : fmaf(kE, rsqrt_approx(rsq), kD);
-            float dot = fmaf(dz, gg.z, dotxy);
-            float gval = fmaf(val, gg.w, -(bq.x * s) * (rsq > 0.f ? dot : 0.f));
-            if (inz && rsq <= bq.w) acc[k] += gval;
-          } else if (BINARY) {
-            if (inz && rsq < bq.w) acc[k] = __fadd_rn(acc[k], bq.x);
-          } else {
-            float v = PRECISE ? density_precise(rsq, bq.y, bq.z, bq.w, gm.A, gm.B, gm.C)
-                              : density_fast(rsq, bq.y, bq.z, bq.w, gm.A, gm.B, gm.C);
-            if (PRECISE) {
-              if (inz) acc[k] = __fadd_rn(acc[k], __fmul_rn(v, bq.x));
-            } else {
-              acc[k] = fmaf(inz ? v : 0.f, bq.x, acc[k]);
-            }
-          }
-        }
-      }
-      __syncwarp();
-    }
-
-    // ---- write this channel's 4 voxels ----
-    if (col_ok) {
-      float* o = outb + (((size_t)chan * dim + vx) * dim + vy) * dim + vz0;
-      if (vec4_ok) {
-        if (vz0 + REG_Z <= gm.dim) {
-          __stcs(reinterpret_cast<float4*>(o), make_float4(acc[0], acc[1], acc[2], acc[3]));
-        }
-      } else {
-#pragma unroll
-        for (int k = 0; k < REG_Z; k++)
-          if (vz0 + k < gm.dim) o[k] = acc[k];
-      }
-    }
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
-// forward, index types: the lists of one region are contiguous over channels, so the warp walks
-// them in chunks of 32 atoms regardless of channel.  Each lane keeps the 4 voxels of the channel
-// it is currently in and stores them when its next atom belongs to another channel.
-// ---------------------------------------------------------------------------------------------
-
-// out[lane j] bit i = in[lane i] bit j
-__device__ __forceinline__ unsigned warp_transpose32(unsigned x, int lane) {
-  unsigned m = 0x0000ffffu;
-#pragma unroll
-  for (int j = 16; j >= 1; j >>= 1) {
-    unsigned p = __shfl_xor_sync(0xffffffffu, x, j);
-    x = (lane & j) ? (((p >> j) & m) | (x & ~m)) : ((x & m) | ((p & m) << j));
-    m ^= m << (j >> 1);
-  }
-  return x;
-}
-
-struct __align__(16) CandI {
-  float4 a;  // x, y, z, Tcull
-  float4 b;  // kexp (ar when PRECISE), 1/ar^2, Tg, Tcut (Tbin when BINARY)
-  uint4 c;   // lo.z|hi.z<<16, channel | zfree<<16, unused, unused
-};
-
-
-// Adds one atom's density at the REG_Z voxels of a lane's column.  CHECKZ applies the footprint's
-// z range [lo.z, hi.z) (zoff = first voxel - lo.z, nz = hi.z - lo.z) on top of the radial test.
-template <bool BINARY, bool PRECISE, bool CHECKZ>
-__device__ __forceinline__ void fwd_eval4(float (&acc)[REG_Z], const float (&gz)[REG_Z], float az,
-                                          float dxy2, float4 bq, float A_, float B_,
-                                          float C_, unsigned zoff, unsigned nz) {
-#pragma unroll
-  for (int k = 0; k < REG_Z; k++) {
-    float dz = __fsub_rn(gz[k], az);
-    float rsq = __fadd_rn(dxy2, __fmul_rn(dz, dz));
-    bool inz = !CHECKZ || (zoff + k) < nz;
-    if (BINARY) {
-      if (inz && rsq < bq.w) acc[k] = 1.f;
-    } else if (PRECISE) {
-      float v = density_precise(rsq, bq.x, bq.z, bq.w, A_, B_, C_);
-      if (inz) acc[k] = __fadd_rn(acc[k], v);
-    } else {
-      // the tail keeps the reference's polynomial and constants so that its rounding residue near
-      // the zero at final_radius_multiple cancels against the reference's instead of adding to it
-      float g = ex2_approx(rsq * bq.x);
-      float sq = sqrt_approx(rsq * bq.y);
-      float q = fmaxf(fmaf(fmaf(A_, sq, B_), sq, C_), 0.f);
-      float v = rsq <= bq.z ? g : q;
-      acc[k] += (inz && rsq <= bq.w) ? v : 0.f;
-    }
-  }
-}
-
-template <bool BINARY, bool PRECISE>
-__global__ void __launch_bounds__(FWD_INDEX_WARPS * 32) k_forward_index(FwdArgs F) {
-  __shared__ CandI cand_s[FWD_INDEX_WARPS][32];
-  const GMParams& gm = F.gm;
-  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  // one block per region; its warps split the channels so that a crowded region is worked on by
-  // several warps, each owning whole channels (no two warps ever write the same voxel)
-  // Blocks run example by example; within an example the x-slabs are visited from the middle of
-  // the grid outwards.  Molecules sit around the grid centre, so each example starts with its
-  // crowded (compute-bound) regions and ends with sparse (store-bound) ones: the end of one example
-  // overlaps the start of the next, and the launch as a whole ends with light work.
-  // (Measured alternatives: all crowded regions of the batch first, or region-major order with
-  // examples fastest, are 10-20 % slower because they separate the two kinds of work.  Persistent
-  // warps taking (region, channel range) items from a device-built list were 40 % slower: sparse
-  // regions are chains of dependent loads, and many short-lived warps hide those better.)
-  int bl = blockIdx.y;
-  int b = F.b0 + bl;
-  int reg;
-  {
-    int per_slab = F.nry * F.nrz;
-    int s = blockIdx.x / per_slab, rest = blockIdx.x - s * per_slab;
-    int mid = (F.nrx - 1) / 2;
-    int rxp = mid + ((s & 1) ? (s + 1) / 2 : -(s / 2));
-    reg = rxp * per_slab + rest;
-  }
-  // (Letting one warp take all channels of a sparsely populated region was tried and is slower:
-  // the warps that leave early keep the block's registers allocated until the last one is done.)
-  const unsigned* cnt = F.cnt + (size_t)bl * F.M;
-  int cbeg = (wid * F.T) / FWD_INDEX_WARPS, cend = ((wid + 1) * F.T) / FWD_INDEX_WARPS;
-  if (cbeg >= cend) return;
-  CandI* cs = cand_s[wid];
-
-  int rz = reg % F.nrz;
-  int ry = (reg / F.nrz) % F.nry;
-  int rx = reg / (F.nrz * F.nry);
-  unsigned x0 = rx * REG_X, y0 = ry * REG_Y;
-  unsigned vx = x0 + (lane >> 3), vy = y0 + (lane & 7), vz0 = rz * REG_Z;
-  bool col_ok = vx < gm.dim && vy < gm.dim;
-
-  float cx, cy, cz;
-  if (F.centers != nullptr) {
-    cx = F.centers[b * 3]; cy = F.centers[b * 3 + 1]; cz = F.centers[b * 3 + 2];
-  } else {
-    cx = F.center_host[0]; cy = F.center_host[1]; cz = F.center_host[2];
-  }
-  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
-  float gx = voxel_coord(ox, vx, gm.res), gy = voxel_coord(oy, vy, gm.res);
-  float gz[REG_Z];
-#pragma unroll
-  for (int k = 0; k < REG_Z; k++) gz[k] = voxel_coord(oz, vz0 + k, gm.res);
-  float gxr[REG_X];
-#pragma unroll
-  for (int k = 0; k < REG_X; k++) gxr[k] = voxel_coord(ox, x0 + k, gm.res);
-
-  const Rec* recs = F.recs + (size_t)bl * F.N;
-  const unsigned* list = F.list + (size_t)bl * F.listcap;
-  size_t dim = gm.dim;
-  float* outb = F.out + (size_t)b * F.T * dim * dim * dim;
-  float* ocol = outb + ((size_t)vx * dim + vy) * dim + vz0;  // + chan * dim^3
-  size_t chan_stride = dim * dim * dim;
-  bool vec4_ok = F.vec4_ok;
-  float A_ = gm.A, B_ = gm.B, C_ = gm.C;
-
-  for (int g0 = cbeg; g0 < cend; g0 += 32) {
-    int g1 = min(g0 + 32, cend);
-    size_t bin0 = (size_t)reg * F.T + g0;
-    unsigned beg = bin0 == 0 ? 0u : cnt[bin0 - 1];
-    unsigned end = cnt[(size_t)reg * F.T + g1 - 1];
-    int cur = -1;
-    unsigned written = 0;
-    float acc[REG_Z];
-#pragma unroll
-    for (int k = 0; k < REG_Z; k++) acc[k] = 0.f;
-
-    auto flush = [&]() {
-      if (cur >= 0 && col_ok) {
-        float* o = ocol + (size_t)cur * chan_stride;
-        if (vec4_ok) {
-          __stcs(reinterpret_cast<float4*>(o), make_float4(acc[0], acc[1], acc[2], acc[3]));
-        } else {
-#pragma unroll
-          for (int k = 0; k < REG_Z; k++)
-            if (vz0 + k < gm.dim) o[k] = acc[k];
-        }
-        written |= 1u << (cur - g0);
-      }
-    };
-
-    // Two-deep prefetch: while chunk j is evaluated, the records of chunk j+1 are in flight (their
-    // list indices were loaded one chunk earlier) and the list indices of chunk j+2 are requested,
-    // so the dependent index -> record gather never stalls the loop.
-    float4 pa = make_float4(0.f, 0.f, 0.f, -1.f), pb = pa, pd = pa;
-    uint4 pc = make_uint4(0u, 0u, 0u, 0u);
-    unsigned nidx = 0;
-    if (beg + lane < end) {
-      const Rec* rp = recs + list[beg + lane];
-      pa = rp->a; pb = rp->b; pc = rp->c; pd = rp->d;
-    }
-    if (beg + 32 + lane < end) nidx = list[beg + 32 + lane];
-    for (unsigned base = beg; base < end; base += 32) {
-      unsigned n = min(32u, end - base);
-      unsigned bm = 0;
-      float4 ra = pa, rb = pb, rd = pd;
-      uint4 rc = pc;
-      if (base + 32 + lane < end) {
-        const Rec* rp = recs + nidx;
-        pa = rp->a; pb = rp->b; pc = rp->c; pd = rp->d;
-      }
-      if (base + 64 + lane < end) nidx = list[base + 64 + lane];
-      if (lane < n) {
-        CandI cd;
-        cd.a = ra;
-        cd.b = make_float4(PRECISE ? rd.z : rb.y * NEG2_LOG2E, rb.y, rb.z, BINARY ? rd.y : rd.x);
-        cd.c = make_uint4(rc.z, (rc.w & 0xffffu) | ((rc.w >> 16) & REC_ZFREE) << 16, 0u, 0u);
-        cs[lane] = cd;
-        // columns of this region inside the atom's integer footprint, minus x-rows that are
-        // farther than the cut-off by their x distance alone
-        int lx = max((int)lo16(rc.x) - (int)x0, 0), hx = min((int)lo16(rc.y) - (int)x0, REG_X);
-        int ly = max((int)hi16(rc.x) - (int)y0, 0), hy = min((int)hi16(rc.y) - (int)y0, REG_Y);
-        unsigned ym = (hy > ly) ? (((1u << hy) - 1u) & ~((1u << ly) - 1u)) : 0u;
-#pragma unroll
-        for (int k = 0; k < REG_X; k++) {
-          float dxr = __fsub_rn(gxr[k], ra.x);
-          bool rowin = k >= lx && k < hx && __fmul_rn(dxr, dxr) <= ra.w;
-          if (rowin) bm |= ym << (8 * k);
-        }
-      }
-      __syncwarp();
-      unsigned mask = warp_transpose32(bm, lane);
-      while (mask) {
-        int i = __ffs(mask) - 1;
-        mask &= mask - 1;
-        float4 a = cs[i].a;
-        float4 bq = cs[i].b;
-        uint4 cc = cs[i].c;
-        int ch = (int)(cc.y & 0xffffu);
-        if (ch != cur) {
-          flush();
-          cur = ch;
-#pragma unroll
-          for (int k = 0; k < REG_Z; k++) acc[k] = 0.f;
-        }
-        float dx = __fsub_rn(gx, a.x), dy = __fsub_rn(gy, a.y);
-        float dxy2 = __fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy));
-        if (!(dxy2 <= a.w)) continue;
-        // the footprint's z range only matters for atoms flagged as needing it (exact ties at the
-        // cut-off, truncated Gaussians); everywhere else the radial test already implies it
-        if (cc.y >> 16) {
-          fwd_eval4<BINARY, PRECISE, false>(acc, gz, a.z, dxy2, bq, A_, B_, C_, 0u, 0u);
-        } else {
-          unsigned loz = lo16(cc.x);
-          fwd_eval4<BINARY, PRECISE, true>(acc, gz, a.z, dxy2, bq, A_, B_, C_, vz0 - loz, hi16(cc.x) - loz);
-        }
-      }
-      __syncwarp();
-    }
-    flush();
-    // channels of this group that no atom of this column touched are zero
-    if (col_ok) {
-      for (int c = g0; c < g1; c++) {
-        if (!((written >> (c - g0)) & 1u)) {
-          float* o = ocol + (size_t)c * chan_stride;
-          if (vec4_ok) {
-            __stcs(reinterpret_cast<float4*>(o), make_float4(0.f, 0.f, 0.f, 0.f));
-          } else {
-#pragma unroll
-            for (int k = 0; k < REG_Z; k++)
-              if (vz0 + k < gm.dim) o[k] = 0.f;
-          }
-        }
-      }
-    }
-  }
-}
-
-// Atoms whose footprint spans more regions than the list capacity (far larger than the expected
-// radius) are not binned; after the main kernel one block per such atom adds its density into
-// the finished grid.  This path only exists so that any radius is handled correctly.
-template <bool BINARY, bool PRECISE>
-__global__ void __launch_bounds__(128) k_forward_big(FwdArgs F) {
-  const GMParams& gm = F.gm;
-  int bl = blockIdx.y;
-  int b = F.b0 + bl;
-  unsigned nbig = F.bigcount[bl];
-  if (nbig == 0) return;
-  float cx, cy, cz;
-  if (F.centers != nullptr) {
-    cx = F.centers[b * 3]; cy = F.centers[b * 3 + 1]; cz = F.centers[b * 3 + 2];
-  } else {
-    cx = F.center_host[0]; cy = F.center_host[1]; cz = F.center_host[2];
-  }
-  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
-  size_t dim = gm.dim;
-  for (unsigned e = blockIdx.x; e < nbig; e += gridDim.x) {
-    const Rec* rp = F.recs + (size_t)bl * F.N + F.biglist[(size_t)bl * F.N + e];
-    float4 ra = rp->a, rb = rp->b, rd = rp->d;
-    uint4 rc = rp->c;
-    unsigned lox = lo16(rc.x), loy = hi16(rc.x), hix = lo16(rc.y), hiy = hi16(rc.y);
-    unsigned loz = lo16(rc.z), hiz = hi16(rc.z);
-    unsigned nx = hix - lox, ny = hiy - loy, nz = hiz - loz;
-    float* o = F.out + ((size_t)b * F.T + (rc.w & 0xffffu)) * dim * dim * dim;
-    size_t total = (size_t)nx * ny * nz;
-    for (size_t v = threadIdx.x; v < total; v += blockDim.x) {
-      unsigned z = loz + (unsigned)(v % nz), y = loy + (unsigned)((v / nz) % ny), x = lox + (unsigned)(v / ((size_t)nz * ny));
-      float dx = __fsub_rn(voxel_coord(ox, x, gm.res), ra.x);
-      float dy = __fsub_rn(voxel_coord(oy, y, gm.res), ra.y);
-      float dz = __fsub_rn(voxel_coord(oz, z, gm.res), ra.z);
-      float rsq = __fadd_rn(__fadd_rn(__fmul_rn(dx, dx), __fmul_rn(dy, dy)), __fmul_rn(dz, dz));
-      float* p = o + ((size_t)x * dim + y) * dim + z;
-      if (BINARY) {
-        if (rsq < rd.y) *p = 1.f;
-      } else {
-        float val = PRECISE ? density_precise(rsq, rd.z, rb.z, rd.x, gm.A, gm.B, gm.C)
-                            : density_fast(rsq, rb.y, rb.z, rd.x, gm.A, gm.B, gm.C);
-        if (val != 0.f) atomicAdd(p, val);
-      }
-    }
-  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -816,19 +182,34 @@ __device__ __forceinline__ ItemParams load_item(const BwdArgs& G, int bl, int b,
 #endif
 constexpr int BWD2_WARPS = LMG_BWD_WARPS;    // warps (work items) per block, backward kernels
 constexpr int SCAT_WARPS = LMG_SCAT_WARPS;   // the same for the scatter kernels
+// One warp per block for the quad forward kernels whose work items differ a lot in size (an atom's
+// footprint grows with the cube of its radius): a block of several warps keeps its registers and
+// its slot until its slowest item is done.  Measured per batch of 50: index-typed forward 0.266 ->
+// 0.258 ms, one-hot vector forward 0.322 -> 0.286 ms; the binary and the weighted-channel kernels
+// are faster with four and keep SCAT_WARPS.
+#ifndef LMG_QS_WARPS
+#define LMG_QS_WARPS 1
+#endif
+constexpr int QS_WARPS = LMG_QS_WARPS;
 constexpr int BWD2_COLS = 256;  // compacted columns held per warp at a time
 constexpr int ZSTEPS = 4;       // z positions per lane and chunk; a chunk covers 4*ZSTEPS voxels
 
-struct ColBuf {
-  unsigned row[BWD2_COLS];  // x*dim + y
-  float dxy2[BWD2_COLS];    // (gx-ax)^2 + (gy-ay)^2
+template <int CAP_>
+struct ColBufT {
+  static constexpr unsigned CAP = CAP_;
+  unsigned row[CAP_];  // x*dim + y
+  float dxy2[CAP_];    // (gx-ax)^2 + (gy-ay)^2
 };
-struct ColBufD {
-  unsigned row[BWD2_COLS];
-  float dxy2[BWD2_COLS];
-  float dx[BWD2_COLS];  // gx-ax
-  float dy[BWD2_COLS];
+template <int CAP_>
+struct ColBufDT {
+  static constexpr unsigned CAP = CAP_;
+  unsigned row[CAP_];
+  float dxy2[CAP_];
+  float dx[CAP_];  // gx-ax
+  float dy[CAP_];
 };
+typedef ColBufT<BWD2_COLS> ColBuf;
+typedef ColBufDT<BWD2_COLS> ColBufD;
 
 // Appends the columns of [cbase, ncols) whose squared distance in the xy plane is <= Tcull to the
 // buffer until it is (nearly) full; returns how many it holds and advances cbase.
@@ -837,7 +218,7 @@ __device__ __forceinline__ unsigned compact_columns(BUF& buf, const ItemParams& 
                                                     unsigned ncols, unsigned ny, float inv_ny, float Tcull,
                                                     float ox, float oy, float res, unsigned dim, int lane) {
   unsigned nkept = 0;
-  while (cbase < ncols && nkept + 32 <= BWD2_COLS) {
+  while (cbase < ncols && nkept + 32 <= BUF::CAP) {
     unsigned c = cbase + lane;
     bool keep = false;
     unsigned x = 0, y = 0;
@@ -1346,10 +727,10 @@ __device__ __forceinline__ void forward_quads_item(const BwdArgs& G, int item, i
 }
 
 template <bool VEC>
-__global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads(BwdArgs G) {
-  __shared__ ColBuf bufs[SCAT_WARPS];
+__global__ void __launch_bounds__(QS_WARPS * 32) k_forward_quads(BwdArgs G) {
+  __shared__ ColBuf bufs[QS_WARPS];
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  int item = blockIdx.x * SCAT_WARPS + wid;
+  int item = blockIdx.x * QS_WARPS + wid;
   if (item >= (VEC ? G.N * G.T : G.N)) return;
   forward_quads_item<VEC>(G, item, blockIdx.y, bufs[wid], lane);
 }
@@ -1383,27 +764,17 @@ __global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads_nz(BwdArgs G)
 }
 
 // The backward passes (modes as in k_backward_warp) on aligned quads.
-template <int MODE, bool BINARY>
-__device__ __forceinline__ void backward_quads_item(const BwdArgs& G, int item, int bl, ColBufD& buf, ZTabs& zt,
-                                                    int lane) {
-  constexpr bool VEC = MODE == 1 || MODE == 3;
+struct BwdSums {
+  float agx, agy, agz, tg;  // reduced over the warp: every lane holds the totals
+};
+
+// The sweep of one work item whose constants are in P: sums over the item's footprint, reduced
+// over the warp.  `item` and `b` only serve MODE 3 (its incoming gradients).
+template <int MODE, bool BINARY, class BUF>
+__device__ __forceinline__ BwdSums backward_quads_core(const BwdArgs& G, ItemParams& P, int b, int item,
+                                                       float ox, float oy, float oz, BUF& buf, ZTabs& zt,
+                                                       int lane) {
   const GMParams& gm = G.gm;
-  int b = G.b0 + bl;
-  if (MODE == 3 || (MODE == 1 && G.type_gradients == nullptr)) {
-    // an (atom, channel) pair without weight contributes nothing: leave before any other load
-    int ea = item / G.T;
-    if (G.type_vector[((size_t)b * G.N + ea) * G.T + (item - ea * G.T)] == 0.f) return;
-  }
-
-  float cx, cy, cz;
-  if (G.centers != nullptr) {
-    cx = G.centers[b * 3]; cy = G.centers[b * 3 + 1]; cz = G.centers[b * 3 + 2];
-  } else {
-    cx = G.center_host[0]; cy = G.center_host[1]; cz = G.center_host[2];
-  }
-  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
-  ItemParams P = load_item<VEC>(G, bl, b, item, ox, oy, oz);
-
   size_t dim = gm.dim;
   size_t chan_off = ((size_t)b * G.T + P.chan) * dim * dim * dim;
   const float* diff = G.diff + chan_off;
@@ -1427,8 +798,8 @@ __device__ __forceinline__ void backward_quads_item(const BwdArgs& G, int item, 
     unsigned ncols = nx * ny;
     float inv_ny = 1.f / (float)ny;
     for (unsigned cbase = 0; cbase < ncols;) {
-      unsigned nkept = compact_columns<ColBufD, true>(buf, P, cbase, ncols, ny, inv_ny, Tcull, ox, oy,
-                                                      gm.res, gm.dim, lane);
+      unsigned nkept = compact_columns<BUF, true>(buf, P, cbase, ncols, ny, inv_ny, Tcull, ox, oy,
+                                                  gm.res, gm.dim, lane);
       for (unsigned zc = P.loz & ~3u; zc < P.hiz; zc += 4 * QPASS) {
         __syncwarp();
         fill_ztabs(zt, zc, P, oz, gm.res, kexp, lane);
@@ -1547,6 +918,35 @@ __device__ __forceinline__ void backward_quads_item(const BwdArgs& G, int item, 
     }
     if (MODE == 1 || MODE == 2) tg += __shfl_xor_sync(0xffffffffu, tg, o);
   }
+  BwdSums R;
+  R.agx = agx; R.agy = agy; R.agz = agz; R.tg = tg;
+  return R;
+}
+
+// One work item (an atom, or an (atom, channel) pair for the vector modes) from its record in the
+// workspace.
+template <int MODE, bool BINARY>
+__device__ __forceinline__ void backward_quads_item(const BwdArgs& G, int item, int bl, ColBufD& buf, ZTabs& zt,
+                                                    int lane) {
+  constexpr bool VEC = MODE == 1 || MODE == 3;
+  const GMParams& gm = G.gm;
+  int b = G.b0 + bl;
+  if (MODE == 3 || (MODE == 1 && G.type_gradients == nullptr)) {
+    // an (atom, channel) pair without weight contributes nothing: leave before any other load
+    int ea = item / G.T;
+    if (G.type_vector[((size_t)b * G.N + ea) * G.T + (item - ea * G.T)] == 0.f) return;
+  }
+
+  float cx, cy, cz;
+  if (G.centers != nullptr) {
+    cx = G.centers[b * 3]; cy = G.centers[b * 3 + 1]; cz = G.centers[b * 3 + 2];
+  } else {
+    cx = G.center_host[0]; cy = G.center_host[1]; cz = G.center_host[2];
+  }
+  float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
+  ItemParams P = load_item<VEC>(G, bl, b, item, ox, oy, oz);
+  BwdSums R = backward_quads_core<MODE, BINARY, ColBufD>(G, P, b, item, ox, oy, oz, buf, zt, lane);
+  float agx = R.agx, agy = R.agy, agz = R.agz, tg = R.tg;
   if (lane == 0) {
     size_t ai = (size_t)b * G.N + (VEC ? item / G.T : item);
     if (MODE == 0) {
@@ -1690,14 +1090,14 @@ constexpr int VA_CH = 32;  // channels per round
 constexpr int VA_SPARSE = 2;  // rounds with at most this many weighted channels sweep once per channel
 
 template <bool BINARY, bool PRECISE>
-__global__ void __launch_bounds__(SCAT_WARPS * 32) k_forward_quads_atom(BwdArgs G) {
-  __shared__ ColBuf bufs[SCAT_WARPS];
-  __shared__ ZTabs ztabs[SCAT_WARPS];
-  __shared__ int nz_t[SCAT_WARPS][VA_CH];
-  __shared__ float nz_w[SCAT_WARPS][VA_CH];
+__global__ void __launch_bounds__(QS_WARPS * 32) k_forward_quads_atom(BwdArgs G) {
+  __shared__ ColBuf bufs[QS_WARPS];
+  __shared__ ZTabs ztabs[QS_WARPS];
+  __shared__ int nz_t[QS_WARPS][VA_CH];
+  __shared__ float nz_w[QS_WARPS][VA_CH];
   const GMParams& gm = G.gm;
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  int item = blockIdx.x * SCAT_WARPS + wid;
+  int item = blockIdx.x * QS_WARPS + wid;
   int bl = blockIdx.y;
   int b = G.b0 + bl;
   if (item >= G.N) return;
@@ -2066,14 +1466,14 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads_atom_ag(BwdA
 // channels in which the atom carries weight take part (src/grid_maker.cpp:573).
 // Grid term, per voxel and such channel t:  density * tgrad_t  -  w_t * s * (delta . agrad), with
 // s = (d density/d dist)/dist: the two voxel-dependent factors are shared by the channels.
-__global__ void __launch_bounds__(SCAT_WARPS * 32) k_gradgrad_quads_atom(BwdArgs G) {
-  __shared__ ColBufD bufs[SCAT_WARPS];
-  __shared__ ZTabs ztabs[SCAT_WARPS];
-  __shared__ int nz_t[SCAT_WARPS][VA_CH];
-  __shared__ float nz_w[SCAT_WARPS][VA_CH], nz_g[SCAT_WARPS][VA_CH];
+__global__ void __launch_bounds__(QS_WARPS * 32) k_gradgrad_quads_atom(BwdArgs G) {
+  __shared__ ColBufD bufs[QS_WARPS];
+  __shared__ ZTabs ztabs[QS_WARPS];
+  __shared__ int nz_t[QS_WARPS][VA_CH];
+  __shared__ float nz_w[QS_WARPS][VA_CH], nz_g[QS_WARPS][VA_CH];
   const GMParams& gm = G.gm;
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  int item = blockIdx.x * SCAT_WARPS + wid;
+  int item = blockIdx.x * QS_WARPS + wid;
   int bl = blockIdx.y;
   int b = G.b0 + bl;
   if (item >= G.N) return;
@@ -2330,41 +1730,6 @@ cudaError_t launch_emit(const EmitArgs& A, cudaStream_t st) {
   return cudaGetLastError();
 }
 
-cudaError_t launch_scan_fill(const EmitArgs& A, cudaStream_t st) {
-  k_scan<<<A.nb, 1024, 0, st>>>(A.cnt, A.M);
-  int n = A.nb * A.N;
-  k_fill<<<(n + 255) / 256, 256, 0, st>>>(A);
-  return cudaGetLastError();
-}
-
-template <bool BINARY, bool PRECISE>
-static void launch_forward_t(const FwdArgs& F, dim3 grid, cudaStream_t st) {
-  if (F.vec) {
-    k_forward_vector<BINARY, PRECISE, false><<<grid, FWD_WARPS * 32, 0, st>>>(F);
-  } else {
-    dim3 gidx(F.nrx * F.nry * F.nrz, F.nb);
-    k_forward_index<BINARY, PRECISE><<<gidx, FWD_INDEX_WARPS * 32, 0, st>>>(F);
-    dim3 gbig(min(F.N, 32), F.nb);
-    k_forward_big<BINARY, PRECISE><<<gbig, 128, 0, st>>>(F);
-  }
-}
-
-cudaError_t launch_forward(const FwdArgs& F, cudaStream_t st) {
-  int nreg = F.nrx * F.nry * F.nrz;
-  dim3 grid((nreg + FWD_WARPS - 1) / FWD_WARPS, F.nb);
-  if (F.gradgrad) {
-    k_forward_vector<false, false, true><<<grid, FWD_WARPS * 32, 0, st>>>(F);
-    return cudaGetLastError();
-  }
-  if (F.gm.binary)
-    launch_forward_t<true, false>(F, grid, st);
-  else if (F.precise)
-    launch_forward_t<false, true>(F, grid, st);
-  else
-    launch_forward_t<false, false>(F, grid, st);
-  return cudaGetLastError();
-}
-
 cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st) {
   long items = (long)G.N * ((mode == 1 || mode == 3) ? G.T : 1);
   if (items == 0 || G.nb == 0) return cudaSuccess;
@@ -2419,8 +1784,8 @@ cudaError_t launch_gradgrad_scatter(const BwdArgs& G, cudaStream_t st) {
   if (items == 0 || G.nb == 0) return cudaSuccess;
   dim3 grid((unsigned)((items + SCAT_WARPS - 1) / SCAT_WARPS), G.nb);
   if (G.quads && !G.gm.rti && G.gm.dim % 4 == 0 && (uintptr_t)G.out_grid % 16 == 0) {
-    dim3 ga((unsigned)((G.N + SCAT_WARPS - 1) / SCAT_WARPS), G.nb);
-    k_gradgrad_quads_atom<<<ga, SCAT_WARPS * 32, 0, st>>>(G);
+    dim3 ga((unsigned)((G.N + QS_WARPS - 1) / QS_WARPS), G.nb);
+    k_gradgrad_quads_atom<<<ga, QS_WARPS * 32, 0, st>>>(G);
   } else if (G.quads && G.gm.dim % 4 == 0 && (uintptr_t)G.out_grid % 16 == 0) {
     dim3 ga((unsigned)(((long)G.N * nz_groups(G.T) + SCAT_WARPS - 1) / SCAT_WARPS), G.nb);
     k_gradgrad_quads_nz<<<ga, SCAT_WARPS * 32, 0, st>>>(G);
@@ -2438,10 +1803,10 @@ cudaError_t launch_forward_scatter(const BwdArgs& G, bool vec, cudaStream_t st) 
   bool aligned = G.quads && G.gm.dim % 4 == 0 && (uintptr_t)G.out_grid % 16 == 0;
   if (vec && !G.gm.rti && aligned) {
     // per-atom radii: one work item per atom, channels inside
-    dim3 ga((unsigned)((G.N + SCAT_WARPS - 1) / SCAT_WARPS), G.nb);
-    if (bin) k_forward_quads_atom<true, false><<<ga, SCAT_WARPS * 32, 0, st>>>(G);
-    else if (G.precise) k_forward_quads_atom<false, true><<<ga, SCAT_WARPS * 32, 0, st>>>(G);
-    else k_forward_quads_atom<false, false><<<ga, SCAT_WARPS * 32, 0, st>>>(G);
+    dim3 ga((unsigned)((G.N + QS_WARPS - 1) / QS_WARPS), G.nb);
+    if (bin) k_forward_quads_atom<true, false><<<ga, QS_WARPS * 32, 0, st>>>(G);
+    else if (G.precise) k_forward_quads_atom<false, true><<<ga, QS_WARPS * 32, 0, st>>>(G);
+    else k_forward_quads_atom<false, false><<<ga, QS_WARPS * 32, 0, st>>>(G);
     return cudaGetLastError();
   }
   if (G.quads && !bin && !G.precise && G.gm.dim % 4 == 0 && (uintptr_t)G.out_grid % 16 == 0) {
@@ -2451,7 +1816,8 @@ cudaError_t launch_forward_scatter(const BwdArgs& G, bool vec, cudaStream_t st) 
       k_forward_quads_nz<<<ga, SCAT_WARPS * 32, 0, st>>>(G);
       return cudaGetLastError();
     }
-    k_forward_quads<false><<<grid, SCAT_WARPS * 32, 0, st>>>(G);
+    dim3 gq((unsigned)((items + QS_WARPS - 1) / QS_WARPS), G.nb);
+    k_forward_quads<false><<<gq, QS_WARPS * 32, 0, st>>>(G);
     return cudaGetLastError();
   }
   if (vec) {
@@ -2466,4 +1832,6 @@ cudaError_t launch_forward_scatter(const BwdArgs& G, bool vec, cudaStream_t st) 
   return cudaGetLastError();
 }
 
+// Slab height: about 110 KB of one channel per block, so that the slabs being worked on together
+// (a few per SM) stay in L2 between their clearing and their last reduction.
 }  // namespace lmg

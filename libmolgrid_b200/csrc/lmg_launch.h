@@ -27,34 +27,7 @@ struct EmitArgs {
   // scratch
   Rec* recs;          // [nb][N]
   ChanParam* chanp;   // [nb][T], type-indexed radii only
-  unsigned* cnt;      // [nb][M] region(/channel) counters, NULL when no lists are needed
-  unsigned* list;     // [nb][listcap]
-  unsigned* bigcount; // [nb]
-  unsigned* biglist;  // [nb][N]
   int* status;
-  int nrx, nry, nrz, M, cap;
-  size_t listcap;
-};
-
-struct FwdArgs {
-  GMParams gm;
-  int b0, nb, N, T;
-  int vec, precise, vec4_ok;
-  int gradgrad;                  // evaluate backward_gradients' grid output instead of the density
-  const float* atom_gradients;   // [B][N][3], gradgrad only
-  const float* type_gradients;   // [B][N][T], gradgrad only
-  const float* type_vector;
-  const float* centers;
-  float center_host[3];
-  const Rec* recs;
-  const ChanParam* chanp;
-  const unsigned* cnt;
-  const unsigned* list;
-  const unsigned* bigcount;
-  const unsigned* biglist;
-  int nrx, nry, nrz, M;
-  size_t listcap;
-  float* out;
 };
 
 struct BwdArgs {
@@ -81,8 +54,6 @@ struct BwdArgs {
 };
 
 cudaError_t launch_emit(const EmitArgs& A, cudaStream_t st);
-cudaError_t launch_scan_fill(const EmitArgs& A, cudaStream_t st);
-cudaError_t launch_forward(const FwdArgs& F, cudaStream_t st);
 cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st);
 cudaError_t launch_forward_scatter(const BwdArgs& G, bool vec, cudaStream_t st);
 cudaError_t launch_gradgrad_scatter(const BwdArgs& G, cudaStream_t st);

@@ -110,7 +110,6 @@ int lmg_backward_static(const lmg_gridmaker* g, const lmg_atoms* a, const float*
   E.round_types = 1;
   E.status = reinterpret_cast<int*>(ws);
   E.recs = reinterpret_cast<lmg::Rec*>(ws + STATIC_STATUS_BYTES);
-  E.cnt = nullptr;  // no region lists are needed by the backward kernel
   e = lmg::launch_emit(E, st);
   if (e != cudaSuccess) return fail(LMG_ERR_CUDA, std::string("CUDA Error: emit: ") + cudaGetErrorString(e));
 

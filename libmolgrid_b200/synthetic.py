@@ -100,3 +100,45 @@ def dense_vector_batch(seed, batch, n, ntypes=28, alpha=0.3):
     tv = rng.dirichlet(np.ones(ntypes) * alpha, (batch, n)).astype(np.float32)
     radii = (1.7 * rng.uniform(0.8, 1.2, (batch, ntypes))).astype(np.float32)
     return coords, tv, radii
+
+
+# ---- the blob workload example by example (so that a rank can make only its own slice) --------------
+
+def blob_counts(seed, batch, nmin=2000, nmax=4000):
+    """Atom counts of the examples of a blob batch."""
+    return np.random.default_rng([seed, 0]).integers(nmin, nmax + 1, batch).astype(np.int32)
+
+
+def type_radii(seed, ntypes=28):
+    """One radius per type, U[1.2, 2.2]: a property of the typing scheme, the same for every example."""
+    return np.random.default_rng([seed, 1]).uniform(1.2, 2.2, ntypes).astype(np.float32)
+
+
+def blob_example(seed, index, n, R):
+    """Example `index` of the blob workload: n atoms (30 % in a 12 A ball, 70 % in a 4 A blob whose
+    centre is uniform in a 6 A ball), types uniform over len(R), radii by type, and the example's
+    transform (random unit quaternion, centre 0, translation U[-2,2]^3) as a row of 10 floats."""
+    rng = np.random.default_rng([seed, 2, index])
+    nblob = int(0.7 * n)
+    c = sphere(rng, 1, 6.0)
+    pts = np.concatenate([sphere(rng, n - nblob, 12.0), sphere(rng, nblob, 4.0) + c])
+    rng.shuffle(pts)
+    t = rng.integers(0, len(R), n)
+    tr = np.zeros(10, np.float32)
+    tr[:4] = random_quaternion(rng, 1)[0]
+    tr[7:] = rng.uniform(-2, 2, 3)
+    return pts.astype(np.float32), t.astype(np.float32), R[t], tr
+
+
+def blob_slice(seed, start, end, counts, R):
+    """Examples [start, end) of the blob workload as padded arrays (coords, types, radii, n, transforms)."""
+    nb = end - start
+    nmaxa = int(counts[start:end].max()) if nb else 0
+    coords = np.zeros((nb, nmaxa, 3), np.float32)
+    types = np.zeros((nb, nmaxa), np.float32)
+    radii = np.zeros((nb, nmaxa), np.float32)
+    tr = np.zeros((nb, 10), np.float32)
+    for i in range(nb):
+        n = int(counts[start + i])
+        coords[i, :n], types[i, :n], radii[i, :n], tr[i] = blob_example(seed, start + i, n, R)
+    return coords, types, radii, counts[start:end].astype(np.int32), tr

@@ -286,29 +286,55 @@ def test_small_workspace_runs_in_passes(port):
 
 
 @pytest.mark.parametrize("binary", [False, True])
-def test_atoms_larger_than_the_radius_hint(port, binary):
-    """Atoms whose footprint exceeds the list capacity take the unbinned path; same grids."""
-    from libmolgrid_b200 import _cabi
-    g, og = gm_pair(port, resolution=0.5, dimension=11.5, binary=binary)
-    T = 5
-    coords, types, radii = cases.index_case(21, 120, T, 6.5)
+def test_footprints_wider_than_the_column_buffer(port, binary):
+    """Atoms whose footprint holds more columns than a warp compacts at a time (256), and whose z
+    extent needs several passes of quads: radius 4 A at 0.25 A is 49 points across."""
+    g, og = gm_pair(port, resolution=0.25, dimension=11.75, binary=binary)
+    T = 3
+    coords, types, radii = cases.index_case(21, 40, T, 6.5)
+    radii[::3] = 4.0
     want = port.forward_index(og, (0, 0, 0), coords, types, radii, T)
-    vc, tv, vr = cases.vector_case(22, 80, T, 6.5)
-    wantv = port.forward_vector(og, (0, 0, 0), vc, tv, vr)
-    _cabi.lib().lmg_set_max_radius_hint(0.4)
-    try:
-        out = torch.empty(g.grid_dimensions(T), device="cuda")
-        g.forward((0, 0, 0), dev(coords), dev(types), dev(radii), out)
-        outv = torch.empty(g.grid_dimensions(T), device="cuda")
-        g.forward((0, 0, 0), dev(vc), dev(tv), dev(vr), outv)
-    finally:
-        _cabi.lib().lmg_set_max_radius_hint(3.5)
+    out = torch.empty(g.grid_dimensions(T), device="cuda")
+    g.forward((0, 0, 0), dev(coords), dev(types), dev(radii), out)
     got = out.cpu().numpy()
     if binary:
         assert np.array_equal(got, want)
     else:
-        assert np.allclose(got, want, **DENS)
-    assert np.allclose(outv.cpu().numpy(), wantv, **DENS)
+        assert np.allclose(got, want, **DENS), np.abs(got - want).max()
+    diff = np.random.default_rng(2).normal(size=want.shape).astype(np.float32)
+    ag = torch.empty((40, 3), device="cuda")
+    g.backward((0, 0, 0), dev(coords), dev(types), dev(radii), dev(diff), ag)
+    grad_close(ag.cpu().numpy(), port.backward_index(og, (0, 0, 0), coords, types, radii, diff), "atom gradients")
+    vc, tv, vr = cases.vector_case(22, 30, T, 6.5)
+    vr[::2] = 3.5
+    outv = torch.empty(g.grid_dimensions(T), device="cuda")
+    g.forward((0, 0, 0), dev(vc), dev(tv), dev(vr), outv)
+    assert np.allclose(outv.cpu().numpy(), port.forward_vector(og, (0, 0, 0), vc, tv, vr), **DENS)
+
+
+@pytest.mark.parametrize("binary", [False, True])
+def test_many_atoms_in_one_channel(port, binary):
+    """More atoms of one channel than a block lists at a time, all other channels empty."""
+    g, og = gm_pair(port, resolution=0.5, dimension=11.5, binary=binary)
+    T, N = 4, 5000
+    rng = np.random.default_rng(77)
+    coords = cases.sphere(rng, N, 7.5)
+    types = np.full(N, 2.0, np.float32)
+    types[:40] = rng.integers(0, T, 40)
+    radii = rng.uniform(0.6, 1.2, N).astype(np.float32)
+    want = port.forward_index(og, (0, 0, 0), coords, types, radii, T)
+    out = torch.full(g.grid_dimensions(T), -1.0, device="cuda")
+    g.forward((0, 0, 0), dev(coords), dev(types), dev(radii), out)
+    got = out.cpu().numpy()
+    if binary:
+        assert np.array_equal(got, want)
+    else:
+        # hundreds of terms per voxel, summed in no fixed order
+        assert np.allclose(got, want, rtol=2e-5, atol=1e-6), np.abs(got - want).max()
+    diff = rng.normal(size=want.shape).astype(np.float32)
+    ag = torch.empty((N, 3), device="cuda")
+    g.backward((0, 0, 0), dev(coords), dev(types), dev(radii), dev(diff), ag)
+    grad_close(ag.cpu().numpy(), port.backward_index(og, (0, 0, 0), coords, types, radii, diff), "atom gradients")
 
 
 @pytest.mark.parametrize("rti", [False, True])

@@ -242,8 +242,22 @@ def main():
             torch.cuda.synchronize()
             wall = (time.perf_counter() - t0) / args.reps
             h2d = float(batch.n_atoms.sum().item()) * 16
-        report("provider", "records -> device batch -> forward, batch 50, wall clock incl. host assembly",
-               wall * 1e3, B, grid.numel() * 4 + h2d, {"h2d_bytes_per_call": h2d})
+            report("provider", "records -> device batch -> forward, batch 50, wall clock incl. host assembly",
+                   wall * 1e3, B, grid.numel() * 4 + h2d, {"h2d_bytes_per_call": h2d})
+            # the same with the host half of the batches running ahead on worker threads
+            for workers in (1, 2, 3):
+                it = prov.device_batches(B, count=args.reps + 4, workers=workers)
+                for _ in range(4):
+                    g.forward(next(it), grid, 2.0, True)
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for batch in it:
+                    g.forward(batch, grid, 2.0, True)
+                torch.cuda.synchronize()
+                wall = (time.perf_counter() - t0) / args.reps
+                report("provider_prefetch", "as provider, host assembly %d batch(es) ahead on %d worker thread(s)"
+                       % (workers + 1, workers), wall * 1e3, B, grid.numel() * 4 + h2d,
+                       {"h2d_bytes_per_call": h2d, "workers": workers})
 
 
 if __name__ == "__main__":

@@ -238,6 +238,24 @@ int lmg_decode_records(const void* records, const lmg_record_set* sets, int nset
                        float* coords, float* type_index, float* radii, float* centers,
                        lmg_transform* transforms, int* status, void* stream);
 
+/* Host-side helper of batch staging (no device work): copies n chunks, chunk i being bytes[i]
+ * bytes at host address src[i], back to back into dst (normally pinned memory that one
+ * host-to-device copy then moves).  The counterpart of the per-atom push_back loops of
+ * Example::merge_coordinates (src/example.cpp:84-96) for raw records. */
+int lmg_gather_host(void* dst, size_t dst_bytes, int n, const unsigned long long* src,
+                    const long long* bytes);
+
+/* sum[ntypes] (+)= the per-type totals of one coordinate set on the device: with type vectors
+ * type_vector[n][ntypes] the column sums, formed atom by atom in order; with type indices
+ * type_index[n] the number of atoms whose rounded index is the type (negative indices are skipped).
+ * zerofirst != 0 clears sum first.  *status (device int, may be NULL) becomes 1 if an index is
+ * >= ntypes, the CPU path's out_of_range.  Exactly one of type_index / type_vector is given.
+ * Replaces CoordinateSet::sum_types on Grid1fCUDA (src/coordinateset.cu:21-57); the results are
+ * those of the CPU overload (src/coordinateset.cpp:352-374), which the reference's own GPU kernel
+ * for type indices does not reproduce (it adds the index instead of 1 and overwrites sum). */
+int lmg_sum_types(const float* type_index, const float* type_vector, int n, int ntypes, float* sum,
+                  int zerofirst, int* status, void* stream);
+
 /* Reads back (synchronising `stream`) the status word that kernels of the last call that used
  * `workspace` wrote: 0, or LMG_ERR_OUT_OF_RANGE / LMG_ERR_INVALID_ARGUMENT when an atom's type
  * index was >= ntypes - the data-dependent checks of src/grid_maker.cpp:172 and :458-460,

@@ -86,6 +86,8 @@ SYMBOLS = [
                                                 _VP, _VP]),
     ("lmg_decode_records", ctypes.c_int, [_VP, _VP, ctypes.c_int, _VP, _VP, ctypes.c_int, ctypes.c_int,
                                           ctypes.c_int, _VP, _VP, _VP, _VP, _VP, _VP, _VP]),
+    ("lmg_gather_host", ctypes.c_int, [_VP, ctypes.c_size_t, ctypes.c_int, _VP, _VP]),
+    ("lmg_sum_types", ctypes.c_int, [_VP, _VP, ctypes.c_int, ctypes.c_int, _VP, ctypes.c_int, _VP, _VP]),
     ("lmg_check_status", ctypes.c_int, [_VP, _VP]),
     ("lmg_last_error", ctypes.c_char_p, []),
     ("lmg_version", ctypes.c_int, []),

@@ -169,6 +169,7 @@ def _current_device():
 
 
 _workspaces = {}
+_transform_ring = {}   # (device, batch) -> pinned staging buffers of GridMaker.batch_transforms
 
 
 def _workspace(device, nbytes):
@@ -474,11 +475,25 @@ class GridMaker(object):
         in example order like the reference's loop (include/libmolgrid/grid_maker.h:194-201).  Keep
         it to hand the same transforms to ``backward``."""
         B = len(batch)
-        rows = torch.empty((B, 10), dtype=torch.float32)   # B x lmg_transform
+        dev = batch.centers.device
+        # B x lmg_transform, drawn on the host into one of a few pinned buffers and copied without
+        # blocking; a buffer is reused only after the copy that last read it has finished
+        ring = _transform_ring.setdefault((dev, B), {"next": 0, "slots": []})
+        if len(ring["slots"]) < 4:
+            ring["slots"].append([torch.empty((B, 10), dtype=torch.float32).pin_memory(), None])
+            slot = ring["slots"][-1]
+        else:
+            slot = ring["slots"][ring["next"]]
+            ring["next"] = (ring["next"] + 1) % 4
+            if slot[1] is not None:
+                slot[1].synchronize()
+        rows = slot[0]
         zero = (ctypes.c_float * 3)(0, 0, 0)
         check(_cabi.lib().lmg_transform_random_batch(ctypes.c_void_p(rows.data_ptr()), B, zero,
                                                      float(random_translation), int(bool(random_rotation))))
-        tr = rows.to(batch.centers.device)
+        tr = rows.to(dev, non_blocking=True)
+        slot[1] = torch.cuda.Event()
+        slot[1].record(torch.cuda.current_stream(dev))
         tr[:, 4:7] = batch.centers
         return tr
 

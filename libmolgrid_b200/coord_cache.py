@@ -13,6 +13,7 @@ vectorised numpy on the host; the result is a CoordinateSet whose arrays go to t
 Shuffling, balancing, stratification and molecule parsing (OpenBabel) are not part of this path.
 """
 import ctypes
+import threading
 import os
 
 import numpy as np
@@ -217,6 +218,14 @@ class DeviceBatch(object):
     def num_types(self):
         return self._num_types
 
+    def check(self):
+        """Waits for the batch's assembly and raises if the decoder refused atoms (a coordinate set
+        of the table did not fit the padded arrays).  Not called on the hot path: it synchronises."""
+        status = self._keep[1]
+        if int(status.item()) != 0:
+            raise RuntimeError("batch assembly dropped atoms: a coordinate set does not fit max_atoms")
+        return self
+
 
 class ExampleProvider(object):
     """Examples in file order: ``populate`` reads example lists, ``next``/``next_batch`` walk them
@@ -235,6 +244,8 @@ class ExampleProvider(object):
         self._stage_slot = 0
         self._packs = {}
         self._tables = None
+        self._ix = None                  # per-example staging index (see _index)
+        self._ix_lock = threading.Lock()
 
     def populate(self, fname, num_labels=-1):
         names = [fname] if isinstance(fname, str) else list(fname)
@@ -246,6 +257,7 @@ class ExampleProvider(object):
                         self.refs.append(ExampleRef(line, nl))
         if not self.refs:
             raise ValueError("No valid examples found in training set.")
+        self._ix = None   # the staging index covers the examples known when it was built
 
     def size(self):
         return len(self.refs)
@@ -299,43 +311,86 @@ class ExampleProvider(object):
                 recs.append(np.ascontiguousarray(r).view(np.uint8))
                 counts.append(len(r)); typers.append(ci); toffs.append(toffset); dst.append(natoms)
                 natoms += len(r)
-                toffset += self.caches[ci].num_types()
+                # a set without atoms after typing does not advance the type offset
+                # (Example::merge_coordinates, src/example.cpp:84-96: "ignore empties")
+                if len(r) and (np.asarray(self.caches[ci].typer.map_types(r["type"])[0]) >= 0).any():
+                    toffset += self.caches[ci].num_types()
             p = (np.concatenate(recs) if recs else np.zeros(0, np.uint8), np.array(counts, np.int32),
                  np.array(typers, np.int32), np.array(toffs, np.int32), np.array(dst, np.int32))
             self._packs[i] = p
         return p
 
-    def next_device_batch(self, batch_size, device=None):
-        """The next ``batch_size`` examples as a DeviceBatch.  The raw records of all their files go
-        to the GPU in ONE copy from pinned memory together with a table of their coordinate sets; a
-        kernel does the type lookup, the merge of each example's sets with type offsets and the
-        padding (``lmg_decode_records``).  Work is queued on the current stream of ``device``."""
+    def _take(self, batch_size):
+        """Indices of the next ``batch_size`` examples (cyclic)."""
         if not self.refs:
             raise RuntimeError("No examples: populate() first")
-        if not torch.cuda.is_available():
-            raise RuntimeError("no CUDA device: this library has no CPU path")
-        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         B = int(batch_size)
         idx = [(self.pos + k) % len(self.refs) for k in range(B)]
         self.pos = (self.pos + B) % len(self.refs)
-        packs = [self._packed(i) for i in idx]
-        nl = len(self.refs[idx[0]].labels)
-        # set table, vectorised over the batch
-        nset = np.array([len(p[1]) for p in packs], dtype=np.int64)
-        counts = np.concatenate([p[1] for p in packs])
-        typers = np.concatenate([p[2] for p in packs])
-        toffs = np.concatenate([p[3] for p in packs])
-        dst = np.concatenate([p[4] for p in packs])
-        nsets = int(counts.size)
-        table = np.zeros(nsets, dtype=_SET_TABLE)
-        table["first"] = np.concatenate(([0], np.cumsum(counts[:-1])))
-        table["count"], table["typer"], table["toff"], table["dst"] = counts, typers, toffs, dst
+        return idx
+
+    def _index(self, idx):
+        """Per-example arrays for staging, built on first use and extended as examples are first
+        seen: address and size of each example's packed records, its label row, and its
+        coordinate sets in one flat table with a start offset per example."""
+        ix = self._ix
+        if ix is None:
+            n = len(self.refs)
+            ix = self._ix = dict(done=np.zeros(n, bool), ptr=np.zeros(n, np.uint64), nbytes=np.zeros(n, np.int64),
+                                 nset=np.zeros(n, np.int64), start=np.zeros(n, np.int64),
+                                 sets=np.zeros(0, dtype=_SET_TABLE), nlab=np.zeros(n, np.int64), labels=None)
+        new = [i for i in set(idx) if not ix["done"][i]]
+        if new:
+            with self._ix_lock:
+                rows = [ix["sets"]]
+                at = len(ix["sets"])
+                for i in new:
+                    if ix["done"][i]:
+                        continue
+                    rec, counts, typers, toffs, dst = self._packed(i)
+                    t = np.zeros(len(counts), dtype=_SET_TABLE)
+                    t["count"], t["typer"], t["toff"], t["dst"] = counts, typers, toffs, dst
+                    t["first"] = np.concatenate(([0], np.cumsum(counts[:-1]))) if len(counts) else 0
+                    if len(counts):
+                        t["center"][-1] = 1
+                    rows.append(t)
+                    ix["ptr"][i], ix["nbytes"][i] = rec.ctypes.data, rec.size
+                    ix["nset"][i], ix["start"][i] = len(counts), at
+                    at += len(counts)
+                    lab = np.asarray(list(self.refs[i].labels), np.float32)
+                    ix["nlab"][i] = lab.size
+                    if ix["labels"] is None:
+                        ix["labels"] = np.zeros((len(self.refs), lab.size), np.float32)
+                    ix["labels"][i, :min(lab.size, ix["labels"].shape[1])] = lab[:ix["labels"].shape[1]]
+                ix["sets"] = np.concatenate(rows)
+                ix["done"][new] = True
+        return ix
+
+    def _assemble(self, idx, slot):
+        """Host half of a device batch (no CUDA work besides waiting for the staging buffer): the raw
+        records of the examples ``idx``, their set table, atom counts, typer tables and labels, laid
+        out in the pinned buffer of staging slot ``slot``.  Safe to run on a worker thread; the copy
+        of the records runs in native code without the interpreter lock."""
+        B = len(idx)
+        ix = self._index(idx)
+        ia = np.asarray(idx, np.int64)
+        nl = int(ix["nlab"][ia[0]])
+        if (ix["nlab"][ia] != nl).any():
+            raise ValueError("examples of one batch carry different numbers of labels: %s vs %d"
+                             % (sorted(set(int(v) for v in ix["nlab"][ia])), nl))
+        # the batch's set table: the cached rows of its examples, re-based
+        nset = ix["nset"][ia]
+        nsets = int(nset.sum())
+        ends = np.cumsum(nset)
+        flat = np.arange(nsets) - np.repeat(ends - nset, nset) + np.repeat(ix["start"][ia], nset)
+        table = ix["sets"][flat]
+        nbytes = ix["nbytes"][ia]
+        rec_first = np.concatenate(([0], np.cumsum(nbytes[:-1]))) // RECORD.itemsize
+        table["first"] += np.repeat(rec_first, nset)
         table["example"] = np.repeat(np.arange(B), nset)
-        last = np.cumsum(nset) - 1
-        table["center"][last] = 1
-        n_atoms = np.array([p[0].size // RECORD.itemsize for p in packs], dtype=np.int32)
+        n_atoms = (nbytes // RECORD.itemsize).astype(np.int32)
         nmax = max(1, int(n_atoms.max()))
-        labels = np.array([list(self.refs[i].labels)[:nl] for i in idx], dtype=np.float32).reshape(B, nl)
+        labels = np.ascontiguousarray(ix["labels"][ia, :nl])
         if self._tables is None:
             tabs = [c.tables() for c in self.caches]
             self._tables = (np.concatenate([t for t, _ in tabs]).astype(np.int32).view(np.uint8),
@@ -343,25 +398,32 @@ class ExampleProvider(object):
         # one pinned blob: records of every example | set table | atom counts | type tables | labels
         small = [table.view(np.uint8), n_atoms.view(np.uint8), self._tables[0], self._tables[1],
                  labels.view(np.uint8).reshape(-1)]
-        rec_bytes = int(n_atoms.sum()) * RECORD.itemsize
+        rec_bytes = int(nbytes.sum())
         offs, total = [0], (rec_bytes + 15) // 16 * 16
         for p in small:
             offs.append(total)
             total += (p.size + 15) // 16 * 16
-        slot = self._stage_slot
-        self._stage_slot ^= 1
         host, busy = self._stage[slot]
         if busy is not None:
             busy.synchronize()               # the copy that last read this staging buffer has finished
         if host is None or host.numel() < total:
             host = torch.empty(max(2 * total, 1 << 20), dtype=torch.uint8).pin_memory()
+            self._stage[slot] = (host, None)
+        ptrs = np.ascontiguousarray(ix["ptr"][ia])
+        nb = np.ascontiguousarray(nbytes)
+        _cabi.check(_cabi.lib().lmg_gather_host(ctypes.c_void_p(host.data_ptr()), rec_bytes, B,
+                                                ctypes.c_void_p(ptrs.ctypes.data), ctypes.c_void_p(nb.ctypes.data)))
         hv = host.numpy()
-        o = 0
-        for p in packs:
-            hv[o:o + p[0].size] = p[0]
-            o += p[0].size
         for p, o in zip(small, offs[1:]):
             hv[o:o + p.size] = p
+        return dict(B=B, nl=nl, nsets=nsets, nmax=nmax, offs=offs, total=total, slot=slot,
+                    max_count=int(table["count"].max()) if nsets else 0)
+
+    def _launch(self, m, dev):
+        """Device half: one host-to-device copy of the staged blob and the decode kernels, queued
+        on the current stream of ``dev``."""
+        B, nl, nmax, offs, total, slot = m["B"], m["nl"], m["nmax"], m["offs"], m["total"], m["slot"]
+        host = self._stage[slot][0]
         blob = torch.empty(total, dtype=torch.uint8, device=dev)
         blob.copy_(host[:total], non_blocking=True)
         busy = torch.cuda.Event()
@@ -375,11 +437,57 @@ class ExampleProvider(object):
         base = blob.data_ptr()
         vp = ctypes.c_void_p
         _cabi.check(_cabi.lib().lmg_decode_records(
-            vp(base + offs[0]), vp(base + offs[1]), nsets, vp(base + offs[3]), vp(base + offs[4]), B, nmax,
-            int(counts.max()) if nsets else 0, vp(coords.data_ptr()), vp(types.data_ptr()),
+            vp(base + offs[0]), vp(base + offs[1]), m["nsets"], vp(base + offs[3]), vp(base + offs[4]), B, nmax,
+            m["max_count"], vp(coords.data_ptr()), vp(types.data_ptr()),
             vp(radii.data_ptr()), vp(centers.data_ptr()), None, vp(status.data_ptr()),
             vp(torch.cuda.current_stream(dev).cuda_stream)))
         dn = blob[offs[2]:offs[2] + 4 * B].view(torch.int32)
         lab = blob[offs[5]:offs[5] + 4 * B * nl].view(torch.float32).view(B, nl)
-        ntypes = self.num_types()
-        return DeviceBatch(coords, types, radii, dn, centers, lab, ntypes, (blob, status, host))
+        return DeviceBatch(coords, types, radii, dn, centers, lab, self.num_types(), (blob, status, host))
+
+    @staticmethod
+    def _device(device):
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device: this library has no CPU path")
+        return torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+
+    def next_device_batch(self, batch_size, device=None):
+        """The next ``batch_size`` examples as a DeviceBatch.  The raw records of all their files go
+        to the GPU in ONE copy from pinned memory together with a table of their coordinate sets; a
+        kernel does the type lookup, the merge of each example's sets with type offsets and the
+        padding (``lmg_decode_records``).  Work is queued on the current stream of ``device``."""
+        dev = self._device(device)
+        idx = self._take(batch_size)
+        slot = self._stage_slot
+        self._stage_slot = (slot + 1) % len(self._stage)
+        return self._launch(self._assemble(idx, slot), dev)
+
+    def device_batches(self, batch_size, count=None, device=None, workers=2):
+        """Generator of DeviceBatches in example order whose host half runs ahead on ``workers``
+        threads: while the GPU grids batch k and the caller issues its kernels, batches k+1.. are
+        being laid out in their own pinned buffers (src/example_provider.cpp:70-90 assembles
+        batches on the calling thread).  ``count`` batches, or without end."""
+        from concurrent.futures import ThreadPoolExecutor
+        dev = self._device(device)
+        workers = max(1, int(workers))
+        depth = workers + 1
+        while len(self._stage) < depth + 1:
+            self._stage.append((None, None))
+        nslots = len(self._stage)
+        pending = []
+        issued = 0
+        with ThreadPoolExecutor(max_workers=workers) as pool:
+            def submit():
+                nonlocal issued
+                slot = self._stage_slot
+                self._stage_slot = (slot + 1) % nslots
+                pending.append(pool.submit(self._assemble, self._take(batch_size), slot))
+                issued += 1
+            while (count is None or issued < count) and len(pending) < depth:
+                submit()
+            while pending:
+                m = pending.pop(0).result()
+                batch = self._launch(m, dev)
+                if count is None or issued < count:
+                    submit()
+                yield batch

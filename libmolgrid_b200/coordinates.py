@@ -5,9 +5,12 @@ include/libmolgrid/example.h with src/example.cpp:40-228 for what the gridding p
 construction from arrays, index/vector typing, merging of sets with type offsets, centre, clone,
 host/device affinity.  Construction from molecule files is outside this path.
 """
+import ctypes
+
 import numpy as np
 import torch
 
+from . import _cabi
 from . import grids as G
 from .grids import MGrid1f, MGrid2f
 
@@ -170,21 +173,45 @@ class CoordinateSet(object):
         return ret // 3
 
     def sum_types(self, out, zerofirst=True):
-        """Per-type sum of the type vectors (or counts of the type indices), src/coordinateset.cpp."""
+        """Per-type sum of the type vectors (or counts of the rounded type indices) added into
+        ``out`` (src/coordinateset.cpp:352-374).  With the output on the GPU the sums are formed by
+        ``lmg_sum_types`` on the device; a host output is summed on the host, as the container's
+        other host-side bookkeeping is."""
         o = G.operand_tensor(out)
         o = torch.from_numpy(o) if isinstance(o, np.ndarray) else o
+        if o.shape[0] != self.num_types():
+            raise ValueError("Type sum output dimension does not match number of types: %d vs %d"
+                             % (o.shape[0], self.num_types()))
+        vec = self.type_vector.size() > 0
+        if o.is_cuda:
+            if not o.is_contiguous() or o.dtype != torch.float32:
+                raise ValueError("type sums: a contiguous float32 tensor is needed")
+            src = (self.type_vector if vec else self.type_index)._current().t.to(o.device).contiguous()
+            status = torch.empty(1, dtype=torch.int32, device=o.device)
+            vp = ctypes.c_void_p
+            with torch.cuda.device(o.device):
+                _cabi.check(_cabi.lib().lmg_sum_types(
+                    None if vec else vp(src.data_ptr()), vp(src.data_ptr()) if vec else None,
+                    int(self.size()), int(o.shape[0]), vp(o.data_ptr()), int(bool(zerofirst)),
+                    vp(status.data_ptr()), vp(torch.cuda.current_stream(o.device).cuda_stream)))
+            if not vec and int(status.item()) != 0:
+                raise IndexError("Somehow an index type is too large (internal error).")
+            return
         if zerofirst:
             o.zero_()
         if self.size() == 0:
             return
-        if self.type_vector.size() > 0:
-            tv = self.type_vector._current().t.to(o.device)
-            w = min(o.shape[0], tv.shape[1])
-            o[:w] += tv[:, :w].sum(0)
+        if vec:
+            tv = self.type_vector._current().t.cpu().numpy()
+            acc = o.numpy()
+            for row in tv:           # atom by atom, as the reference's loop
+                acc += row
         else:
-            ti = self.type_index._current().t.to(o.device).to(torch.long)
-            ok = (ti >= 0) & (ti < o.shape[0])
-            o.index_add_(0, ti[ok], torch.ones(int(ok.sum()), dtype=o.dtype, device=o.device))
+            ti = np.round(self.type_index._current().t.cpu().numpy()).astype(np.int64)
+            if (ti >= o.shape[0]).any():
+                raise IndexError("Somehow an index type is too large (internal error).")
+            cnt = np.bincount(ti[ti >= 0], minlength=o.shape[0]).astype(np.float32)
+            o += torch.from_numpy(cnt)
 
     def mergeInto(self, rec, lig, unique_index_types=True):
         """This set becomes ``rec`` followed by ``lig``; with ``unique_index_types`` the second set's
@@ -365,14 +392,22 @@ class Example(object):
         return out
 
     def sum_types(self, out, unique_types=True):
+        """Type sums of the sets side by side (``unique_types``: every set clears and fills its own
+        range) or added into one shared range, which is not cleared first (src/example.cpp:355-374)."""
         o = G.operand_tensor(out)
         o = torch.from_numpy(o) if isinstance(o, np.ndarray) else o
-        o.zero_()
+        nt_all = self.num_types(unique_types)
+        if o.shape[0] != nt_all:
+            raise ValueError("Size of sum output doesn't match number of types in example: %d vs %d"
+                             % (o.shape[0], nt_all))
         offset = 0
         for s in self.coord_sets:
             if unique_types:
-                s.sum_types(o[offset:offset + s.max_type], zerofirst=False)
-                offset += s.max_type
+                nt = s.num_types()
+                if nt == 0:
+                    continue
+                s.sum_types(o[offset:offset + nt], zerofirst=True)
+                offset += nt
             else:
                 s.sum_types(o, zerofirst=False)
 

@@ -7,6 +7,8 @@
 #include <string>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "../../include/lmg_b200.h"
 #include "lmg_launch.h"
 #include "lmg_misc.h"
@@ -38,6 +40,13 @@ ProfRec* prof_begin(int kind, cudaStream_t st) {
 void prof_end(ProfRec* r, cudaStream_t st) {
   if (r != nullptr) cudaEventRecord(r->e1, st);
 }
+
+// A named range on the calling thread for the stages of a pass (visible in timeline tools; a
+// no-op when no tool is attached).
+struct Range {
+  explicit Range(const char* name) { nvtxRangePushA(name); }
+  ~Range() { nvtxRangePop(); }
+};
 
 int fail(int code, const std::string& msg) {
   g_err = msg;
@@ -361,8 +370,12 @@ int lmg_forward(const lmg_gridmaker* g, const lmg_atoms* a, float* out, void* wo
   // kernels occupy every SM, so the scatter blocks merely queue behind them; and letting each
   // scatter launch clear the next chunk of examples - ten small launches lose more in ramp-up and
   // tail than the overlap gains.)
+  Range whole("lmg_forward");
   ProfRec* pr_fill = prof_begin(2, st);
-  e = cudaMemsetAsync(out, 0, grid_elems * a->batch * sizeof(float), st);
+  {
+    Range r("zero fill");
+    e = cudaMemsetAsync(out, 0, grid_elems * a->batch * sizeof(float), st);
+  }
   prof_end(pr_fill, st);
   if (e != cudaSuccess) return cuda_fail(e, "zeroing output");
   for (int b0 = 0; b0 < a->batch; b0 += per_pass) {
@@ -373,7 +386,10 @@ int lmg_forward(const lmg_gridmaker* g, const lmg_atoms* a, float* out, void* wo
     carve(E, L, ws);
     E.b0 = b0; E.nb = nb;
     E.round_types = 0;
-    e = lmg::launch_emit(E, st);
+    {
+      Range r("emit");
+      e = lmg::launch_emit(E, st);
+    }
     if (e != cudaSuccess) return cuda_fail(e, "emit");
     lmg::BwdArgs S;
     std::memset(&S, 0, sizeof S);
@@ -386,7 +402,10 @@ int lmg_forward(const lmg_gridmaker* g, const lmg_atoms* a, float* out, void* wo
     S.precise = use_precise(g);
     S.quads = g_quads;
     ProfRec* pr = prof_begin(0, st);
-    e = lmg::launch_forward_scatter(S, vec != 0, st);
+    {
+      Range r("forward scatter");
+      e = lmg::launch_forward_scatter(S, vec != 0, st);
+    }
     prof_end(pr, st);
     g_launches += 2 + ((vec && g->radii_type_indexed) ? 1 : 0);
     if (e != cudaSuccess) return cuda_fail(e, "forward scatter");
@@ -417,7 +436,10 @@ static int backward_common(const lmg_gridmaker* g, const lmg_atoms* a, int op, i
     carve(E, L, ws);
     E.b0 = b0; E.nb = nb;
     E.round_types = 1;
-    e = lmg::launch_emit(E, st);
+    {
+      Range r("emit");
+      e = lmg::launch_emit(E, st);
+    }
     if (e != cudaSuccess) return cuda_fail(e, "emit");
     lmg::BwdArgs B;
     std::memset(&B, 0, sizeof B);
@@ -432,7 +454,10 @@ static int backward_common(const lmg_gridmaker* g, const lmg_atoms* a, int op, i
     B.quads = g_quads;
     g_launches += 1 + ((vec && g->radii_type_indexed) ? 1 : 0);
     ProfRec* pr = prof_begin(1, st);
-    e = lmg::launch_backward(B, mode, st);
+    {
+      Range r(mode == 2 ? "backward relevance" : "backward");
+      e = lmg::launch_backward(B, mode, st);
+    }
     prof_end(pr, st);
     g_launches += mode == 1 ? 2 : 1;
     if (e != cudaSuccess) return cuda_fail(e, "backward");

@@ -15,6 +15,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstring>
 #include <string>
 
 #include "../../include/lmg_b200.h"
@@ -100,7 +101,81 @@ __global__ void __launch_bounds__(128) k_batch_centers(const Record* rec, const 
   }
 }
 
+// CoordinateSet::sum_types for vector types: one thread per type walks the atoms in order, so the
+// sum is formed in the order of the CPU loop (src/coordinateset.cpp:364-371) and agrees bit for bit;
+// neighbouring threads read neighbouring floats of a row.
+__global__ void __launch_bounds__(128) k_sum_vector_types(const float* __restrict__ tv, int n, int T,
+                                                          float* __restrict__ sum) {
+  int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  float s = sum[t];
+  for (int i = 0; i < n; i++) s = __fadd_rn(s, tv[(size_t)i * T + t]);
+  sum[t] = s;
+}
+
+// ... for index types: a block per type counts the atoms whose rounded index is that type
+// (src/coordinateset.cpp:357-362; the count is exact, so the order does not matter); block 0 also
+// reports an index >= T through the status word.
+__global__ void __launch_bounds__(256) k_sum_index_types(const float* __restrict__ ti, int n, int T,
+                                                         float* __restrict__ sum, int* status) {
+  __shared__ unsigned s_count;
+  if (threadIdx.x == 0) s_count = 0;
+  __syncthreads();
+  const float t = (float)blockIdx.x;
+  unsigned mine = 0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float r = roundf(ti[i]);
+    mine += r == t;
+    if (blockIdx.x == 0 && r >= (float)T && status != nullptr) atomicMax(status, 1);
+  }
+  mine = __reduce_add_sync(0xffffffffu, mine);
+  if ((threadIdx.x & 31) == 0 && mine) atomicAdd(&s_count, mine);
+  __syncthreads();
+  if (threadIdx.x == 0) sum[blockIdx.x] = __fadd_rn(sum[blockIdx.x], (float)s_count);
+}
+
 }  // namespace
+
+// Host-side half of batch staging: n chunks of bytes (the raw records of n examples) copied back to
+// back into `dst` (pinned memory).  Plain memcpy on the calling thread; the Python caller releases
+// the interpreter lock for the duration, so several batches can be staged at the same time.
+extern "C" int lmg_gather_host(void* dst, size_t dst_bytes, int n, const unsigned long long* src,
+                               const long long* bytes) {
+  if (n < 0) return fail(LMG_ERR_INVALID_ARGUMENT, "negative size");
+  if (n == 0) return LMG_OK;
+  if (dst == nullptr || src == nullptr || bytes == nullptr)
+    return fail(LMG_ERR_INVALID_ARGUMENT, "gather argument missing memory");
+  size_t o = 0;
+  for (int i = 0; i < n; i++) {
+    if (bytes[i] < 0 || o + (size_t)bytes[i] > dst_bytes)
+      return fail(LMG_ERR_INVALID_ARGUMENT, "gathered chunks do not fit the destination");
+    if (bytes[i] > 0) std::memcpy(static_cast<char*>(dst) + o, reinterpret_cast<const void*>(src[i]), (size_t)bytes[i]);
+    o += (size_t)bytes[i];
+  }
+  return LMG_OK;
+}
+
+extern "C" int lmg_sum_types(const float* type_index, const float* type_vector, int n, int ntypes, float* sum,
+                             int zerofirst, int* status, void* stream) {
+  if (n < 0 || ntypes < 0) return fail(LMG_ERR_INVALID_ARGUMENT, "negative size");
+  if (ntypes == 0) return LMG_OK;
+  if (sum == nullptr) return fail(LMG_ERR_INVALID_ARGUMENT, "Type sum output missing memory");
+  if ((type_index == nullptr) == (type_vector == nullptr) && n > 0)
+    return fail(LMG_ERR_INVALID_ARGUMENT, "exactly one of type_index and type_vector must be given");
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaSuccess;
+  if (zerofirst) e = cudaMemsetAsync(sum, 0, sizeof(float) * (size_t)ntypes, st);
+  if (e == cudaSuccess && status != nullptr) e = cudaMemsetAsync(status, 0, sizeof(int), st);
+  if (e == cudaSuccess && n > 0) {
+    if (type_vector != nullptr)
+      k_sum_vector_types<<<(ntypes + 127) / 128, 128, 0, st>>>(type_vector, n, ntypes, sum);
+    else
+      k_sum_index_types<<<ntypes, 256, 0, st>>>(type_index, n, ntypes, sum, status);
+    e = cudaGetLastError();
+  }
+  if (e != cudaSuccess) return fail(LMG_ERR_CUDA, std::string("summing types: ") + cudaGetErrorString(e));
+  return LMG_OK;
+}
 
 extern "C" int lmg_decode_records(const void* records, const lmg_record_set* sets, int nsets,
                                   const int* type_map, const float* type_radius, int batch, int max_atoms,

@@ -96,7 +96,7 @@ def main():
 
 
 MOL_OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "molecule.npz")
-REF_DATA = "/root/reference/test/data"
+REF_DATA = os.path.join(os.environ.get("LMG_REFERENCE_ROOT", "/root/reference"), "test", "data")
 
 
 def molecule_diff(shape):

@@ -10,7 +10,8 @@ from libmolgrid_b200 import atom_typing, coord_cache
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 MOL = np.load(os.path.join(HERE, "golden", "molecule.npz"))
-REF_DATA = "/root/reference/test/data"
+# the reference tree, where it is mounted (LMG_REFERENCE_ROOT overrides the usual place)
+REF_DATA = os.path.join(os.environ.get("LMG_REFERENCE_ROOT", "/root/reference"), "test", "data")
 
 
 def test_typers():
@@ -124,3 +125,34 @@ def test_reader_on_reference_fixtures():
     assert len(mc.offsets) > 100
     name = next(iter(mc.offsets))
     assert coord_cache.coordinate_set_from_records(mc.records(name), atom_typing.default_ligand_typer()).size() > 0
+
+
+def _ligonly_first_example():
+    p = coord_cache.ExampleProvider(data_root=os.path.join(REF_DATA, "structs"))
+    p.populate(os.path.join(REF_DATA, "ligonly.types"))
+    return p, p.next()
+
+
+@pytest.mark.skipif(not os.path.isdir(REF_DATA), reason="reference fixtures not mounted")
+def test_sum_types_known_answer_host():
+    """Type counts of the first example of the reference's ligonly.types
+    (test/test_example_provider.py:278-302 states them for one-hot type vectors; counting the
+    type indices gives the same totals)."""
+    p, ex = _ligonly_first_example()
+    want = [0.] * 14 + [2., 3., 0., 0., 0., 0., 0., 0., 2., 2., 1., 0., 0., 0.]
+    out = np.full(p.num_types(), 7.0, np.float32)
+    ex.sum_types(out)
+    np.testing.assert_array_equal(out, want)
+    # shared range: not cleared first, sets must agree on the number of types
+    shared = np.ones(14, np.float32)
+    ex.sum_types(shared, False)
+    np.testing.assert_array_equal(shared, np.array(want[14:]) + 1)
+    with pytest.raises(ValueError):
+        ex.sum_types(np.zeros(5, np.float32))
+    # type vectors: column sums in atom order, added into the output
+    cs = molgrid.CoordinateSet(np.zeros((3, 3), np.float32),
+                               np.array([[0.5, 0, 0.25], [0.25, 1, 0], [0, 0, 0.125]], np.float32),
+                               np.ones(3, np.float32))
+    acc = np.array([1, 0, 0], np.float32)
+    cs.sum_types(acc, zerofirst=False)
+    np.testing.assert_array_equal(acc, [1.75, 1, 0.375])

@@ -97,6 +97,32 @@ def test_device_batch_matches_host_examples(provider_dir):
         assert float(grads[b, :ns[b]][~keep].abs().sum()) == 0
 
 
+def test_empty_first_set_does_not_shift_the_channels(tmp_path):
+    """'none lig' and a receptor whose atoms all map to nothing: the ligand keeps channels [0, 14) on
+    both paths, as in Example::merge_coordinates (src/example.cpp:84-96), which ignores empty sets."""
+    rng = np.random.default_rng(3)
+    coord_cache.write_gninatypes(tmp_path / "lig.gninatypes", rng.normal(size=(12, 3)) * 2, rng.integers(2, 20, 12))
+    coord_cache.write_gninatypes(tmp_path / "hyd.gninatypes", rng.normal(size=(5, 3)), [0, 1, 0, 1, 0])
+    (tmp_path / "l.types").write_text("1 none lig.gninatypes\n0 hyd.gninatypes lig.gninatypes\n")
+    pa, pb = (coord_cache.ExampleProvider(data_root=str(tmp_path)) for _ in range(2))
+    for p in (pa, pb):
+        p.populate(str(tmp_path / "l.types"))
+    exs = pa.next_batch(2)
+    batch = pb.next_device_batch(2).check()
+    types = batch.type_index.cpu().numpy()
+    ns = batch.n_atoms.cpu().numpy()
+    for b, ex in enumerate(exs):
+        m = ex.merge_coordinates()
+        keep = types[b, :ns[b]] >= 0
+        np.testing.assert_array_equal(types[b, :ns[b]][keep], m.type_index.tonumpy())
+        assert m.size() > 0 and types[b, :ns[b]][keep].max() < pa.caches[1].num_types()
+    with pytest.raises(ValueError):
+        (tmp_path / "bad.types").write_text("1 0.5 none lig.gninatypes\n0 none lig.gninatypes\n")
+        pc = coord_cache.ExampleProvider(data_root=str(tmp_path))
+        pc.populate(str(tmp_path / "bad.types"))
+        pc.next_device_batch(2)
+
+
 def test_decode_reports_sets_that_do_not_fit(provider_dir):
     from libmolgrid_b200 import _cabi
     import ctypes
@@ -119,3 +145,70 @@ def test_decode_reports_sets_that_do_not_fit(provider_dir):
     with pytest.raises(ValueError):
         _cabi.check(_cabi.lib().lmg_decode_records(None, None, 1, None, None, 1, 4, 8, None, None, None, None,
                                                    None, None, None))
+
+
+def test_sum_types_on_the_device_equals_the_host_sums():
+    """lmg_sum_types against the host-side sums of the same sets: bit for bit with type vectors
+    (same order of addition), exact counts with type indices, accumulation into the output, and the
+    out-of-range report."""
+    rng = np.random.default_rng(12)
+    n, T = 3000, 28
+    coords = rng.normal(size=(n, 3)).astype(np.float32)
+    radii = np.ones(n, np.float32)
+    tv = rng.dirichlet(np.ones(T) * 0.3, n).astype(np.float32)
+    cs = molgrid.CoordinateSet(coords, tv, radii)
+    start = rng.normal(size=T).astype(np.float32)
+    host = start.copy()
+    cs.sum_types(host, zerofirst=False)
+    dev = torch.from_numpy(start.copy()).cuda()
+    cs.sum_types(dev, zerofirst=False)
+    np.testing.assert_array_equal(dev.cpu().numpy(), host)
+    cs.sum_types(dev)                                   # cleared first
+    host0 = np.zeros(T, np.float32)
+    cs.sum_types(host0)
+    np.testing.assert_array_equal(dev.cpu().numpy(), host0)
+
+    ti = rng.integers(-1, T, n).astype(np.float32)
+    ti[:10] += 0.4                                       # rounds down
+    ti[10:20] -= 0.4                                     # rounds up; -1.4 stays negative
+    ci = molgrid.CoordinateSet(coords, ti, radii, T)
+    host = np.zeros(T, np.float32)
+    ci.sum_types(host)
+    dev = torch.full((T,), 3.0, device="cuda")
+    ci.sum_types(dev)
+    np.testing.assert_array_equal(dev.cpu().numpy(), host)
+    assert host.sum() == (np.round(ti) >= 0).sum()
+    ti[5] = T
+    bad = molgrid.CoordinateSet(coords, ti, radii, T)
+    with pytest.raises(IndexError):
+        bad.sum_types(torch.zeros(T, device="cuda"))
+    with pytest.raises(IndexError):
+        bad.sum_types(np.zeros(T, np.float32))
+
+    # an Example lays its sets side by side
+    ex = molgrid.Example()
+    ex.coord_sets += [ci, molgrid.CoordinateSet(coords[:50], ti[100:150], radii[:50], T)]
+    both = torch.full((2 * T,), -1.0, device="cuda")
+    ex.sum_types(both)
+    hb = np.zeros(2 * T, np.float32)
+    ex.sum_types(hb)
+    np.testing.assert_array_equal(both.cpu().numpy(), hb)
+
+
+def test_prefetched_batches_equal_sequential_batches(provider_dir):
+    """device_batches (host assembly on worker threads, several staging buffers in flight) yields
+    the batches next_device_batch yields, in the same order."""
+    pa, pb = providers(provider_dir)
+    got = []
+    for batch in pb.device_batches(4, count=7, workers=3):
+        got.append([x.clone() for x in (batch.coords, batch.type_index, batch.radii, batch.n_atoms,
+                                        batch.centers, batch.labels)])
+        batch.check()
+    assert len(got) == 7 and pb.pos == (7 * 4) % pb.size()
+    for g in got:
+        want = pa.next_device_batch(4)
+        ns = want.n_atoms.cpu().numpy()
+        assert torch.equal(g[3], want.n_atoms) and torch.equal(g[4], want.centers) and torch.equal(g[5], want.labels)
+        for b in range(4):
+            for x, y in zip(g[:3], (want.coords, want.type_index, want.radii)):
+                assert torch.equal(x[b, :ns[b]], y[b, :ns[b]])

@@ -116,9 +116,7 @@ def main():
     if set(ops) & {"forward_vector", "backward_vector", "backward_gradients"}:
         B, N = 4, 3000
         rng = np.random.default_rng(1003)
-        coords = np.stack([cases.blob_batch(1003 + b, 1, N, N, T)[0][0] for b in range(B)])
-        tv = rng.dirichlet(np.ones(T) * 0.3, (B, N)).astype(np.float32)
-        rad = (1.7 * rng.uniform(0.8, 1.2, (B, T))).astype(np.float32)
+        coords, tv, rad = cases.dense_vector_batch(1003, B, N, T)
         g = lmg.GridMaker(0.25, 23.75, False, True)
         dc, dtv, dr = d(coords), d(tv), d(rad)
         cen = torch.zeros((B, 3), device=dev)
@@ -132,20 +130,36 @@ def main():
         pairs_fwd = float(((tv != 0) * vol[:, None, :]).sum())
         pairs_all = float(N * vol.sum())
         wl = "vector types, 28x96^3, batch %d x %d atoms, type-indexed radii" % (B, N)
+        # This configuration is bound by arithmetic, not by bytes: its roofline is the slower of the
+        # special-function unit (16 results per clock per SM) and FP32 issue (128 lanes per clock per
+        # SM) on the ALGORITHMIC work, i.e. the pair evaluations inside the cut-off spheres times
+        # the operations one evaluation needs (forward: ~12 FP32 + 2 special-function results - a
+        # square root and an exponential; backward: ~16 + 3; backward_gradients, both terms: ~80 + 3).
+        prop = torch.cuda.get_device_properties(dev)
+        clock_hz = float(getattr(prop, "clock_rate", 1965000)) * 1e3
+        xu_peak = prop.multi_processor_count * 16 * clock_hz
+        fp_peak = prop.multi_processor_count * 128 * clock_hz
+
+        def compute_roof(pairs, fp32, mufu, ms):
+            t = max(pairs * mufu / xu_peak, pairs * fp32 / fp_peak)
+            return {"pair_evaluations_per_s": pairs / (ms * 1e-3),
+                    "roofline_compute": {"bound": "special-function unit" if pairs * mufu / xu_peak >= pairs * fp32 / fp_peak
+                                         else "fp32 issue", "sms": prop.multi_processor_count, "clock_mhz": clock_hz / 1e6,
+                                         "xu_peak_per_s": xu_peak, "fp32_lane_peak_per_s": fp_peak,
+                                         "pair_evaluations": pairs, "fp32_per_pair": fp32, "xu_per_pair": mufu,
+                                         "roofline_ms": t * 1e3, "frac": t * 1e3 / ms}}
         if "forward_vector" in ops:
             ms = timeit(lambda: g.forward(cen, dc, dtv, dr, grid))
-            report("forward_vector", wl, ms, B, gb + B * N * (12 + 4 * T),
-                   {"pair_evaluations_per_s": pairs_fwd / (ms * 1e-3)})
+            report("forward_vector", wl, ms, B, gb + B * N * (12 + 4 * T), compute_roof(pairs_fwd, 12, 2, ms))
         g.forward(cen, dc, dtv, dr, grid)
         if "backward_vector" in ops:
             ms = timeit(lambda: g.backward(cen, dc, dtv, dr, diff, ag, tg))
-            report("backward_vector", wl, ms, B, gb + B * N * (12 + 4 * T) * 2,
-                   {"pair_evaluations_per_s": pairs_all / (ms * 1e-3)})
+            report("backward_vector", wl, ms, B, gb + B * N * (12 + 4 * T) * 2, compute_roof(pairs_all, 16, 3, ms))
         g.backward(cen, dc, dtv, dr, diff, ag, tg)
         if "backward_gradients" in ops:
             ms = timeit(lambda: g.backward_gradients(cen, dc, dtv, dr, diff, ag, tg, dd, add, tdd))
             report("backward_gradients", wl, ms, B, 2 * gb + B * N * (12 + 4 * T) * 3,
-                   {"pair_evaluations_per_s": 2 * pairs_fwd / (ms * 1e-3)})
+                   compute_roof(2 * pairs_fwd, 40, 3, ms))
         del grid, diff, dd
 
     # ---- vector types with per-atom radii (the autograd bindings' layout), 48^3 -------------------

@@ -59,9 +59,10 @@ int cuda_fail(cudaError_t e, const char* what) {
 
 size_t align_up(size_t v, size_t a = 256) { return (v + a - 1) / a * a; }
 
-// Tensor map over the interpolater's input seen as {z, y, x, example*channel}, box ITILE_BZ x ITILE_BY x
-// ITILE_BX x 1, zero fill outside.  The encoder is a driver entry point; false if it is not there.
-bool make_input_map(CUtensorMap* map, const float* in, unsigned dim, size_t nchan) {
+// Tensor maps over the interpolater's input seen as {z, y, x, example*channel}: one per box size
+// {ITILE_ZS[iz], ITILE_XYS[iy], ITILE_XYS[ix], 1}, zero fill outside.  The encoder is a driver entry point; false
+// if it is not there.
+bool make_input_maps(lmg::InterpMaps* maps, const float* in, unsigned dim, size_t nchan) {
   typedef CUresult (*Encode)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -77,12 +78,19 @@ bool make_input_map(CUtensorMap* map, const float* in, unsigned dim, size_t ncha
   cuuint64_t d = dim;
   cuuint64_t gdim[4] = {d, d, d, (cuuint64_t)nchan};
   cuuint64_t gstride[3] = {d * 4, d * d * 4, d * d * d * 4};  // bytes, dimensions 1..3
-  cuuint32_t boxdim[4] = {lmg::ITILE_BZ, lmg::ITILE_BY, lmg::ITILE_BX, 1};
   cuuint32_t estride[4] = {1, 1, 1, 1};
-  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(in), gdim, gstride, boxdim,
-                      estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  for (int ix = 0; ix < lmg::ITILE_NXY; ix++)
+    for (int iy = 0; iy < lmg::ITILE_NXY; iy++)
+      for (int iz = 0; iz < lmg::ITILE_NZ; iz++) {
+        cuuint32_t boxdim[4] = {(cuuint32_t)lmg::ITILE_ZS[iz], (cuuint32_t)lmg::ITILE_XYS[iy],
+                                (cuuint32_t)lmg::ITILE_XYS[ix], 1};
+        CUresult r = encode(&maps->m[(ix * lmg::ITILE_NXY + iy) * lmg::ITILE_NZ + iz], CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                            4, const_cast<float*>(in), gdim, gstride, boxdim, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return false;
+      }
+  return true;
 }
 
 }  // namespace
@@ -613,12 +621,12 @@ int lmg_interpolate(const lmg_interpolater* gi, int batch, int nchannels, const 
   // The tiled kernel stages boxes of the input through tensor copies: rows of the input must start
   // on 16-byte boundaries, and an 8^3 output tile must map into a 16x16x20 box of input voxels under
   // any rotation (8*sqrt(3)*out_res/in_res + 2 <= 16).
-  CUtensorMap map;
+  lmg::InterpMaps maps;
   bool tiled = g_interp_tiled && batch > 0 && nchannels > 0 && gi->in_dim > 0 &&
                (uintptr_t)in % 16 == 0 && (gi->in_dim * sizeof(float)) % 16 == 0 &&
                gi->out_resolution <= 1.008f * gi->in_resolution &&
                (size_t)batch * nchannels < (size_t)1 << 31 &&
-               make_input_map(&map, in, gi->in_dim, (size_t)batch * nchannels);
+               make_input_maps(&maps, in, gi->in_dim, (size_t)batch * nchannels);
   for (int b0 = 0; b0 < batch; b0 += lmg::INTERP_MAX_EX) {
     int nb = std::min(lmg::INTERP_MAX_EX, batch - b0);
     I.b0 = b0;
@@ -629,7 +637,7 @@ int lmg_interpolate(const lmg_interpolater* gi, int batch, int nchannels, const 
         I.ex[i].out_center[k] = out_centers[(size_t)(b0 + i) * 3 + k];
       }
     }
-    cudaError_t e = tiled ? lmg::launch_interpolate_tiled(map, I, nb, (cudaStream_t)stream)
+    cudaError_t e = tiled ? lmg::launch_interpolate_tiled(maps, I, nb, (cudaStream_t)stream)
                           : lmg::launch_interpolate(I, nb, (cudaStream_t)stream);
     g_launches += 1;
     if (e != cudaSuccess) return cuda_fail(e, "interpolate");

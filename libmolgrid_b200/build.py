@@ -48,7 +48,7 @@ def build_library(force=False, verbose=False):
     return LIB
 
 
-NATIVE_SRC = os.path.join(HERE, "cpp", "bindings.cpp")
+NATIVE_SRCS = [os.path.join(HERE, "cpp", "bindings.cpp"), os.path.join(HERE, "cpp", "bindings_objects.cpp")]
 
 
 def native_module_path():
@@ -61,7 +61,7 @@ def build_native_module(force=False):
     import pybind11
     import sysconfig
     out = native_module_path()
-    deps = [NATIVE_SRC, LIB] + [os.path.join(HERE, "cpp", "include", "libmolgrid", f)
+    deps = NATIVE_SRCS + [os.path.join(HERE, "cpp", "bindings_common.h"), LIB] + [os.path.join(HERE, "cpp", "include", "libmolgrid", f)
                                 for f in os.listdir(os.path.join(HERE, "cpp", "include", "libmolgrid"))]
     if not force and os.path.exists(out) and all(os.path.getmtime(d) <= os.path.getmtime(out) for d in deps):
         return out
@@ -69,7 +69,7 @@ def build_native_module(force=False):
     cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden",
            "-I" + pybind11.get_include(), "-I" + sysconfig.get_paths()["include"],
            "-I" + os.path.join(HERE, "cpp", "include"), "-I" + os.path.join(HERE, "..", "include"),
-           "-I" + os.path.join(cuda, "include"), NATIVE_SRC, "-o", out,
+           "-I" + os.path.join(cuda, "include")] + NATIVE_SRCS + ["-o", out,
            "-L" + HERE, "-llmg_b200", "-L" + os.path.join(cuda, "lib64"), "-lcudart",
            "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(cuda, "lib64")]
     res = subprocess.run(cmd, capture_output=True, text=True)

@@ -15,6 +15,7 @@
 #include <string>
 #include <vector>
 
+#include "bindings_common.h"
 #include "libmolgrid/libmolgrid.h"
 
 namespace py = pybind11;
@@ -22,86 +23,7 @@ using namespace libmolgrid;
 
 namespace {
 
-bool g_gpu_enabled = true;
-
-float3 to_float3(const py::handle& h) {
-  if (py::isinstance<float3>(h)) return h.cast<float3>();
-  py::sequence s = py::reinterpret_borrow<py::sequence>(h);
-  if (py::len(s) != 3) throw py::value_error("a point needs three coordinates");
-  return make_float3(s[0].cast<float>(), s[1].cast<float>(), s[2].cast<float>());
-}
-
-// A float32 array argument: where it lives, its shape, and (for host arrays) its device copy.
-class Arg {
- public:
-  Arg(const py::handle& h, const char* name, int ndim, bool output) : name_(name), output_(output) {
-    py::object o = py::reinterpret_borrow<py::object>(h);
-    if (py::hasattr(o, "ongpu") && py::hasattr(o, "gpu")) o = g_gpu_enabled ? o.attr("gpu")() : o.attr("cpu")();
-    if (py::hasattr(o, "t") && py::hasattr(o, "dimension")) o = o.attr("t");  // Grid view of this package
-    if (py::hasattr(o, "data_ptr") && py::hasattr(o, "is_cuda")) {
-      if (std::string(py::str(o.attr("dtype"))) != "torch.float32")
-        throw py::value_error(name_ + ": tensors must be float32 (double grids are not supported on the GPU path)");
-      if (!o.attr("is_contiguous")().cast<bool>()) throw py::value_error("Attempt to use non-contiguous tensor as grid");
-      cuda_ = o.attr("is_cuda").cast<bool>();
-      if (cuda_) {
-        int dev = o.attr("device").attr("index").cast<int>(), cur = 0;
-        LMG_CUDA_CHECK(cudaGetDevice(&cur));
-        if (dev != cur)
-          throw py::value_error("Tensor on different device than current: " + std::to_string(dev) + " vs " +
-                                std::to_string(cur));
-      }
-      data_ = reinterpret_cast<float*>(o.attr("data_ptr")().cast<size_t>());
-      for (auto d : o.attr("shape")) shape_.push_back(d.cast<size_t>());
-    } else if (py::isinstance<py::array>(o)) {
-      py::array a = py::reinterpret_borrow<py::array>(o);
-      if (!py::isinstance<py::array_t<float>>(a) || !(a.flags() & py::array::c_style))
-        throw py::value_error(name_ + ": numpy arrays must be C-contiguous float32");
-      if (output && !a.writeable()) throw py::value_error(name_ + ": array is read-only");
-      data_ = static_cast<float*>(a.mutable_data());
-      for (py::ssize_t i = 0; i < a.ndim(); i++) shape_.push_back((size_t)a.shape(i));
-    } else {
-      throw py::type_error(name_ + ": expected a Grid, MGrid, torch tensor or numpy array");
-    }
-    keep_ = o;
-    if ((int)shape_.size() != ndim)
-      throw py::type_error(name_ + ": expected " + std::to_string(ndim) + " dimensions, got " +
-                           std::to_string(shape_.size()));
-    if (!cuda_) staged_.reset(new detail::Staged<float>(data_, size(), !output, output));
-  }
-  size_t size() const {
-    size_t n = 1;
-    for (size_t d : shape_) n *= d;
-    return n;
-  }
-  size_t dim(int i) const { return shape_[i]; }
-  float* dev() const { return cuda_ ? data_ : staged_->get(); }
-  bool cuda() const { return cuda_; }
-  void finish() {
-    if (staged_) staged_->finish();
-  }
-  Grid<float, 1, true> g1() const { return Grid<float, 1, true>(dev(), shape_[0]); }
-  Grid<float, 2, true> g2() const { return Grid<float, 2, true>(dev(), shape_[0], shape_[1]); }
-  Grid<float, 3, true> g3() const { return Grid<float, 3, true>(dev(), shape_[0], shape_[1], shape_[2]); }
-  Grid<float, 4, true> g4() const { return Grid<float, 4, true>(dev(), shape_[0], shape_[1], shape_[2], shape_[3]); }
-  Grid<float, 5, true> g5() const {
-    return Grid<float, 5, true>(dev(), shape_[0], shape_[1], shape_[2], shape_[3], shape_[4]);
-  }
-
- private:
-  std::string name_;
-  bool output_;
-  bool cuda_ = false;
-  float* data_ = nullptr;
-  std::vector<size_t> shape_;
-  py::object keep_;
-  std::unique_ptr<detail::Staged<float>> staged_;
-};
-
-int ndim_of(const py::handle& h) {
-  py::object o = py::reinterpret_borrow<py::object>(h);
-  if (py::hasattr(o, "shape")) return (int)py::len(o.attr("shape"));
-  throw py::type_error("expected an array");
-}
+using namespace lmgpy;
 
 // forward(center, coords, types, radii, grid): index or vector types, single example or batch
 void gm_forward_arrays(const GridMaker& gm, const py::object& center, const py::object& coords,
@@ -177,8 +99,8 @@ PYBIND11_MODULE(molgrid_native, m) {
   m.doc() = "GridMaker, GridInterpolater, Transform, Quaternion and float3 of libmolgrid's gridding path on B200";
 
   m.def("set_random_seed", [](unsigned seed) { set_random_seed(seed); }, py::arg("seed"));
-  m.def("set_gpu_enabled", [](bool on) { g_gpu_enabled = on; });
-  m.def("get_gpu_enabled", []() { return g_gpu_enabled; });
+  m.def("set_gpu_enabled", [](bool on) { gpu_enabled() = on; });
+  m.def("get_gpu_enabled", []() { return gpu_enabled(); });
   m.def("set_gpu_device", [](int dev) { LMG_CUDA_CHECK(cudaSetDevice(dev)); });
   m.def("get_gpu_device", []() {
     int dev = 0;
@@ -226,7 +148,8 @@ PYBIND11_MODULE(molgrid_native, m) {
       .def(py::self /= py::self)
       .def(py::self == py::self);
 
-  py::class_<Transform>(m, "Transform")
+  py::class_<Transform> tr_class(m, "Transform");
+  tr_class
       .def(py::init<>())
       .def(py::init([](const Quaternion& q) { return Transform(q); }))
       .def(py::init([](const Quaternion& q, const py::object& c) { return Transform(q, to_float3(c)); }))
@@ -250,7 +173,8 @@ PYBIND11_MODULE(molgrid_native, m) {
                           bool dotranslate) { transform_apply(t, in, out, dotranslate, false); },
            py::arg("in"), py::arg("out"), py::arg("dotranslate") = true);
 
-  py::class_<GridMaker>(m, "GridMaker")
+  py::class_<GridMaker> gm_class(m, "GridMaker");
+  gm_class
       .def(py::init<float, float, bool, bool, float, float>(), py::arg("resolution") = 0.5f,
            py::arg("dimension") = 23.5f, py::arg("binary") = false, py::arg("radius_type_indexed") = false,
            py::arg("radius_scale") = 1.0f, py::arg("gaussian_radius_multiple") = 1.0f)
@@ -355,4 +279,6 @@ PYBIND11_MODULE(molgrid_native, m) {
              }
              o.finish();
            });
+
+  bind_objects(m, gm_class, tr_class);
 }

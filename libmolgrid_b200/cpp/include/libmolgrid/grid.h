@@ -20,6 +20,12 @@ inline cudaMemcpyKind copy_kind(bool src_gpu, bool dst_gpu) {
   if (src_gpu) return dst_gpu ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost;
   return dst_gpu ? cudaMemcpyHostToDevice : cudaMemcpyHostToHost;
 }
+// bytes from one side to the other; host-to-host copies need no CUDA runtime
+inline void copy_bytes(void* dst, const void* src, size_t bytes, bool src_gpu, bool dst_gpu) {
+  if (!bytes) return;
+  if (!src_gpu && !dst_gpu) std::memcpy(dst, src, bytes);
+  else LMG_CUDA_CHECK(cudaMemcpy(dst, src, bytes, copy_kind(src_gpu, dst_gpu)));
+}
 inline void bounds(size_t i, size_t n) {
   if (i >= n) throw std::out_of_range("Invalid range. " + itoa((long long)i) + " >= " + itoa((long long)n));
 }
@@ -102,13 +108,13 @@ class Grid {
   template <bool destCUDA>
   size_t copyTo(Grid<Dtype, NumDims, destCUDA>& dest) const {
     size_t n = std::min(size(), dest.size());
-    if (n) LMG_CUDA_CHECK(cudaMemcpy(dest.data(), buffer, n * sizeof(Dtype), detail::copy_kind(isCUDA, destCUDA)));
+    detail::copy_bytes(dest.data(), buffer, n * sizeof(Dtype), isCUDA, destCUDA);
     return n;
   }
   template <bool srcCUDA>
   size_t copyFrom(const Grid<Dtype, NumDims, srcCUDA>& src) {
     size_t n = std::min(size(), src.size());
-    if (n) LMG_CUDA_CHECK(cudaMemcpy(buffer, src.data(), n * sizeof(Dtype), detail::copy_kind(srcCUDA, isCUDA)));
+    detail::copy_bytes(buffer, src.data(), n * sizeof(Dtype), srcCUDA, isCUDA);
     return n;
   }
   void fill_zero() {
@@ -174,13 +180,13 @@ class Grid<Dtype, 1, isCUDA> {
   template <bool destCUDA>
   size_t copyTo(Grid<Dtype, 1, destCUDA>& dest) const {
     size_t n = std::min(size(), dest.size());
-    if (n) LMG_CUDA_CHECK(cudaMemcpy(dest.data(), buffer, n * sizeof(Dtype), detail::copy_kind(isCUDA, destCUDA)));
+    detail::copy_bytes(dest.data(), buffer, n * sizeof(Dtype), isCUDA, destCUDA);
     return n;
   }
   template <bool srcCUDA>
   size_t copyFrom(const Grid<Dtype, 1, srcCUDA>& src) {
     size_t n = std::min(size(), src.size());
-    if (n) LMG_CUDA_CHECK(cudaMemcpy(buffer, src.data(), n * sizeof(Dtype), detail::copy_kind(srcCUDA, isCUDA)));
+    detail::copy_bytes(buffer, src.data(), n * sizeof(Dtype), srcCUDA, isCUDA);
     return n;
   }
   void fill_zero() {

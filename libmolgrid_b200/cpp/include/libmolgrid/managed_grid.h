@@ -236,6 +236,8 @@ LMGB200_MGRID_TYPEDEFS(3)
 LMGB200_MGRID_TYPEDEFS(4)
 LMGB200_MGRID_TYPEDEFS(5)
 LMGB200_MGRID_TYPEDEFS(6)
+LMGB200_MGRID_TYPEDEFS(7)
+LMGB200_MGRID_TYPEDEFS(8)
 #undef LMGB200_MGRID_TYPEDEFS
 
 }  // namespace libmolgrid

@@ -1,0 +1,96 @@
+"""``import molgrid``: the reference's usage patterns running on the compiled module's classes
+(C++ host layer), with the real-molecule known answers of test/test_gridmaker.py:72-103 and the
+autograd bindings on top of the compiled GridMaker."""
+import numpy as np
+import pytest
+import torch
+
+from tests.golden.make_golden import molecule_diff
+from tests.test_coord_cache import MOL
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def molgrid():
+    import molgrid
+    return molgrid
+
+
+def golden_example(molgrid):
+    ex = molgrid.Example()
+    ex.coord_sets.append(molgrid.CoordinateSet(MOL["rec_coords"], MOL["rec_types"], MOL["rec_radii"], 14))
+    ex.coord_sets.append(molgrid.CoordinateSet(MOL["lig_coords"], MOL["lig_types"], MOL["lig_radii"], 14))
+    ex.labels = [float(v) for v in MOL["labels"]]
+    return ex
+
+
+def test_classes_come_from_the_compiled_module(molgrid):
+    for name in ("GridInterpolater", "Transform", "Quaternion", "float3", "CoordinateSet", "Example", "ExampleVec",
+                 "Grid4f", "Grid4fCUDA", "MGrid4f", "MGrid5f"):
+        assert getattr(molgrid, name).__module__.endswith("molgrid_native"), name
+    assert issubclass(molgrid.GridMaker, molgrid.native.GridMaker)
+    assert molgrid.Coords2Grid is not None and molgrid.ExampleProvider is not None
+
+
+def test_molecule_known_answers_through_the_compiled_classes(molgrid):
+    ex = golden_example(molgrid)
+    c = ex.coord_sets[1]
+    gmaker = molgrid.GridMaker()
+    dims = gmaker.grid_dimensions(c.max_type)
+    center = tuple(c.center())
+    mgridgpu = molgrid.MGrid4f(*dims)
+    npout = np.zeros(dims, dtype=np.float32)
+    cudaout = torch.zeros(dims, dtype=torch.float32, device="cuda")
+    gmaker.forward(center, c, mgridgpu.gpu())
+    gmaker.forward(center, c, npout)
+    gmaker.forward(center, c, cudaout)
+    newt = gmaker.make_tensor(center, c)
+    assert newt.is_cuda
+    for got in (mgridgpu.tonumpy(), npout, cudaout.cpu().numpy(), newt.cpu().numpy(), gmaker.make_ndarray(center, c)):
+        assert float(got.max()) == pytest.approx(1.438691, abs=2e-6)
+    dims = gmaker.grid_dimensions(ex.num_types())
+    mg = molgrid.MGrid4f(*dims)
+    gmaker.forward(ex, molgrid.Transform(center, 0, False), mg.gpu())
+    g = mg.tonumpy()
+    assert float(g.max()) == pytest.approx(2.094017, abs=2e-6)
+    want = MOL["ex_sample"]
+    got = g.reshape(-1)[MOL["sample"]]
+    assert np.all(np.abs(got - want) <= 1e-6 + 1e-5 * np.abs(want))
+    mg2 = molgrid.MGrid4f(*dims)
+    gmaker.forward(ex, mg2)                        # default centre = the last set's centre
+    np.testing.assert_allclose(mg2.tonumpy(), g, rtol=1e-6, atol=1e-7)
+    batch = torch.zeros((2,) + dims, device="cuda")
+    gmaker.forward(molgrid.ExampleVec([ex, ex]), batch, 0.0, random_rotation=False)
+    np.testing.assert_allclose(batch[1].cpu().numpy(), g, rtol=1e-6, atol=1e-7)
+
+    m = ex.merge_coordinates()
+    diff = torch.from_numpy(molecule_diff(gmaker.grid_dimensions(28))).cuda()
+    grad = molgrid.MGrid2f(m.size(), 3)
+    gmaker.backward(tuple(MOL["center"]), m, diff, grad.gpu())
+    got, want = grad.tonumpy(), MOL["backward"]
+    assert np.all(np.abs(got - want) <= 1e-5 + 1e-4 * np.abs(want))
+
+
+def test_autograd_on_the_compiled_gridmaker(molgrid):
+    """Coords2Grid over molgrid.GridMaker: the values and gradients of the Python layer's own."""
+    import libmolgrid_b200 as layer
+    rng = np.random.default_rng(4)
+    B, N, T = 2, 30, 4
+    coords = torch.tensor(rng.uniform(-4, 4, (B, N, 3)), dtype=torch.float32, device="cuda")
+    types = torch.tensor(rng.dirichlet(np.ones(T), (B, N)), dtype=torch.float32, device="cuda")
+    radii = torch.tensor(rng.uniform(1, 2, (B, N)), dtype=torch.float32, device="cuda")
+    results = []
+    for mod in (molgrid, layer):
+        gm = mod.GridMaker(resolution=0.5, dimension=11.5)
+        c = coords.clone().requires_grad_(True)
+        t = types.clone().requires_grad_(True)
+        out = mod.Coords2Grid(gm, center=(0, 0, 0))(c, t, radii)
+        w = torch.linspace(0, 1, out.numel(), device="cuda").view(out.shape)
+        (out * w).sum().backward()
+        results.append((out.detach(), c.grad, t.grad))
+        single = mod.Coords2Grid(gm, center=(0, 0, 0))(coords[0], types[0], radii[0])
+        assert torch.allclose(single, out[0].detach(), rtol=1e-5, atol=1e-6)
+    for a, b in zip(*results):
+        assert torch.allclose(a, b, rtol=1e-5, atol=1e-6)
+    assert float(results[0][1].abs().max()) > 0

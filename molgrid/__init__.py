@@ -70,7 +70,9 @@ class GridMaker(native.GridMaker):
         return bool(args) and isinstance(args[0], _DeviceBatch)
 
     def forward(self, *args, **kw):
-        if self._extension(args, kw):
+        # a batch of arrays about one common centre given as a tuple is this library's shorthand
+        one_centre = len(args) > 1 and _ndim(args[1]) == 3 and _ndim(args[0]) < 0
+        if self._extension(args, kw) or one_centre:
             return self._twin().forward(*args, **kw)
         return native.GridMaker.forward(self, *args, **kw)
 

@@ -175,5 +175,10 @@ def test_examplevec_labels():
 
 def test_reference_module_name():
     import molgrid as mg
-    assert mg.GridMaker is molgrid.GridMaker and mg.MGrid4f is molgrid.MGrid4f
-    assert mg.Coords2Grid is molgrid.Coords2Grid and mg.ExampleProvider is molgrid.ExampleProvider
+    from libmolgrid_b200 import molgrid_native
+    # the compiled classes where the compiled module defines them ...
+    assert issubclass(mg.GridMaker, molgrid_native.GridMaker) and mg.MGrid4f is molgrid_native.MGrid4f
+    assert mg.CoordinateSet is molgrid_native.CoordinateSet and mg.Transform is molgrid_native.Transform
+    # ... the Python layer for the rest
+    assert mg.Coords2Grid is molgrid.Coords2Grid and issubclass(mg.ExampleProvider, molgrid.ExampleProvider)
+    assert mg.FileMappedGninaTyper is molgrid.FileMappedGninaTyper

@@ -48,6 +48,7 @@ def main():
                                       "backward_vector,backward_gradients,onehot_forward,onehot_backward,onehot_gradgrad,interpolate,"
                                       "provider")
     ap.add_argument("--interp-batch", type=int, default=48)
+    ap.add_argument("--onehot-batch", type=int, default=50, help="smaller for a profiler capture")
     args = ap.parse_args()
     import torch
     import libmolgrid_b200 as lmg
@@ -164,7 +165,7 @@ def main():
 
     # ---- vector types with per-atom radii (the autograd bindings' layout), 48^3 -------------------
     if set(ops) & {"onehot_forward", "onehot_backward", "onehot_gradgrad"}:
-        B = 50
+        B = args.onehot_batch
         coords, types, radii, ns, tr = cases.blob_batch(1001, B, 2000, 4000, T)
         tv = np.zeros(types.shape + (T,), np.float32)
         np.put_along_axis(tv, types.astype(np.int64)[..., None], 1.0, axis=2)
@@ -177,7 +178,7 @@ def main():
         tg = torch.empty((B, coords.shape[1], T), device=dev)
         natoms = float(ns.sum())
         gb = grid.numel() * 4
-        wl = "one-hot type vectors, per-atom radii, 28x48^3, batch 50 x [2000,4000] atoms"
+        wl = "one-hot type vectors, per-atom radii, 28x48^3, batch %d x [2000,4000] atoms" % B
         if "onehot_forward" in ops:
             report("onehot_forward", wl,
                    timeit(lambda: g.forward(cen, dc, dtv, dr, grid, transforms=dtr, n_atoms=dn)),

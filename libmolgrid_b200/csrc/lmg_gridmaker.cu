@@ -1225,21 +1225,143 @@ __global__ void __launch_bounds__(QS_WARPS * 32) k_forward_quads_atom(BwdArgs G)
 
 // Backward for the same layout: atom gradient = sum over voxels of s * delta * (sum_t w_t diff_t),
 // type gradient of EVERY channel = sum over voxels of density * diff_t (src/grid_maker.cpp:508-517).
-// A lane keeps the type gradients of a round's channels in registers; rounds of VA_BCH channels.
-constexpr int VA_BCH = 16;
+// A lane keeps the type gradients of a round's channels in registers; rounds of VA_BCH channels,
+// the quads of VA_LD channels requested together.  The kernel waits on those loads (they come from
+// L2: every channel is read under every footprint), so what counts is how many are in flight per SM:
+// registers per warp against loads per warp.  Measured per batch of 50 (28 channels, one-hot types):
+// rounds of 16 with 4 loads together 2.79 ms, 8 / 8 2.08 ms, 14 / 7 1.82 ms, 14 / 14 1.70 ms,
+// 16 / 16 2.17 ms, 28 / 14 2.05 ms; capping the registers below what the compiler picks, blocks of
+// several warps, or atoms sorted by cell (for L1 reuse between neighbours) change nothing or lose.
+#ifndef LMG_VA_BCH
+#define LMG_VA_BCH 14
+#endif
+constexpr int VA_BCH = LMG_VA_BCH;
+#ifndef LMG_VA_LD
+#define LMG_VA_LD 14
+#endif
+constexpr int VA_LD = LMG_VA_LD;  // channels whose quads are requested together
+static_assert(VA_BCH % VA_LD == 0, "a round is a whole number of load batches");
+static_assert(VA_BCH <= 32, "a lane per channel of a round reads the weights");
+#ifndef LMG_VA_WARPS
+#define LMG_VA_WARPS BWD2_WARPS
+#endif
+constexpr int VA_WARPS = LMG_VA_WARPS;
+#ifndef LMG_VA_REREAD
+#define LMG_VA_REREAD 2
+#endif
+constexpr int VA_REREAD = LMG_VA_REREAD;  // weighted channels of a round up to which they are re-read from a list
+
+// per-warp shared state of the kernel below
+struct VaShared {
+  ColBufD buf;
+  float w[VA_BCH];   // weights of the round's channels
+  int nz_t[VA_BCH];  // the weighted ones: channel (relative to the round) and weight
+  float nz_w[VA_BCH];
+};
+
+// One round of k_backward_quads_atom: channels [tb, tb + nch) under the whole footprint of the atom.
+// Lanes as (column, z-quad): the lanes of a column read neighbouring 16-byte pieces of one line in
+// every channel, a quarter of the lines a lane-per-column load touches.  The sum over weighted
+// channels that the atom gradient needs is taken inside the channel loop when many channels of the
+// round carry weight (DENSE), and from a re-read of the few that do otherwise (one-hot types: one
+// extra load per quad in one round, nothing in the others).
+template <bool BINARY, bool DENSE>
+__device__ __forceinline__ void va_round(const BwdArgs& G, const ItemParams& P, VaShared& sh, const float* diffb,
+                                         int tb, int nch, int nnz, float ox, float oy, float oz,
+                                         float (&tgacc)[VA_BCH], float& agx, float& agy, float& agz, int lane) {
+  const GMParams& gm = G.gm;
+  const size_t dim = gm.dim;
+  const size_t cs4 = dim * dim * dim / 4;  // channel stride in quads
+  const float Tcull = fmaxf(P.Tcut, BINARY ? P.Tbin : -1.f);
+  const float kexp = P.inv_ar2 * NEG2_LOG2E;
+  const float k4 = 4.f * P.inv_ar2, kD = -gm.D * P.inv_ar2, kE = -gm.E * P.inv_ar;
+  const float ta = gm.ta, ntb = -gm.tb;
+  const unsigned span = quad_span(P);
+  ColBufD& buf = sh.buf;
+  unsigned nx = P.hix - P.lox, ny = P.hiy - P.loy;
+  unsigned ncols = nx * ny;
+  float inv_ny = 1.f / (float)ny;
+  for (unsigned cbase = 0; cbase < ncols;) {
+    unsigned nkept = compact_columns<ColBufD, true>(buf, P, cbase, ncols, ny, inv_ny, Tcull, ox, oy, gm.res,
+                                                    gm.dim, lane);
+    __syncwarp();
+    auto quad = [&](unsigned i, float dxy2, float exy, const float (&d2v)[4], const float (&ev)[4],
+                    const float (&dzv)[4], size_t off) {
+      float v[4], dsum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float rsq = __fadd_rn(dxy2, d2v[j]);
+        if (BINARY) {
+          v[j] = rsq < P.Tbin ? 1.f : 0.f;
+        } else {
+          float tq = fminf(fmaf(ta, sqrt_approx(rsq * P.inv_ar2), ntb), 0.f);
+          float val = rsq <= P.Tg ? exy * ev[j] : tq * tq;
+          v[j] = rsq <= P.Tcut ? val : 0.f;
+        }
+      }
+      const float4* qp = reinterpret_cast<const float4*>(diffb + off) + (size_t)tb * cs4;
+#pragma unroll
+      for (int c4 = 0; c4 < VA_BCH; c4 += VA_LD) {
+        if (c4 >= nch) break;
+        // a batch of channels requested together, then used
+        float4 dv[VA_LD];
+#pragma unroll
+        for (int u = 0; u < VA_LD; u++) {
+          dv[u] = (c4 + u < nch) ? __ldg(qp) : make_float4(0.f, 0.f, 0.f, 0.f);
+          qp += cs4;
+        }
+#pragma unroll
+        for (int u = 0; u < VA_LD; u++) {
+          tgacc[c4 + u] = fmaf(v[0], dv[u].x, fmaf(v[1], dv[u].y, fmaf(v[2], dv[u].z,
+                               fmaf(v[3], dv[u].w, tgacc[c4 + u]))));
+          if (DENSE) {
+            float wk = sh.w[c4 + u];
+            dsum[0] = fmaf(wk, dv[u].x, dsum[0]);
+            dsum[1] = fmaf(wk, dv[u].y, dsum[1]);
+            dsum[2] = fmaf(wk, dv[u].z, dsum[2]);
+            dsum[3] = fmaf(wk, dv[u].w, dsum[3]);
+          }
+        }
+      }
+      if (!DENSE) {
+        if (nnz == 0) return;  // the same for every lane
+        const float4* q0 = reinterpret_cast<const float4*>(diffb + off) + (size_t)tb * cs4;
+        for (int k = 0; k < nnz; k++) {
+          float4 d = __ldg(q0 + (size_t)sh.nz_t[k] * cs4);
+          float wk = sh.nz_w[k];
+          dsum[0] = fmaf(wk, d.x, dsum[0]);
+          dsum[1] = fmaf(wk, d.y, dsum[1]);
+          dsum[2] = fmaf(wk, d.z, dsum[2]);
+          dsum[3] = fmaf(wk, d.w, dsum[3]);
+        }
+      }
+      float fsum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float rsq = __fadd_rn(dxy2, d2v[j]);
+        float s1 = rsq <= P.Tg ? k4 * (exy * ev[j]) : fmaf(kE, rsqrt_approx(rsq), kD);
+        float f = (rsq <= P.Tcut ? s1 : 0.f) * dsum[j];
+        fsum += f;
+        agz = fmaf(f, dzv[j], agz);
+      }
+      agx = fmaf(fsum, buf.dx[i], agx);
+      agy = fmaf(fsum, buf.dy[i], agy);
+    };
+    qlane_sweep_span(span, P, buf, nkept, dim, oz, gm.res, kexp, Tcull, lane, quad);
+    __syncwarp();
+  }
+}
 
 template <bool BINARY>
-__global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads_atom(BwdArgs G) {
-  __shared__ ColBufD bufs[BWD2_WARPS];
-  __shared__ ZTabs ztabs[BWD2_WARPS];
+__global__ void __launch_bounds__(VA_WARPS * 32) k_backward_quads_atom(BwdArgs G) {
+  __shared__ VaShared shs[VA_WARPS];
   const GMParams& gm = G.gm;
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  int item = blockIdx.x * BWD2_WARPS + wid;
+  int item = blockIdx.x * VA_WARPS + wid;
   int bl = blockIdx.y;
   int b = G.b0 + bl;
   if (item >= G.N) return;
-  ColBufD& buf = bufs[wid];
-  ZTabs& zt = ztabs[wid];
+  VaShared& sh = shs[wid];
 
   float cx, cy, cz;
   if (G.centers != nullptr) {
@@ -1250,99 +1372,32 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads_atom(BwdArgs
   float ox = __fsub_rn(cx, gm.half), oy = __fsub_rn(cy, gm.half), oz = __fsub_rn(cz, gm.half);
   ItemParams P = load_item<false>(G, bl, b, item, ox, oy, oz);
 
-  size_t dim = gm.dim;
-  const size_t chan_stride = dim * dim * dim;
+  const size_t chan_stride = (size_t)gm.dim * gm.dim * gm.dim;
   const float* diffb = G.diff + (size_t)b * G.T * chan_stride;
   const size_t ai = (size_t)b * G.N + item;
   const float* wrow = G.type_vector + ai * G.T;
-  const float Tcull = fmaxf(P.Tcut, BINARY ? P.Tbin : -1.f);
-  const float kexp = P.inv_ar2 * NEG2_LOG2E;
-  const float k4 = 4.f * P.inv_ar2, kD = -gm.D * P.inv_ar2, kE = -gm.E * P.inv_ar;
-  const float ta = gm.ta, ntb = -gm.tb;
   float agx = 0.f, agy = 0.f, agz = 0.f;
 
   for (int tb = 0; tb < G.T; tb += VA_BCH) {
     const int nch = min(VA_BCH, G.T - tb);
-    float wch[VA_BCH], tgacc[VA_BCH];
+    float tgacc[VA_BCH];
 #pragma unroll
-    for (int c = 0; c < VA_BCH; c++) {
-      wch[c] = c < nch ? wrow[tb + c] : 0.f;
-      tgacc[c] = 0.f;
-    }
+    for (int c = 0; c < VA_BCH; c++) tgacc[c] = 0.f;
     if (P.valid) {
-      unsigned nx = P.hix - P.lox, ny = P.hiy - P.loy;
-      unsigned ncols = nx * ny;
-      float inv_ny = 1.f / (float)ny;
-      for (unsigned cbase = 0; cbase < ncols;) {
-        unsigned nkept = compact_columns<ColBufD, true>(buf, P, cbase, ncols, ny, inv_ny, Tcull, ox, oy,
-                                                        gm.res, gm.dim, lane);
-        for (unsigned zc = P.loz & ~3u; zc < P.hiz; zc += 4 * QPASS) {
-          __syncwarp();
-          fill_ztabs(zt, zc, P, oz, gm.res, kexp, lane);
-          __syncwarp();
-          unsigned nq = min((unsigned)QPASS, (P.hiz - zc + 3) >> 2);
-          for (unsigned c0 = 0; c0 < nkept; c0 += 32) {
-            unsigned i = c0 + lane;
-            bool have = i < nkept;
-            float dxy2 = have ? buf.dxy2[i] : CUDART_NAN_F;
-            float dx = have ? buf.dx[i] : 0.f, dy = have ? buf.dy[i] : 0.f;
-            const float* row = diffb + (size_t)(have ? buf.row[i] : 0u) * dim + zc;
-            float exy = ex2_approx(dxy2 * kexp);
-            float fsum = 0.f;
-            for (unsigned q = 0; q < nq; q++) {
-              float4 d2 = zt.dz2[q], e = zt.ez[q], dz = zt.dz[q];
-              float lo = fminf(fminf(d2.x, d2.y), fminf(d2.z, d2.w));  // fminf skips the NaN entries
-              if (!(__fadd_rn(dxy2, lo) <= Tcull)) continue;            // no voxel of this lane's quad
-              float d2v[4] = {d2.x, d2.y, d2.z, d2.w}, ev[4] = {e.x, e.y, e.z, e.w};
-              float dzv[4] = {dz.x, dz.y, dz.z, dz.w};
-              float v[4], sg[4], dsum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-              for (int j = 0; j < 4; j++) {
-                float rsq = __fadd_rn(dxy2, d2v[j]);
-                float g = exy * ev[j];
-                float s1 = rsq <= P.Tg ? k4 * g : fmaf(kE, rsqrt_approx(rsq), kD);
-                sg[j] = rsq <= P.Tcut ? s1 : 0.f;
-                if (BINARY) {
-                  v[j] = rsq < P.Tbin ? 1.f : 0.f;
-                } else {
-                  float tq = fminf(fmaf(ta, sqrt_approx(rsq * P.inv_ar2), ntb), 0.f);
-                  float val = rsq <= P.Tg ? g : tq * tq;
-                  v[j] = rsq <= P.Tcut ? val : 0.f;
-                }
-              }
-              const float4* qp = reinterpret_cast<const float4*>(row) + q;
-#pragma unroll
-              for (int c4 = 0; c4 < VA_BCH; c4 += 4) {
-                // four channels requested together, then used
-                float4 dv[4];
-#pragma unroll
-                for (int u = 0; u < 4; u++)
-                  dv[u] = (c4 + u < nch) ? __ldg(qp + (size_t)(tb + c4 + u) * (chan_stride / 4))
-                                         : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                  float wk = wch[c4 + u];
-                  tgacc[c4 + u] = fmaf(v[0], dv[u].x, fmaf(v[1], dv[u].y, fmaf(v[2], dv[u].z,
-                                       fmaf(v[3], dv[u].w, tgacc[c4 + u]))));
-                  dsum[0] = fmaf(wk, dv[u].x, dsum[0]);
-                  dsum[1] = fmaf(wk, dv[u].y, dsum[1]);
-                  dsum[2] = fmaf(wk, dv[u].z, dsum[2]);
-                  dsum[3] = fmaf(wk, dv[u].w, dsum[3]);
-                }
-              }
-#pragma unroll
-              for (int j = 0; j < 4; j++) {
-                float f = sg[j] * dsum[j];
-                fsum += f;
-                agz = fmaf(f, dzv[j], agz);
-              }
-            }
-            agx = fmaf(fsum, dx, agx);
-            agy = fmaf(fsum, dy, agy);
-          }
-        }
-        __syncwarp();
+      // the round's weights, and the list of the channels that carry one
+      __syncwarp();
+      float w = lane < nch ? wrow[tb + lane] : 0.f;
+      unsigned m = __ballot_sync(0xffffffffu, w != 0.f);
+      if (lane < VA_BCH) sh.w[lane] = w;
+      if (w != 0.f) {
+        int k = __popc(m & ((1u << lane) - 1u));
+        sh.nz_t[k] = lane;
+        sh.nz_w[k] = w;
       }
+      __syncwarp();
+      int nnz = __popc(m);
+      if (nnz > VA_REREAD) va_round<BINARY, true>(G, P, sh, diffb, tb, nch, nnz, ox, oy, oz, tgacc, agx, agy, agz, lane);
+      else va_round<BINARY, false>(G, P, sh, diffb, tb, nch, nnz, ox, oy, oz, tgacc, agx, agy, agz, lane);
     }
     // type gradients of this round
 #pragma unroll
@@ -1758,9 +1813,10 @@ cudaError_t launch_backward(const BwdArgs& G, int mode, cudaStream_t st) {
   } else if (mode == 1 && quads && !G.gm.rti) {
     // per-atom radii: one work item per atom writes both gradients, no reduction over channels after it
     dim3 ga((unsigned)((G.N + BWD2_WARPS - 1) / BWD2_WARPS), G.nb);
+    dim3 gv((unsigned)((G.N + VA_WARPS - 1) / VA_WARPS), G.nb);
     if (G.type_gradients == nullptr) k_backward_quads_atom_ag<<<ga, BWD2_WARPS * 32, 0, st>>>(G);
-    else if (bin) k_backward_quads_atom<true><<<ga, BWD2_WARPS * 32, 0, st>>>(G);
-    else k_backward_quads_atom<false><<<ga, BWD2_WARPS * 32, 0, st>>>(G);
+    else if (bin) k_backward_quads_atom<true><<<gv, VA_WARPS * 32, 0, st>>>(G);
+    else k_backward_quads_atom<false><<<gv, VA_WARPS * 32, 0, st>>>(G);
   } else if (mode == 1 && quads && G.type_gradients == nullptr) {
     // radii by channel, no type gradients wanted: only the weighted channels of each atom
     dim3 ga((unsigned)(((long)G.N * nz_groups(G.T) + BWD2_WARPS - 1) / BWD2_WARPS), G.nb);

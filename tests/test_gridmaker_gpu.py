@@ -391,3 +391,27 @@ def test_backward_vector_without_type_gradients(port, kw, rti):
     grad_close(ag.cpu().numpy(), wag, "atom gradients")
     grad_close(tg.cpu().numpy(), wtg, "type gradients")
     grad_close(only.cpu().numpy(), wag, "atom gradients alone")
+
+
+@pytest.mark.parametrize("binary", [False, True])
+def test_backward_vector_rounds_of_channels(port, binary):
+    """Per-atom radii with 28 channels: the kernel takes the channels in rounds, and a round may hold
+    no weighted channel of an atom, one or two (one-hot and two-hot types) or many."""
+    g, og = gm_pair(port, resolution=0.5, dimension=11.5, binary=binary)
+    T, N = 28, 120
+    coords, tv, radii = cases.vector_case(21, N, T, 6.5)
+    rng = np.random.default_rng(3)
+    tv[:40] = 0
+    tv[np.arange(40), rng.integers(0, T, 40)] = 1.0                 # one-hot
+    tv[40:80] = 0
+    for a in range(40, 80):                                         # two channels, often in one round
+        c = rng.integers(0, T - 1)
+        tv[a, c], tv[a, c + 1] = 0.25, 0.75
+    tv[80:90] = rng.uniform(0.1, 1.0, (10, T)).astype(np.float32)   # every channel weighted
+    diff = rng.normal(size=g.grid_dimensions(T)).astype(np.float32)
+    wag, wtg = port.backward_vector(og, (0, 0, 0), coords, tv, radii, diff)
+    ag = torch.full((N, 3), 9.0, device="cuda")
+    tg = torch.full((N, T), 9.0, device="cuda")
+    g.backward((0, 0, 0), dev(coords), dev(tv), dev(radii), dev(diff), ag, tg)
+    grad_close(ag.cpu().numpy(), wag, "atom gradients")
+    grad_close(tg.cpu().numpy(), wtg, "type gradients")

@@ -157,16 +157,24 @@ __global__ void __launch_bounds__(256) k_interpolate(InterpArgs I) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Tiled interpolation: a block owns an 8x8x8 tile of output voxels.  The input voxels that tile can
-// touch form a box of at most 16x16x20 (the rotated tile's bounding box, z rounded down to a
-// 16-byte boundary).  One elected thread brings that box of channel c into shared memory with a
-// single tensor copy (cp.async.bulk.tensor, zero fill outside the grid = the reference's zero
-// padding) whose extents are, per axis, the smallest of a few fixed sizes that hold the tile (one
-// tensor map per combination).  Two channels are in flight, and the 256 threads blend their two
-// voxels each from shared memory.  The blend arithmetic is that of the direct kernel.  Every wait
-// on a copy is bounded; a wait that runs out makes the block finish its tile through the direct
-// reads.  (Staging the box one x plane per copy, which needs fewer maps and fewer bytes, is slower:
-// 1.08 against 0.83 ms per 48 examples - the copy engine works row by row and per copy.)
+// Tiled interpolation: a block owns an ITILE^3 tile of output voxels (12^3).  The input voxels that
+// tile can touch form a box (the rotated tile's bounding box, z rounded down to a 16-byte
+// boundary).  One elected thread brings that box of channel c into shared memory with a single
+// tensor copy (cp.async.bulk.tensor, zero fill outside the grid = the reference's zero padding)
+// whose extents are, per axis, the smallest of a few fixed sizes that hold the tile (one tensor map
+// per combination).  The staging area of a block is cut into as many slots as boxes of its extents
+// fit (two to three on average, one for the few tiles that need the largest box), and each thread
+// blends its voxels of the channel from shared memory.  The blend arithmetic is that of the direct
+// kernel.  Every wait on a copy is bounded; a wait that runs out makes the block finish its tile
+// through the direct reads.
+// Measured per 48 examples of 28 x 48^3 with random rotations: tiles of 8^3 with 256 threads 0.683
+// ms, 16^3 with 512 threads 0.644 ms, 12^3 with 432 threads and two blocks per SM 0.574 ms.  The
+// number of slots (2 to 6) changes nothing: the kernel issues instructions 55 % of the time (about
+// 65 per voxel and channel: 8 shared loads, 21 roundings of the blend, addresses) and its shared
+// loads see three-way bank conflicts on average, which no row pitch that a tensor copy can write
+// (multiples of 16 bytes) avoids for every rotation.  (Staging the box one x plane per copy, which
+// needs fewer maps and fewer bytes, is slower: 1.08 against 0.83 ms - the copy engine works row by
+// row and per copy.)
 // ---------------------------------------------------------------------------------------------
 __device__ unsigned g_tma_timeouts = 0;
 
@@ -206,16 +214,40 @@ __device__ __forceinline__ void tma_load_box(float* dst, const CUtensorMap* map,
       : "memory");
 }
 
+#ifndef LMG_INTERP_THREADS
+#define LMG_INTERP_THREADS 432
+#endif
 #ifndef LMG_INTERP_MINBLOCKS
-#define LMG_INTERP_MINBLOCKS 4
+#define LMG_INTERP_MINBLOCKS 2
 #endif
-#ifndef LMG_INTERP_STAGES
-#define LMG_INTERP_STAGES 2
+#ifndef LMG_INTERP_MAXSTAGES
+#define LMG_INTERP_MAXSTAGES 4
 #endif
-constexpr int ISTAGES = LMG_INTERP_STAGES;  // channels whose boxes are in flight or in use per block
-__global__ void __launch_bounds__(256, LMG_INTERP_MINBLOCKS) k_interpolate_tiled(const __grid_constant__ InterpMaps maps, InterpArgs I) {
-  __shared__ __align__(128) float box[ISTAGES][ITILE_BOX];
-  __shared__ __align__(8) uint64_t bar[ISTAGES];
+constexpr int INT = LMG_INTERP_THREADS;                 // threads per block
+constexpr int IVPT = ITILE * ITILE * ITILE / INT;       // voxels per thread
+static_assert(IVPT * INT == ITILE * ITILE * ITILE, "the threads of a block share the tile evenly");
+constexpr int IMAXST = LMG_INTERP_MAXSTAGES;            // most boxes in flight or in use per block
+#ifndef LMG_INTERP_RING
+#define LMG_INTERP_RING 28160  // 110 KB: two blocks per SM
+#endif
+constexpr int IRING = LMG_INTERP_RING;                  // floats of staging per block
+static_assert(IMAXST >= 1 && IRING >= ITILE_BOX && IRING % 32 == 0, "the staging area holds at least one box");
+static_assert(ITILE_BX * ITILE_BY * ITILE_BZ < (1 << 15) && ITILE_BY * ITILE_BZ < (1 << 10) && ITILE_BZ < (1 << 6),
+              "a voxel's offsets into the box are packed into one word each");
+
+// What a thread keeps per voxel between the channels: the offset of corner (xl, yl, zl) in the box,
+// the steps to the upper corners (zero where floor == ceil) packed as sx | sy << 10 | sz << 16, and
+// the three upper weights.
+struct InterpVoxel {
+  int base;
+  unsigned steps;
+  float xd, yd, zd;
+};
+
+__global__ void __launch_bounds__(INT, LMG_INTERP_MINBLOCKS) k_interpolate_tiled(const __grid_constant__ InterpMaps maps, InterpArgs I) {
+  // the staging area is cut into as many slots as boxes of this block's extents fit
+  extern __shared__ __align__(128) float ring[];
+  __shared__ __align__(8) uint64_t bar[IMAXST];
   const int tid = threadIdx.x, bl = blockIdx.y;
   const InterpExample& E = I.ex[bl];
   const unsigned od = I.out_dim;
@@ -253,95 +285,122 @@ __global__ void __launch_bounds__(256, LMG_INTERP_MINBLOCKS) k_interpolate_tiled
     int nx = (int)ceilf(hi[0] + 0.01f) - bx0 + 1, ny = (int)ceilf(hi[1] + 0.01f) - by0 + 1,
         nz = (int)ceilf(hi[2] + 0.01f) - bz0 + 1;
     tiled = nx <= ITILE_BX && ny <= ITILE_BY && nz <= ITILE_BZ;
-    int ix = nx <= 10 ? 0 : nx <= 12 ? 1 : nx <= 14 ? 2 : 3;
-    int iy = ny <= 10 ? 0 : ny <= 12 ? 1 : ny <= 14 ? 2 : 3;
-    int iz = nz <= 12 ? 0 : nz <= 16 ? 1 : 2;
-    BX = 10 + 2 * ix;
-    BY = 10 + 2 * iy;
-    BZ = 12 + 4 * iz;
+    int ix = nx <= ITILE_XY0 ? 0 : (nx - ITILE_XY0 + ITILE_XYSTEP - 1) / ITILE_XYSTEP;
+    int iy = ny <= ITILE_XY0 ? 0 : (ny - ITILE_XY0 + ITILE_XYSTEP - 1) / ITILE_XYSTEP;
+    int iz = nz <= ITILE_Z0 ? 0 : (nz - ITILE_Z0 + 3) / 4;
+    BX = itile_xy(ix);
+    BY = itile_xy(iy);
+    BZ = itile_z(iz);
     mapi = (ix * ITILE_NXY + iy) * ITILE_NZ + iz;
   }
 
-  // this thread's two voxels
+  // this thread's voxels
   const int id = (int)I.in_dim;
   const size_t ichan = (size_t)id * id * id, ochan = (size_t)od * od * od;
   const size_t b = (size_t)I.b0 + bl;
   const float* in = I.in + b * I.K * ichan;
   float* outb = I.out + b * I.K * ochan;
-  InterpCell C[2];
-  size_t ov[2];
-  bool live[2];
-  int base[2], sx[2], sy[2], sz[2];
+  InterpVoxel V[IVPT];
+  unsigned livemask = 0;
+  static_assert(INT % (ITILE * ITILE) == 0, "a thread's voxels differ in the slowest index only");
+  // voxel u of this thread: (i0 + u * INT / ITILE^2, j0, k0) within the tile
+  const unsigned i0 = ti * ITILE + tid / (ITILE * ITILE), j0 = tj * ITILE + (tid / ITILE) % ITILE,
+                 k0 = tk * ITILE + tid % ITILE;
+  const size_t ov0 = ((size_t)i0 * od + j0) * od + k0;
+  const size_t ovstep = (size_t)(INT / (ITILE * ITILE)) * od * od;
 #pragma unroll
-  for (int u = 0; u < 2; u++) {
-    int o = tid + 256 * u;
-    unsigned i = ti * ITILE + (o >> 6), j = tj * ITILE + ((o >> 3) & 7), k = tk * ITILE + (o & 7);
-    live[u] = i < od && j < od && k < od;
+  for (int u = 0; u < IVPT; u++) {
+    unsigned i = i0 + u * (INT / (ITILE * ITILE));
+    bool live = i < od && j0 < od && k0 < od;
     float gx, gy, gz;
-    interp_point(I, F, min(i, od - 1), min(j, od - 1), min(k, od - 1), gx, gy, gz);
-    C[u] = interp_cell(gx, gy, gz);
-    ov[u] = ((size_t)i * od + j) * od + k;
-    base[u] = ((C[u].xl - bx0) * BY + (C[u].yl - by0)) * BZ + (C[u].zl - bz0);
-    sx[u] = (C[u].xh - C[u].xl) * BY * BZ;
-    sy[u] = (C[u].yh - C[u].yl) * BZ;
-    sz[u] = C[u].zh - C[u].zl;
+    interp_point(I, F, min(i, od - 1), min(j0, od - 1), min(k0, od - 1), gx, gy, gz);
+    InterpCell C = interp_cell(gx, gy, gz);
+    V[u].base = ((C.xl - bx0) * BY + (C.yl - by0)) * BZ + (C.zl - bz0);
+    V[u].steps = (unsigned)((C.xh - C.xl) * BY * BZ) | (unsigned)((C.yh - C.yl) * BZ) << 10 |
+                 (unsigned)(C.zh - C.zl) << 16;
+    V[u].xd = C.xd; V[u].yd = C.yd; V[u].zd = C.zd;
     // belt and braces: a corner outside the staged box sends the whole block down the direct path
-    bool inside = C[u].xl >= bx0 && C[u].xh < bx0 + BX && C[u].yl >= by0 && C[u].yh < by0 + BY &&
-                  C[u].zl >= bz0 && C[u].zh < bz0 + BZ;
-    if (live[u] && !inside) tiled = false;
+    bool inside = C.xl >= bx0 && C.xh < bx0 + BX && C.yl >= by0 && C.yh < by0 + BY &&
+                  C.zl >= bz0 && C.zh < bz0 + BZ;
+    if (live && !inside) tiled = false;
+    if (live) livemask |= 1u << u;
+    if (!live) {  // reads the first word of the box, stores nothing
+      V[u].base = 0;
+      V[u].steps = 0;
+    }
   }
   tiled = __syncthreads_and(tiled) != 0;
 
   int c = 0;
   if (tiled) {
     const int chan0 = (int)(b * I.K);
+    const int slot = (BX * BY * BZ + 31) & ~31;  // floats from box to box: 128-byte boundaries
+    const int nst = min(IMAXST, IRING / slot);
     if (tid == 0) {
-      for (int s = 0; s < ISTAGES; s++) mbar_init(&bar[s], 1);
+      for (int s = 0; s < IMAXST; s++) mbar_init(&bar[s], 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
     const CUtensorMap* map = &maps.m[mapi];
     auto stage = [&](int s, int chan) {
       mbar_expect_tx(&bar[s], (unsigned)(BX * BY * BZ) * (unsigned)sizeof(float));
-      tma_load_box(box[s], map, &bar[s], bz0, by0, bx0, chan);
+      tma_load_box(ring + s * slot, map, &bar[s], bz0, by0, bx0, chan);
     };
     if (tid == 0) {
-      for (int s = 0; s < ISTAGES && s < I.K; s++) stage(s, chan0 + s);
+      for (int s = 0; s < nst && s < I.K; s++) stage(s, chan0 + s);
     }
-    int inflight = min(ISTAGES, I.K);
-    for (; c < I.K; c++) {
-      const int s = c % ISTAGES;
-      bool ok = mbar_wait_bounded(&bar[s], (c / ISTAGES) & 1);
+    int inflight = min(nst, I.K);
+    int s = 0;
+    unsigned phase = 0;
+    float* oc = outb + ov0;  // this thread's first voxel in channel c
+    for (; c < I.K; c++, oc += ochan) {
+      bool ok = mbar_wait_bounded(&bar[s], phase);
       if (__syncthreads_or(!ok)) break;  // a copy did not arrive: finish through the direct reads
       inflight--;
-      const float* sm = box[s];
+      const float* sm = ring + s * slot;
 #pragma unroll
-      for (int u = 0; u < 2; u++) {
-        if (!live[u]) continue;
-        const float* p = sm + base[u];
-        float res = interp_blend(C[u], p[0], p[sz[u]], p[sy[u]], p[sy[u] + sz[u]], p[sx[u]], p[sx[u] + sz[u]],
-                                 p[sx[u] + sy[u]], p[sx[u] + sy[u] + sz[u]]);
-        __stcs(outb + c * ochan + ov[u], res);
+      for (int u = 0; u < IVPT; u++) {
+        const float* p = sm + V[u].base;
+        const int sx = (int)(V[u].steps & 1023u), sy = (int)(V[u].steps >> 10 & 63u), sz = (int)(V[u].steps >> 16);
+        InterpCell C;
+        C.xd = V[u].xd; C.yd = V[u].yd; C.zd = V[u].zd;
+        C.xm = __fsub_rn(1.f, C.xd); C.ym = __fsub_rn(1.f, C.yd); C.zm = __fsub_rn(1.f, C.zd);
+        float res = interp_blend(C, p[0], p[sz], p[sy], p[sy + sz], p[sx], p[sx + sz], p[sx + sy], p[sx + sy + sz]);
+        if (livemask >> u & 1u) __stcs(oc + u * ovstep, res);
       }
-      __syncthreads();  // everyone is done with box[s] before it is refilled
-      if (tid == 0 && c + ISTAGES < I.K) stage(s, chan0 + c + ISTAGES);
-      if (c + ISTAGES < I.K) inflight++;
+      __syncthreads();  // everyone is done with this slot before it is refilled
+      if (tid == 0 && c + nst < I.K) stage(s, chan0 + c + nst);
+      if (c + nst < I.K) inflight++;
+      if (++s == nst) {
+        s = 0;
+        phase ^= 1u;
+      }
     }
     if (c < I.K) {
       // give the copies still in flight a second, equally bounded chance to land before the shared
       // memory is given up; then fall through to the direct reads
       if (tid == 0) atomicAdd(&g_tma_timeouts, 1u);
       for (int w = 0; w < inflight; w++) {
-        int cc = c + w;
-        if (cc < I.K) mbar_wait_bounded(&bar[cc % ISTAGES], (cc / ISTAGES) & 1);
+        mbar_wait_bounded(&bar[s], phase);
+        if (++s == nst) {
+          s = 0;
+          phase ^= 1u;
+        }
       }
       __syncthreads();
     }
   }
-  for (; c < I.K; c++) {
-#pragma unroll
-    for (int u = 0; u < 2; u++)
-      if (live[u]) __stcs(outb + c * ochan + ov[u], interp_direct(C[u], in + c * ichan, id));
+  if (c < I.K) {
+    const InterpFrame F2 = interp_frame(I, E);  // computed again: nothing of it stays live over the channel loop
+#pragma unroll 1
+    for (int u = 0; u < IVPT; u++) {
+      if (!(livemask >> u & 1u)) continue;
+      float gx, gy, gz;
+      interp_point(I, F2, i0 + u * (INT / (ITILE * ITILE)), j0, k0, gx, gy, gz);
+      InterpCell C = interp_cell(gx, gy, gz);
+      size_t ov = ov0 + u * ovstep;
+      for (int cc = c; cc < I.K; cc++) __stcs(outb + cc * ochan + ov, interp_direct(C, in + cc * ichan, id));
+    }
   }
 }
 
@@ -354,7 +413,20 @@ cudaError_t launch_interpolate_tiled(const InterpMaps& maps, const InterpArgs& I
   unsigned ntiles = interp_tile_count(I.out_dim);
   if (ntiles == 0 || nb == 0 || I.K == 0) return cudaSuccess;
   dim3 grid(ntiles, nb);
-  k_interpolate_tiled<<<grid, 256, 0, st>>>(maps, I);
+  constexpr size_t smem = (size_t)IRING * sizeof(float);
+  if (smem > 48 * 1024) {
+    // more than the default dynamic shared memory: opted into once per device
+    static bool opted[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64 || !opted[dev]) {
+      e = cudaFuncSetAttribute(k_interpolate_tiled, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      if (dev >= 0 && dev < 64) opted[dev] = true;
+    }
+  }
+  k_interpolate_tiled<<<grid, INT, smem, st>>>(maps, I);
   return cudaGetLastError();
 }
 

@@ -335,6 +335,22 @@ def run_gpu_arm(args, rank, world, local_rank):
     clocks = sampler.stop()
     launches = lib.lmg_launch_count() - launches0
 
+    # what a step costs the calling thread: short bursts into an idle GPU, so that the launch queue
+    # never fills and the host is never held back by the device (the host time of the long timed
+    # runs is the device's pace)
+    def host_burst(fn, n=20):
+        best = None
+        for _ in range(3):
+            torch.cuda.synchronize()
+            h0 = time.perf_counter()
+            for _ in range(n):
+                fn()
+            us = (time.perf_counter() - h0) * 1e6 / n
+            best = us if best is None else min(best, us)
+        torch.cuda.synchronize()
+        return best
+    host_issue_us = host_burst(step)
+
     # per-kernel durations in a pass of their own (CUDA events around each launch, on its stream)
     ksteps = min(args.steps, 200)
     lib.lmg_profile_enable(4 * ksteps + 8)
@@ -414,6 +430,10 @@ def run_gpu_arm(args, rank, world, local_rank):
                             "note": "pinned host arrays handed to GridMaker.forward/backward themselves: the "
                                     "calls copy atoms in and gradients out on the calling stream, no overlap"},
         "per_rank": per_rank,
+        "host_issue_us_per_step": {"value": round(host_issue_us, 1),
+                                   "note": "calling thread, forward + backward through the Python layer, bursts "
+                                           "of 20 steps into an idle GPU (rank 0); the host_issue_ms of per_rank "
+                                           "is the device's pace once the launch queue is full"},
         "gpu_launches": int(launches),
         "clocks": clocks,
     }

@@ -14,11 +14,14 @@ from .grids import __all__ as _grid_names
 from .coordinates import CoordinateSet, Example, ExampleVec  # noqa: F401
 from .atom_typing import (GninaIndexTyper, FileAtomMapper, FileMappedGninaTyper,  # noqa: F401
                           default_receptor_typer, default_ligand_typer)
-from .coord_cache import CoordCache, DeviceBatch, ExampleProvider, read_gninatypes  # noqa: F401
+from .coord_cache import (CoordCache, DeviceBatch, ExampleDataset, ExampleProvider,  # noqa: F401
+                          read_gninatypes)
+from .example_order import ExampleProviderSettings, IterationScheme  # noqa: F401
 from . import _cabi  # noqa: F401
 
 __all__ = ["GridMaker", "GridInterpolater", "Transform", "Quaternion", "float3", "set_random_seed",
            "Coords2Grid", "Coords2GridFunction", "BatchedCoords2GridFunction", "Grid2CoordsGradientFunction",
            "CoordinateSet", "Example", "ExampleVec", "GninaIndexTyper", "FileAtomMapper",
            "FileMappedGninaTyper", "default_receptor_typer", "default_ligand_typer", "CoordCache",
-           "ExampleProvider", "DeviceBatch", "read_gninatypes"] + list(_grid_names)
+           "ExampleProvider", "ExampleDataset", "ExampleProviderSettings", "IterationScheme", "DeviceBatch",
+           "read_gninatypes"] + list(_grid_names)

@@ -10,7 +10,8 @@
 
 Atoms whose mapped type is negative are dropped, as in the reference.  Records are decoded with
 vectorised numpy on the host; the result is a CoordinateSet whose arrays go to the GPU in one copy.
-Shuffling, balancing, stratification and molecule parsing (OpenBabel) are not part of this path.
+The order of the examples (shuffling, balancing, stratification, grouping) follows the reference's
+settings (``example_order``); molecule parsing (OpenBabel) is not part of this path.
 """
 import ctypes
 import threading
@@ -22,6 +23,7 @@ import torch
 from . import _cabi
 from .atom_typing import default_ligand_typer, default_receptor_typer
 from .coordinates import CoordinateSet, Example, ExampleVec
+from .example_order import ExampleProviderSettings, IterationScheme, Uniform, create_provider
 
 RECORD = np.dtype([("x", "<f4"), ("y", "<f4"), ("z", "<f4"), ("type", "<i4")])
 
@@ -228,17 +230,31 @@ class DeviceBatch(object):
 
 
 class ExampleProvider(object):
-    """Examples in file order: ``populate`` reads example lists, ``next``/``next_batch`` walk them
-    cyclically.  The typers apply to the files of a line in order, the last one repeating
-    (src/example_extractor.cpp:21-37); the defaults are the receptor and ligand groupings."""
+    """Examples from example lists: ``populate`` reads the lists, ``next`` / ``next_batch`` hand the
+    examples out in the order the settings ask for (file order by default; ``shuffle``, ``balanced``,
+    ``stratify_receptor``, ``stratify_min/max/step``, ``max_group_size`` as in the reference,
+    src/example_provider.cpp:103-213).  The typers apply to the files of a line in order, the last
+    one repeating (src/example_extractor.cpp:21-37); the defaults are the receptor and ligand
+    groupings.  ``seed`` seeds the shuffles of this provider."""
 
-    def __init__(self, *typers, data_root="", recmolcache="", ligmolcache="", num_labels=-1):
+    def __init__(self, *typers, num_labels=-1, seed=0, **settings):
+        if typers and isinstance(typers[0], ExampleProviderSettings):
+            self.settings, typers = typers[0], typers[1:]
+            if settings:
+                raise TypeError("settings given twice")
+        else:
+            self.settings = ExampleProviderSettings(**settings)
+        st = self.settings
         if not typers:
             typers = (default_receptor_typer(), default_ligand_typer())
-        caches = [recmolcache, ligmolcache]
-        self.caches = [CoordCache(t, data_root, caches[i] if i < 2 else "") for i, t in enumerate(typers)]
+        caches = [st.recmolcache, st.ligmolcache]
+        self.caches = [CoordCache(t, st.data_root, caches[i] if i < 2 else "") for i, t in enumerate(typers)]
         self.refs = []
-        self.pos = 0
+        self._rng = np.random.default_rng(seed)
+        self._order = create_provider(st, self._rng)
+        self._grouped = bool(getattr(self._order, "has_group", False))
+        self._pads = {}                  # (files, labels) of a line -> index of its padding frame
+        self._last_epoch = 0
         self._num_labels = num_labels
         self._stage = [(None, None), (None, None)]   # two pinned staging buffers (+ "copy done" events)
         self._stage_slot = 0
@@ -251,16 +267,23 @@ class ExampleProvider(object):
         names = [fname] if isinstance(fname, str) else list(fname)
         nl = num_labels if num_labels >= 0 else self._num_labels
         for name in names:
-            with open(name) as f:
+            try:
+                f = open(name)
+            except OSError:
+                raise ValueError("Could not open file " + name)
+            with f:
                 for line in f:
                     if line.strip():
-                        self.refs.append(ExampleRef(line, nl))
+                        ref = ExampleRef(line, nl, self._grouped)
+                        self.refs.append(ref)
+                        self._order.addref(len(self.refs) - 1, ref)
         if not self.refs:
             raise ValueError("No valid examples found in training set.")
+        self._order.setup()
         self._ix = None   # the staging index covers the examples known when it was built
 
     def size(self):
-        return len(self.refs)
+        return self._order.size()
 
     def num_labels(self):
         return len(self.refs[0].labels) if self.refs else 0
@@ -268,6 +291,10 @@ class ExampleProvider(object):
     def num_types(self):
         """Channels of a gridded example: one block of types per coordinate set of a line."""
         n = len(self.refs[0].files) if self.refs else len(self.caches)
+        if self.settings.duplicate_first and n > 2:
+            n = 2 * (n - 1)   # the first set again before every further one (count_types, :59-74)
+            return sum(self.caches[0].num_types() if i % 2 == 0 else
+                       self.caches[min(i // 2 + 1, len(self.caches) - 1)].num_types() for i in range(n))
         return sum(self.caches[min(i, len(self.caches) - 1)].num_types() for i in range(n))
 
     def get_type_names(self):
@@ -277,25 +304,110 @@ class ExampleProvider(object):
         return out
 
     def reset(self):
-        self.pos = 0
+        self._order.reset()
+        self._last_epoch = 0
+
+    def small_epoch_size(self):
+        return self._order.small_epoch_size()
+
+    def large_epoch_size(self):
+        return self._order.large_epoch_size()
+
+    def get_small_epoch_num(self):
+        return self._order.get_small_epoch_num()
+
+    def get_large_epoch_num(self):
+        return self._order.get_large_epoch_num()
+
+    def skip(self, n):
+        for _ in range(int(n)):
+            self._order.nextref()
+
+    def at_new_epoch(self):
+        """True once per epoch of the configured iteration scheme, when the next example belongs to a
+        new epoch (include/libmolgrid/example_provider.h:135-152)."""
+        sch = self.settings.iteration_scheme
+        if sch == IterationScheme.LargeEpoch:
+            e = self._order.get_large_epoch_num()
+        elif sch == IterationScheme.SmallEpoch:
+            e = self._order.get_small_epoch_num()
+        else:
+            return False
+        if e != self._last_epoch:
+            self._last_epoch = e
+            return True
+        return False
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        """Batches of ``default_batch_size`` until the epoch ends (never with the continuous scheme)."""
+        if self.at_new_epoch():
+            raise StopIteration("End of epoch.")
+        return self.next_batch()
+
+    @property
+    def pos(self):
+        """Position in the list while it is walked in file order."""
+        return getattr(self._order, "current", 0)
+
+    def _files(self, ref):
+        """(file, typer index) of the coordinate sets of a line: the first file again before every
+        further one with ``duplicate_first`` and three or more files (src/example_extractor.cpp:39-55)."""
+        last = len(self.caches) - 1
+        if self.settings.duplicate_first and len(ref.files) >= 3:
+            out = []
+            for i in range(1, len(ref.files)):
+                out += [(ref.files[0], 0), (ref.files[i], min(i, last))]
+            return out
+        return [(f, min(i, last)) for i, f in enumerate(ref.files)]
+
+    def _next_index(self):
+        """Index of the next line, with a group's padding frames turned into lines of their own (the
+        files of the group's last frame replaced by the empty set, labels NaN)."""
+        r = self._order.nextref()
+        if not self._grouped:
+            return r, None
+        i, padded, group, seqcont = r
+        if padded:
+            ref = self.refs[i]
+            key = (len(ref.files), len(ref.labels))
+            j = self._pads.get(key)
+            if j is None:
+                pad = ExampleRef.__new__(ExampleRef)
+                pad.group, pad.labels, pad.files = -1, [float("nan")] * key[1], ["none"] * key[0]
+                self.refs.append(pad)
+                j = self._pads[key] = len(self.refs) - 1
+                self._ix = None
+            i = j
+        return i, (group, seqcont)
 
     def _make(self, ref):
         ex = Example()
         ex.labels = list(ref.labels)
         ex.group = ref.group
-        for i, fname in enumerate(ref.files):
-            ex.coord_sets.append(self.caches[min(i, len(self.caches) - 1)].make_coords(fname))
+        for fname, ci in self._files(ref):
+            c = self.caches[ci].make_coords(fname)
+            if self.settings.make_vector_types and c.has_indexed_types():
+                c.make_vector_types(False, self.caches[ci].typer.get_type_radii())
+            ex.coord_sets.append(c)
         return ex
 
     def next(self):
         if not self.refs:
             raise RuntimeError("No examples: populate() first")
-        ex = self._make(self.refs[self.pos])
-        self.pos = (self.pos + 1) % len(self.refs)
+        i, frame = self._next_index()
+        ex = self._make(self.refs[i])
+        if frame is not None:
+            ex.group, ex.seqcont = frame
         return ex
 
-    def next_batch(self, batch_size):
-        return ExampleVec([self.next() for _ in range(int(batch_size))])
+    def next_batch(self, batch_size=0):
+        B = int(batch_size) or int(self.settings.default_batch_size)
+        if hasattr(self._order, "check_batch_size"):
+            self._order.check_batch_size(B)
+        return ExampleVec([self.next() for _ in range(B)])
 
     def _packed(self, i):
         """Example i ready for staging: the bytes of all its sets' records back to back, and per set
@@ -305,8 +417,7 @@ class ExampleProvider(object):
             ref = self.refs[i]
             recs, counts, typers, toffs, dst = [], [], [], [], []
             toffset = natoms = 0
-            for k, fname in enumerate(ref.files):
-                ci = min(k, len(self.caches) - 1)
+            for fname, ci in self._files(ref):
                 r = self.caches[ci].records(fname)
                 recs.append(np.ascontiguousarray(r).view(np.uint8))
                 counts.append(len(r)); typers.append(ci); toffs.append(toffset); dst.append(natoms)
@@ -321,13 +432,15 @@ class ExampleProvider(object):
         return p
 
     def _take(self, batch_size):
-        """Indices of the next ``batch_size`` examples (cyclic)."""
+        """Indices of the next ``batch_size`` examples."""
         if not self.refs:
             raise RuntimeError("No examples: populate() first")
-        B = int(batch_size)
-        idx = [(self.pos + k) % len(self.refs) for k in range(B)]
-        self.pos = (self.pos + B) % len(self.refs)
-        return idx
+        if self.settings.make_vector_types:
+            raise ValueError("device batches carry index types; make_vector_types applies to next()/next_batch()")
+        B = int(batch_size) or int(self.settings.default_batch_size)
+        if hasattr(self._order, "check_batch_size"):
+            self._order.check_batch_size(B)
+        return [self._next_index()[0] for _ in range(B)]
 
     def _index(self, idx):
         """Per-example arrays for staging, built on first use and extended as examples are first
@@ -491,3 +604,24 @@ class ExampleProvider(object):
                 if count is None or issued < count:
                     submit()
                 yield batch
+
+
+class ExampleDataset(ExampleProvider):
+    """Random access to the examples of the lists, for map-style data sets: ``len(d)`` examples,
+    ``d[i]`` the i-th line in file order (python/bindings.in.cpp: ExampleDataset; settings that
+    concern iteration are ignored)."""
+
+    def __init__(self, *typers, **kw):
+        for k in ("shuffle", "balanced", "stratify_receptor", "stratify_min", "stratify_max", "stratify_step",
+                  "max_group_size", "group_batch_size", "num_copies"):
+            kw.pop(k, None)
+        ExampleProvider.__init__(self, *typers, **kw)
+
+    def __len__(self):
+        return len(self.refs)
+
+    def __getitem__(self, i):
+        n = len(self.refs)
+        if not -n <= i < n:
+            raise IndexError("Invalid index: %d > %d" % (i, n))
+        return self._make(self.refs[i % n])

@@ -135,5 +135,8 @@ class ExampleProvider(_py.ExampleProvider):
         ex.group = int(pex.group) if pex.group is not None else -1
         return ex
 
-    def next_batch(self, batch_size):
-        return native.ExampleVec([self.next() for _ in range(int(batch_size))])
+    def next_batch(self, batch_size=0):
+        B = int(batch_size) or int(self.settings.default_batch_size)
+        if hasattr(self._order, "check_batch_size"):
+            self._order.check_batch_size(B)
+        return native.ExampleVec([self.next() for _ in range(B)])

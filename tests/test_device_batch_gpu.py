@@ -212,3 +212,31 @@ def test_prefetched_batches_equal_sequential_batches(provider_dir):
         for b in range(4):
             for x, y in zip(g[:3], (want.coords, want.type_index, want.radii)):
                 assert torch.equal(x[b, :ns[b]], y[b, :ns[b]])
+
+
+@pytest.mark.parametrize("settings", [dict(shuffle=True, balanced=True), dict(stratify_receptor=True, num_copies=2),
+                                      dict(duplicate_first=True)])
+def test_device_batches_follow_the_order_settings(provider_dir, settings):
+    """Shuffled, balanced, stratified or duplicated: the device batch holds the examples next_batch
+    hands out for the same settings and seed."""
+    ps = []
+    for _ in range(2):
+        p = coord_cache.ExampleProvider(data_root=str(provider_dir), seed=11, **settings)
+        p.populate(str(provider_dir / "list.types"))
+        ps.append(p)
+    pa, pb = ps
+    B = 6
+    for _ in range(3):
+        exs = pa.next_batch(B)
+        batch = pb.next_device_batch(B).check()
+        labels = np.zeros((B, 2), np.float32)
+        exs.extract_labels(labels)
+        np.testing.assert_array_equal(batch.labels.cpu().numpy(), labels)
+        types = batch.type_index.cpu().numpy()
+        coords = batch.coords.cpu().numpy()
+        ns = batch.n_atoms.cpu().numpy()
+        for b, ex in enumerate(exs):
+            m = ex.merge_coordinates()
+            keep = types[b, :ns[b]] >= 0
+            np.testing.assert_array_equal(coords[b, :ns[b]][keep], m.coords.tonumpy())
+            np.testing.assert_array_equal(types[b, :ns[b]][keep], m.type_index.tonumpy())

@@ -113,7 +113,8 @@ def set_random_seed(seed):
 # tensor plumbing
 # ------------------------------------------------------------------------------------------------
 def _stream_ptr(device):
-    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    # the raw handle of torch's current stream on the device, without building a Stream object
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(device.index))
 
 
 class _Arg(object):
@@ -121,6 +122,10 @@ class _Arg(object):
 
     def __init__(self, obj, device, ndim, name, output=False):
         self.host = None
+        if type(obj) is torch.Tensor and obj.is_cuda and obj.dtype is torch.float32 and obj.dim() == ndim \
+                and obj.device == device and obj.is_contiguous():
+            self.t, self.output = obj, output      # the common case: a resident tensor, nothing to stage
+            return
         obj = _grids.operand_tensor(obj)
         if isinstance(obj, np.ndarray):
             if obj.dtype != np.float32 or not obj.flags["C_CONTIGUOUS"]:
@@ -162,9 +167,14 @@ class _Arg(object):
             self.host.copy_(self.t)
 
 
+_have_cuda = []   # filled on the first successful check
+
+
 def _current_device():
-    if not torch.cuda.is_available():
-        raise RuntimeError("no CUDA device: this library has no CPU path")
+    if not _have_cuda:
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device: this library has no CPU path")
+        _have_cuda.append(True)
     return torch.device("cuda", torch.cuda.current_device())
 
 
@@ -422,9 +432,13 @@ class GridMaker(object):
             raise exc("radii does not match number of atoms: %d vs %d" % (nr, N))
 
     def _ws(self, dev, op, B, N, T, vec):
-        need = _cabi.lib().lmg_workspace_bytes(ctypes.byref(self.s), op, B, N, T, int(vec))
-        ws = _workspace(dev, min(need, MAX_WORKSPACE_BYTES))
-        return ws
+        # the size depends on the shapes and the settings: asked once per combination
+        key = (op, B, N, T, vec, self.s.radii_type_indexed, self.s.binary, self.s.dim)
+        sizes = self.__dict__.setdefault("_ws_sizes", {})
+        need = sizes.get(key)
+        if need is None:
+            need = sizes[key] = _cabi.lib().lmg_workspace_bytes(ctypes.byref(self.s), op, B, N, T, int(vec))
+        return _workspace(dev, min(need, MAX_WORKSPACE_BYTES))
 
     # --- forward -----------------------------------------------------------------------------
     def forward(self, *args, **kw):

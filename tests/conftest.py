@@ -12,6 +12,14 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
 
 
+@pytest.fixture(autouse=True)
+def _seeded_torch():
+    """Every test draws the same torch random numbers on every run (host and device generators)."""
+    import torch
+    torch.manual_seed(20240)
+    yield
+
+
 @pytest.fixture(scope="session")
 def port():
     from oracle.oracle import CpuOracle

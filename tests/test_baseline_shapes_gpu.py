@@ -117,6 +117,31 @@ def test_interpolate_28x48_rotated_against_oracle(port):
     assert _cabi.lib().lmg_tma_timeouts() == 0
 
 
+@pytest.mark.parametrize("axis_angle", [((1.0, 0.0, 0.0), 0.0), ((0.0, 0.0, 1.0), 90.0), ((0.0, 0.0, 1.0), 45.0),
+                                        ((1.0, -1.0, 0.0), 54.735610317245346), ((1.0, 1.0, 1.0), 60.0)])
+def test_interpolate_48_cubed_special_rotations(port, axis_angle):
+    """Rotations at the ends of the staged boxes' range: none (the smallest box), quarter turns (integer
+    voxel positions: floor == ceil), 45 degrees, and the turn that puts a tile's diagonal along an
+    axis (the largest box, a single staging slot); partly outside the input through the translation."""
+    import libmolgrid_b200 as lmg
+    from libmolgrid_b200 import _cabi
+    (ax, ay, az), deg = axis_angle
+    n = float(np.sqrt(ax * ax + ay * ay + az * az))
+    h = np.deg2rad(deg) / 2
+    q = (float(np.cos(h)), float(np.sin(h) * ax / n), float(np.sin(h) * ay / n), float(np.sin(h) * az / n))
+    rng = np.random.default_rng(77)
+    grid = rng.uniform(-1, 1, (3, 48, 48, 48)).astype(np.float32)
+    tr = port.tr(q, (0, 0, 0), (1.5, -0.5, 3.0))
+    want = port.interpolate([0.5, 23.5, 0.5, 23.5], (0, 0, 0), grid, tr, (0, 0, 0))
+    gi = lmg.GridInterpolater(0.5, 23.5, 0.5, 23.5)
+    t = lmg.Transform(lmg.Quaternion(*q), (0, 0, 0), (1.5, -0.5, 3.0))
+    out = torch.full((3, 48, 48, 48), -1.0, device="cuda")
+    gi.forward((0, 0, 0), dev(grid), t, (0, 0, 0), out)
+    got = out.cpu().numpy()
+    assert np.array_equal(got, want), np.abs(got - want).max()
+    assert _cabi.lib().lmg_tma_timeouts() == 0
+
+
 # ---- guard words around the outputs -----------------------------------------------------------------
 
 GUARD = 0x7fc0dead  # a NaN payload no kernel produces

@@ -171,6 +171,7 @@ def test_interpolate_backward_is_the_adjoint(gi):
     reproduces the forward pass's weights (checked through a finite difference of the forward)."""
     import libmolgrid_b200 as lmg
     rng = np.random.default_rng(41)
+    torch.manual_seed(41)          # the random grids below: the same on every run
     g = lmg.GridInterpolater(*gi)
     din, dout = g.s.in_dim, g.s.out_dim
     K = 3
@@ -183,8 +184,10 @@ def test_interpolate_backward_is_the_adjoint(gi):
     g.backward(y, tr, by)
     lhs = float((fx.double() * y.double()).sum())
     rhs = float((x.double() * by.double()).sum())
-    assert abs(lhs) > 1.0
-    assert lhs == pytest.approx(rhs, rel=1e-4)
+    # float32 accumulation on both sides: the bound is relative to the size of the terms, since
+    # y has both signs and the sums may cancel
+    scale = float((fx.double() * y.double()).abs().sum())
+    assert scale > 1.0 and abs(lhs - rhs) <= 1e-5 * scale
     # linearity in x: forward(x + h e) - forward(x) = h * forward(e); <that, y> = h * by[e]
     e = (1, din // 2, din // 2 - 1, din // 2)
     x2 = x.clone()
@@ -200,6 +203,7 @@ def test_interpolate_backward_is_the_adjoint(gi):
     fb, bb = torch.empty_like(yb), torch.empty_like(xb)
     g.forward(cen, xb, trs, cen, fb)
     g.backward(cen, yb, trs, cen, bb)
-    assert float((fb.double() * yb.double()).sum()) == pytest.approx(float((xb.double() * bb.double()).sum()), rel=1e-4)
+    scale = float((fb.double() * yb.double()).abs().sum())
+    assert abs(float((fb.double() * yb.double()).sum()) - float((xb.double() * bb.double()).sum())) <= 1e-5 * scale
     with pytest.raises(ValueError):
         g.backward(y, tr, torch.empty_like(y) if din != dout else y)

@@ -805,7 +805,13 @@ __device__ __forceinline__ BwdSums backward_quads_core(const BwdArgs& G, ItemPar
     if (!want_ag) P.valid = false;  // zero-weight channels contribute nothing (src/grid_maker.cpp:573)
   }
   const float kexp = P.inv_ar2 * NEG2_LOG2E;
-  const float k4 = 4.f * P.inv_ar2, kD = -gm.D * P.inv_ar2, kE = -gm.E * P.inv_ar;
+  // The gradient's radial factor beyond the Gaussian part is kE/d + kD: positive inside the cut-off,
+  // zero at it (the tail polynomial has a double root there) and negative beyond, so a clamp at zero
+  // stands in for the comparison with the cut-off.  Items that want no atom gradient (zero weight)
+  // and grid makers without a tail (ta == tb == 0) get zero factors.
+  const bool tail = gm.ta != 0.f || gm.tb != 0.f;
+  const float k4 = want_ag ? 4.f * P.inv_ar2 : 0.f;
+  const float kD = (want_ag && tail) ? -gm.D * P.inv_ar2 : 0.f, kE = (want_ag && tail) ? -gm.E * P.inv_ar : 0.f;
   const float ta = gm.ta, ntb = -gm.tb;
 
   if (P.valid) {
@@ -865,8 +871,9 @@ __device__ __forceinline__ BwdSums backward_quads_core(const BwdArgs& G, ItemPar
                   if (MODE == 0 || MODE == 1) {
                     // -(d density / d dist) / dist * dv, src/grid_maker.cu:881-919; rsq == 0
                     // contributes nothing because dx = dy = dz = 0 there
-                    float sg = rsq <= P.Tg ? exy4 * ev[j] : fmaf(kE, rsqrt_approx(rsq), kD);
-                    float f = (want_ag && rsq <= P.Tcut) ? sg * dvv[j] : 0.f;
+                    // a NaN rsq (z outside the footprint) takes the second branch and clamps to zero
+                    float sg = rsq <= P.Tg ? exy4 * ev[j] : fmaxf(fmaf(kE, rsqrt_approx(rsq), kD), 0.f);
+                    float f = sg * dvv[j];
                     fsum += f;
                     agz = fmaf(f, dzv[j], agz);
                   }
@@ -876,8 +883,7 @@ __device__ __forceinline__ BwdSums backward_quads_core(const BwdArgs& G, ItemPar
                       v = rsq < P.Tbin ? 1.f : 0.f;
                     } else {
                       float tq = fminf(fmaf(ta, sqrt_approx(rsq * P.inv_ar2), ntb), 0.f);
-                      v = rsq <= P.Tg ? g : tq * tq;
-                      v = rsq <= P.Tcut ? v : 0.f;
+                      v = rsq <= P.Tg ? g : tq * tq;  // tq is zero beyond the cut-off and for a NaN rsq
                     }
                     tg = fmaf(v, dvv[j], tg);
                   }
@@ -1274,7 +1280,8 @@ __device__ __forceinline__ void va_round(const BwdArgs& G, const ItemParams& P, 
   const size_t cs4 = dim * dim * dim / 4;  // channel stride in quads
   const float Tcull = fmaxf(P.Tcut, BINARY ? P.Tbin : -1.f);
   const float kexp = P.inv_ar2 * NEG2_LOG2E;
-  const float k4 = 4.f * P.inv_ar2, kD = -gm.D * P.inv_ar2, kE = -gm.E * P.inv_ar;
+  const bool tail = gm.ta != 0.f || gm.tb != 0.f;  // without a tail nothing lies beyond the Gaussian part
+  const float k4 = 4.f * P.inv_ar2, kD = tail ? -gm.D * P.inv_ar2 : 0.f, kE = tail ? -gm.E * P.inv_ar : 0.f;
   const float ta = gm.ta, ntb = -gm.tb;
   const unsigned span = quad_span(P);
   ColBufD& buf = sh.buf;
@@ -1295,8 +1302,7 @@ __device__ __forceinline__ void va_round(const BwdArgs& G, const ItemParams& P, 
           v[j] = rsq < P.Tbin ? 1.f : 0.f;
         } else {
           float tq = fminf(fmaf(ta, sqrt_approx(rsq * P.inv_ar2), ntb), 0.f);
-          float val = rsq <= P.Tg ? exy * ev[j] : tq * tq;
-          v[j] = rsq <= P.Tcut ? val : 0.f;
+          v[j] = rsq <= P.Tg ? exy * ev[j] : tq * tq;  // tq is zero beyond the cut-off and for a NaN rsq
         }
       }
       const float4* qp = reinterpret_cast<const float4*>(diffb + off) + (size_t)tb * cs4;
@@ -1339,8 +1345,9 @@ __device__ __forceinline__ void va_round(const BwdArgs& G, const ItemParams& P, 
 #pragma unroll
       for (int j = 0; j < 4; j++) {
         float rsq = __fadd_rn(dxy2, d2v[j]);
-        float s1 = rsq <= P.Tg ? k4 * (exy * ev[j]) : fmaf(kE, rsqrt_approx(rsq), kD);
-        float f = (rsq <= P.Tcut ? s1 : 0.f) * dsum[j];
+        // kE/d + kD is zero at the cut-off and negative beyond it: the clamp stands in for the comparison
+        float s1 = rsq <= P.Tg ? k4 * (exy * ev[j]) : fmaxf(fmaf(kE, rsqrt_approx(rsq), kD), 0.f);
+        float f = s1 * dsum[j];
         fsum += f;
         agz = fmaf(f, dzv[j], agz);
       }

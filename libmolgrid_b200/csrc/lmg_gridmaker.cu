@@ -619,6 +619,7 @@ struct __align__(16) ZTabs {
   float4 dz2[QPASS];  // (gz-az)^2, NaN outside [loz, hiz)
   float4 ez[QPASS];   // exp(-2 dz2 / ar^2)
   float4 dz[QPASS];   // gz-az
+  float lo[QPASS];    // smallest dz2 of the quad (NaN when no z of it lies in the footprint)
 };
 
 __device__ __forceinline__ void fill_ztabs(ZTabs& zt, unsigned zc, const ItemParams& P, float oz, float res,
@@ -630,6 +631,9 @@ __device__ __forceinline__ void fill_ztabs(ZTabs& zt, unsigned zc, const ItemPar
   reinterpret_cast<float*>(zt.dz2)[lane] = d2;
   reinterpret_cast<float*>(zt.ez)[lane] = ex2_approx(d2 * kexp);
   reinterpret_cast<float*>(zt.dz)[lane] = dz;
+  float lo = fminf(d2, __shfl_xor_sync(0xffffffffu, d2, 1));  // fminf skips the NaN entries
+  lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, 2));
+  if ((lane & 3) == 0) zt.lo[lane >> 2] = lo;
 }
 
 __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
@@ -843,11 +847,8 @@ __device__ __forceinline__ BwdSums backward_quads_core(const BwdArgs& G, ItemPar
 #pragma unroll
             for (int u = 0; u < 4; u++) {
               dv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (q0 + u < nq) {
-                float4 d2 = zt.dz2[q0 + u];
-                float lo = fminf(fminf(d2.x, d2.y), fminf(d2.z, d2.w));  // fminf skips the NaN entries
-                if (__fadd_rn(dxy2, lo) <= Tcull) dv[u] = __ldg(row + q0 + u);
-              }
+              // no load where no voxel of the quad can lie inside the cut-off (false for a NaN too)
+              if (q0 + u < nq && __fadd_rn(dxy2, zt.lo[q0 + u]) <= Tcull) dv[u] = __ldg(row + q0 + u);
             }
 #pragma unroll
             for (int u = 0; u < 4; u++) {
@@ -858,8 +859,7 @@ __device__ __forceinline__ BwdSums backward_quads_core(const BwdArgs& G, ItemPar
                 float dev[4] = {0.f, 0.f, 0.f, 0.f};
                 if (MODE == 2) {
                   // the density is only needed where this quad can hold a voxel of the atom
-                  float lo = fminf(fminf(d2.x, d2.y), fminf(d2.z, d2.w));
-                  if (__fadd_rn(dxy2, lo) <= Tcull) {
+                  if (__fadd_rn(dxy2, zt.lo[q0 + u]) <= Tcull) {
                     float4 de = __ldg(reinterpret_cast<const float4*>(dens + rowoff) + q0 + u);
                     dev[0] = de.x; dev[1] = de.y; dev[2] = de.z; dev[3] = de.w;
                   }
@@ -1496,7 +1496,7 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads_atom_ag(BwdA
           float fsum = 0.f;
           for (unsigned q = 0; q < nq; q++) {
             float4 d2 = zt.dz2[q], e = zt.ez[q], dz = zt.dz[q];
-            float lo = fminf(fminf(d2.x, d2.y), fminf(d2.z, d2.w));  // fminf skips the NaN entries
+            float lo = zt.lo[q];
             bool live = __fadd_rn(dxy2, lo) <= P.Tcut;
             float4 ds = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int k = 0; k < nnz; k++) {
@@ -1714,7 +1714,7 @@ __global__ void __launch_bounds__(BWD2_WARPS * 32) k_backward_quads_atom_gg(BwdA
           float dotxy = fmaf(dx, inx, dy * iny);
           for (unsigned q = 0; q < nq; q++) {
             float4 d2 = zt.dz2[q], e = zt.ez[q], dz = zt.dz[q];
-            float lo = fminf(fminf(d2.x, d2.y), fminf(d2.z, d2.w));  // fminf skips the NaN entries
+            float lo = zt.lo[q];
             if (!(__fadd_rn(dxy2, lo) <= P.Tcut)) continue;
             float s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
             for (int k = 0; k < nnz; k++) {

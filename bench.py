@@ -291,6 +291,18 @@ def run_gpu_arm(args, rank, world, local_rank):
         g.forward(hcen, hc, ht, hr, grid, transforms=htr_rows, n_atoms=dn)
         g.backward(hcen, hc, ht, hr, diff, hag[0], transforms=htr_rows, n_atoms=dn)
 
+    # Every buffer on the host, the grids too: the forward call copies 12.4 MB per example out, the
+    # backward call as much in.  What a caller pays who keeps nothing on the device.
+    host_grid = {}
+
+    def step_host_grids():
+        if not host_grid:
+            host_grid["out"] = torch.empty(tuple(grid.shape)).pin_memory()
+            host_grid["diff"] = torch.empty(tuple(grid.shape)).pin_memory()
+            host_grid["diff"].copy_(diff)
+        g.forward(hcen, hc, ht, hr, host_grid["out"], transforms=htr_rows, n_atoms=dn)
+        g.backward(hcen, hc, ht, hr, host_grid["diff"], hag[0], transforms=htr_rows, n_atoms=dn)
+
     def barrier():
         if world > 1:
             dist.barrier()
@@ -367,6 +379,10 @@ def run_gpu_arm(args, rank, world, local_rank):
     for _ in range(2):
         step_host_api()
     ms_host = timed(step_host_api, hsteps, "host_api")
+    gsteps = min(args.steps, 5)
+    step_host_grids()
+    ms_hostgrid = timed(step_host_grids, gsteps, "host_grids")
+    host_grid.clear()
 
     # sanity: the timed kernels did the work (cheap property checks, outside the timed region)
     assert torch.isfinite(ag).all() and float(grid.sum()) > 0
@@ -429,6 +445,10 @@ def run_gpu_arm(args, rank, world, local_rank):
         "e2e_host_arrays": {"value": global_batch * hsteps / (ms_host * 1e-3), "unit": "examples/s", "steps": hsteps,
                             "note": "pinned host arrays handed to GridMaker.forward/backward themselves: the "
                                     "calls copy atoms in and gradients out on the calling stream, no overlap"},
+        "e2e_host_grids": {"value": global_batch * gsteps / (ms_hostgrid * 1e-3), "unit": "examples/s", "steps": gsteps,
+                           "h2d_bytes_per_step": int(h2d + nex * GRID_BYTES), "d2h_bytes_per_step": int(d2h + nex * GRID_BYTES),
+                           "note": "every array in pinned host memory, the grids and their gradients too: "
+                                   "bound by the host link (12.4 MB per example each way)"},
         "per_rank": per_rank,
         "host_issue_us_per_step": {"value": round(host_issue_us, 1),
                                    "note": "calling thread, forward + backward through the Python layer, bursts "

@@ -144,24 +144,37 @@ class CoordCache(object):
             self._raw[fname] = rec
         return rec
 
+    def mem_cache_size(self):
+        return len(self._raw)
+
+    def save_mem_cache(self, out):
+        """Writes the records read so far (name, count, records) to the open binary file ``out``."""
+        out.write(np.uint64(len(self._raw)).tobytes())
+        for name, rec in self._raw.items():
+            b = name.encode()
+            out.write(np.uint32(len(b)).tobytes() + b + np.uint64(len(rec)).tobytes())
+            out.write(np.ascontiguousarray(rec).tobytes())
+
+    def load_mem_cache(self, inp):
+        (n,) = np.frombuffer(inp.read(8), np.uint64)
+        for _ in range(int(n)):
+            (ln,) = np.frombuffer(inp.read(4), np.uint32)
+            name = inp.read(int(ln)).decode()
+            (cnt,) = np.frombuffer(inp.read(8), np.uint64)
+            self._raw[name] = np.frombuffer(inp.read(int(cnt) * RECORD.itemsize), dtype=RECORD).copy()
+
     def tables(self):
         """(channel or -1, radius) for the record type numbers 0..27, as the device decoder wants them."""
         t, r = self.typer.map_types(np.arange(_cabi.RECORD_TYPES))
         return np.asarray(t, dtype=np.int32), np.asarray(r, dtype=np.float32)
 
     def make_coords(self, fname):
-        if self.cache is not None and fname in self.cache:
-            return coordinate_set_from_records(self.cache.records(fname), self.typer, src=fname)
-        if fname.endswith("none"):  # reserved word: an empty set
-            c = CoordinateSet()
+        if fname.endswith("none") and not (self.cache is not None and fname in self.cache):
+            c = CoordinateSet()  # reserved word: an empty set
             c.max_type = self.typer.num_types()
             return c
-        if not fname.endswith(".gninatypes"):
-            raise ValueError("Only pre-typed input (.gninatypes, .molcache2) is read here: " + fname)
-        full = fname if os.path.isabs(fname) or not self.data_root else os.path.join(self.data_root, fname)
-        c = read_gninatypes(full, self.typer)
-        c.src = fname
-        return c
+        # through the in-memory records: a structure is read from its file once
+        return coordinate_set_from_records(self.records(fname), self.typer, src=fname)
 
     def set_coords(self, fname, cset):
         c = self.make_coords(fname)
@@ -322,6 +335,24 @@ class ExampleProvider(object):
     def skip(self, n):
         for _ in range(int(n)):
             self._order.nextref()
+
+    def mem_caches_size(self):
+        """Coordinate sets held in memory (src/example_extractor.cpp:104-110)."""
+        return sum(c.mem_cache_size() for c in self.caches)
+
+    def save_mem_caches(self, fname):
+        """Writes the structures read so far to ``fname``, one block per typer in order; a later
+        ``load_mem_caches`` serves them without the structure files (include/libmolgrid/
+        example_provider.h:166-193).  The layout is this library's own (records as read, before
+        typing), not the reference's serialisation."""
+        with open(fname, "wb") as f:
+            for c in self.caches:
+                c.save_mem_cache(f)
+
+    def load_mem_caches(self, fname):
+        with open(fname, "rb") as f:
+            for c in self.caches:
+                c.load_mem_cache(f)
 
     def at_new_epoch(self):
         """True once per epoch of the configured iteration scheme, when the next example belongs to a

@@ -207,3 +207,19 @@ def test_dataset_random_access(lists):
 def test_unknown_setting_is_refused():
     with pytest.raises(TypeError):
         molgrid.ExampleProvider(shufle=True)
+
+
+def test_mem_caches_round_trip(lists, tmp_path_factory):
+    d, f, _ = lists
+    p = _provider(d, f)
+    want = [(_lig(x), x.coord_sets[1].coords.tonumpy().copy()) for x in (p.next() for _ in range(40))]
+    assert p.mem_caches_size() == 4 + 40
+    cache = str(tmp_path_factory.mktemp("c") / "mem.cache")
+    p.save_mem_caches(cache)
+    empty = tmp_path_factory.mktemp("nofiles")             # no structure files here: only the cache can serve
+    q = molgrid.ExampleProvider(data_root=str(empty))
+    q.load_mem_caches(cache)
+    q.populate(f)
+    for name, coords in want:
+        x = q.next()
+        assert _lig(x) == name and np.array_equal(x.coord_sets[1].coords.tonumpy(), coords)

@@ -495,7 +495,7 @@ int lmg_backward(const lmg_gridmaker* g, const lmg_atoms* a, const float* diff, 
                  float* type_gradients, void* workspace, size_t workspace_bytes, void* stream) {
   int rc = check_common(g, a, workspace);
   if (rc) return rc;
-  if (a->batch == 0) return LMG_OK;
+  if (a->batch == 0 || a->max_atoms == 0) return LMG_OK;  // no atom, no gradient row to write
   int vec = a->type_vector != nullptr;
   if (diff == nullptr || atom_gradients == nullptr)
     return fail(LMG_ERR_INVALID_ARGUMENT, "diff/atom_gradients missing memory");
@@ -510,7 +510,7 @@ int lmg_backward_relevance(const lmg_gridmaker* g, const lmg_atoms* a, const flo
                            size_t workspace_bytes, void* stream) {
   int rc = check_common(g, a, workspace);
   if (rc) return rc;
-  if (a->batch == 0) return LMG_OK;
+  if (a->batch == 0 || a->max_atoms == 0) return LMG_OK;  // no atom, no relevance to write
   if (a->type_index == nullptr)
     return fail(LMG_ERR_INVALID_ARGUMENT, "backward_relevance needs index types");
   if (density == nullptr || diff == nullptr || relevance == nullptr)
@@ -528,6 +528,13 @@ int lmg_backward_gradients(const lmg_gridmaker* g, const lmg_atoms* a, const flo
   // src/grid_maker.cpp:559 and the vector-types-only overload set (include/libmolgrid/grid_maker.h:463-547)
   if (g->binary) return fail(LMG_ERR_INVALID_ARGUMENT, "Binary densities not supported");
   if (a->batch == 0) return LMG_OK;
+  if (a->max_atoms == 0) {
+    // no atoms: the gradient of the grid gradient is zero, the per-atom outputs are empty
+    if (diffdiff == nullptr) return fail(LMG_ERR_INVALID_ARGUMENT, "backward_gradients argument missing memory");
+    size_t bytes = (size_t)a->batch * a->ntypes * g->dim * g->dim * g->dim * sizeof(float);
+    cudaError_t e0 = cudaMemsetAsync(diffdiff, 0, bytes, (cudaStream_t)stream);
+    return e0 == cudaSuccess ? LMG_OK : cuda_fail(e0, "zeroing diffdiff");
+  }
   if (a->type_vector == nullptr)
     return fail(LMG_ERR_INVALID_ARGUMENT, "backward_gradients needs vector types");
   if (diff == nullptr || atom_gradients == nullptr || type_gradients == nullptr || diffdiff == nullptr ||

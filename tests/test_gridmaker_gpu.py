@@ -415,3 +415,41 @@ def test_backward_vector_rounds_of_channels(port, binary):
     g.backward((0, 0, 0), dev(coords), dev(tv), dev(radii), dev(diff), ag, tg)
     grad_close(ag.cpu().numpy(), wag, "atom gradients")
     grad_close(tg.cpu().numpy(), wtg, "type gradients")
+
+
+def test_empty_and_ragged_inputs(port):
+    """No atoms, no examples, examples of a ragged batch without atoms, atoms far outside the grid:
+    the forward still clears its output, the backward still writes every gradient row."""
+    g, og = gm_pair(port, resolution=0.5, dimension=11.5)
+    T = 5
+    dims = g.grid_dimensions(T)
+    none = torch.zeros((0, 3), device="cuda")
+    out = torch.full(dims, 7.0, device="cuda")
+    g.forward((0, 0, 0), none, torch.zeros((0,), device="cuda"), torch.zeros((0,), device="cuda"), out)
+    assert not out.any()
+    ag = torch.full((0, 3), 7.0, device="cuda")
+    g.backward((0, 0, 0), none, torch.zeros((0,), device="cuda"), torch.zeros((0,), device="cuda"),
+               torch.ones(dims, device="cuda"), ag)
+    # a batch of no examples
+    outb = torch.empty((0,) + dims, device="cuda")
+    g.forward(torch.zeros((0, 3), device="cuda"), torch.zeros((0, 4, 3), device="cuda"),
+              torch.zeros((0, 4), device="cuda"), torch.zeros((0, 4), device="cuda"), outb)
+    # ragged: example 1 has no atoms, example 2 only atoms far outside the grid
+    coords, types, radii = cases.index_case(9, 30, T, 5.0)
+    B, N = 3, 30
+    cb = np.zeros((B, N, 3), np.float32); tb = np.zeros((B, N), np.float32); rb = np.ones((B, N), np.float32)
+    cb[0], tb[0], rb[0] = coords, types, radii
+    cb[2] = coords + 100.0
+    tb[2], rb[2] = types, radii
+    ns = torch.tensor([N, 0, N], dtype=torch.int32)
+    outb = torch.full((B,) + dims, 7.0, device="cuda")
+    cen = torch.zeros((B, 3), device="cuda")
+    g.forward(cen, dev(cb), dev(tb), dev(rb), outb, n_atoms=ns)
+    want = port.forward_index(og, (0, 0, 0), coords, types, radii, T)
+    assert np.allclose(outb[0].cpu().numpy(), want, rtol=1e-5, atol=1e-6)
+    assert not outb[1].any() and not outb[2].any()
+    agb = torch.full((B, N, 3), 7.0, device="cuda")
+    diff = np.random.default_rng(2).normal(size=(B,) + dims).astype(np.float32)
+    g.backward(cen, dev(cb), dev(tb), dev(rb), dev(diff), agb, n_atoms=ns)
+    grad_close(agb[0].cpu().numpy(), port.backward_index(og, (0, 0, 0), coords, types, radii, diff[0]), "example 0")
+    assert not agb[1].any() and not agb[2].any()

@@ -453,3 +453,45 @@ def test_empty_and_ragged_inputs(port):
     g.backward(cen, dev(cb), dev(tb), dev(rb), dev(diff), agb, n_atoms=ns)
     grad_close(agb[0].cpu().numpy(), port.backward_index(og, (0, 0, 0), coords, types, radii, diff[0]), "example 0")
     assert not agb[1].any() and not agb[2].any()
+
+
+def test_extreme_shapes(port):
+    """One channel, a grid of a single point, vector types without atoms, and one example with
+    far more atoms than a launch dimension or a column buffer holds."""
+    import libmolgrid_b200 as lmg
+    # a single grid point (dimension 0): every atom either covers it or not
+    g, og = gm_pair(port, resolution=0.5, dimension=0.0)
+    assert g.grid_dimensions(1) == (1, 1, 1, 1)
+    coords = np.array([[0.2, 0, 0], [3.0, 0, 0], [0, -0.4, 0.3]], np.float32)
+    types = np.zeros(3, np.float32)
+    radii = np.array([1.0, 1.0, 2.0], np.float32)
+    out = torch.full((1, 1, 1, 1), 7.0, device="cuda")
+    g.forward((0, 0, 0), dev(coords), dev(types), dev(radii), out)
+    want = port.forward_index(og, (0, 0, 0), coords, types, radii, 1)
+    assert np.allclose(out.cpu().numpy(), want, **DENS) and want[0, 0, 0, 0] > 0
+    ag = torch.full((3, 3), 7.0, device="cuda")
+    diff = np.ones((1, 1, 1, 1), np.float32)
+    g.backward((0, 0, 0), dev(coords), dev(types), dev(radii), dev(diff), ag)
+    grad_close(ag.cpu().numpy(), port.backward_index(og, (0, 0, 0), coords, types, radii, diff), "single point")
+    # vector types, no atoms
+    g, og = gm_pair(port, resolution=0.5, dimension=5.5)
+    T = 3
+    out = torch.full(g.grid_dimensions(T), 7.0, device="cuda")
+    g.forward((0, 0, 0), torch.zeros((0, 3), device="cuda"), torch.zeros((0, T), device="cuda"),
+              torch.zeros((0,), device="cuda"), out)
+    assert not out.any()
+    # 70000 atoms in one example (more than 65535), two channels
+    rng = np.random.default_rng(12)
+    n = 70000
+    coords = rng.uniform(-3.5, 3.5, (n, 3)).astype(np.float32)
+    types = rng.integers(0, 2, n).astype(np.float32)
+    radii = rng.uniform(0.8, 1.4, n).astype(np.float32)
+    out = torch.empty(g.grid_dimensions(2), device="cuda")
+    g.forward((0, 0, 0), dev(coords), dev(types), dev(radii), out)
+    want = port.forward_index(og, (0, 0, 0), coords, types, radii, 2)
+    # thousands of terms per voxel in arbitrary order: the bound is relative to the voxel's value
+    assert np.allclose(out.cpu().numpy(), want, rtol=2e-5, atol=1e-6)
+    diff = rng.normal(size=g.grid_dimensions(2)).astype(np.float32)
+    ag = torch.empty((n, 3), device="cuda")
+    g.backward((0, 0, 0), dev(coords), dev(types), dev(radii), dev(diff), ag)
+    grad_close(ag.cpu().numpy(), port.backward_index(og, (0, 0, 0), coords, types, radii, diff), "70000 atoms")

@@ -80,7 +80,7 @@ int lmg_backward_static(const lmg_gridmaker* g, const lmg_atoms* a, const float*
   if (g == nullptr || a == nullptr) return fail(LMG_ERR_INVALID_ARGUMENT, "null settings or atoms");
   if (a->batch < 0 || a->max_atoms < 0 || a->ntypes <= 0 || a->ntypes > 65535)
     return fail(LMG_ERR_INVALID_ARGUMENT, "bad batch, atom or type count");
-  if (a->type_index == nullptr || a->type_vector != nullptr)
+  if (a->type_vector != nullptr || (a->type_index == nullptr && a->batch > 0 && a->max_atoms > 0))
     return fail(LMG_ERR_INVALID_ARGUMENT, "lmg_backward_static takes index types only");
   if (g->radii_type_indexed)
     return fail(LMG_ERR_INVALID_ARGUMENT, "Type indexed radii not supported with index types.");

@@ -362,6 +362,19 @@ def run_gpu_arm(args, rank, world, local_rank):
         torch.cuda.synchronize()
         return best
     host_issue_us = host_burst(step)
+    # the same step through `import molgrid`: the compiled GridMaker (pybind11 over the C++ host layer)
+    try:
+        import molgrid as _mg
+        gc = _mg.GridMaker(0.5, 23.5)
+
+        def step_compiled():
+            gc.forward(cen, dc, dt, dr, grid, transforms=dtr, n_atoms=dn)
+            gc.backward(cen, dc, dt, dr, diff, ag, transforms=dtr, n_atoms=dn)
+        step_compiled()
+        host_issue_compiled_us = host_burst(step_compiled)
+    except Exception as e:  # the compiled module is an extra: the benchmark runs without it
+        sys.stderr.write("compiled module not measured: %r\n" % (e,))
+        host_issue_compiled_us = None
 
     # per-kernel durations in a pass of their own (CUDA events around each launch, on its stream)
     ksteps = min(args.steps, 200)
@@ -451,6 +464,7 @@ def run_gpu_arm(args, rank, world, local_rank):
                                    "bound by the host link (12.4 MB per example each way)"},
         "per_rank": per_rank,
         "host_issue_us_per_step": {"value": round(host_issue_us, 1),
+                                   "compiled_module": None if host_issue_compiled_us is None else round(host_issue_compiled_us, 1),
                                    "note": "calling thread, forward + backward through the Python layer, bursts "
                                            "of 20 steps into an idle GPU (rank 0); the host_issue_ms of per_rank "
                                            "is the device's pace once the launch queue is full"},

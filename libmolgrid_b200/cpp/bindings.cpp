@@ -26,10 +26,15 @@ namespace {
 using namespace lmgpy;
 
 // forward(center, coords, types, radii, grid): index or vector types, single example or batch
+// (plus, for batches, this library's additions: `transforms`, a (B,10) float32 CUDA tensor of
+// lmg_transform rows applied inside the kernels, and `n_atoms`, an int32 CUDA tensor of valid atoms)
 void gm_forward_arrays(const GridMaker& gm, const py::object& center, const py::object& coords,
-                       const py::object& types, const py::object& radii, const py::object& out) {
+                       const py::object& types, const py::object& radii, const py::object& out,
+                       const py::object& transforms, const py::object& n_atoms) {
   bool batched = ndim_of(coords) == 3;
   if (!batched) {
+    if (!transforms.is_none() || !n_atoms.is_none())
+      throw py::type_error("transforms= and n_atoms= belong to the batched overload");
     Arg c(coords, "coords", 2, false), r(radii, "radii", 1, false), o(out, "grid", 4, true);
     bool vec = ndim_of(types) == 2;
     Arg t(types, "types", vec ? 2 : 1, false);
@@ -47,18 +52,69 @@ void gm_forward_arrays(const GridMaker& gm, const py::object& center, const py::
       o(out, "grid", 5, true);
   bool vec = ndim_of(types) == 3;
   Arg t(types, "types", vec ? 3 : 2, false);
+  const lmg_transform* trs = nullptr;
+  const int* counts = nullptr;
+  std::unique_ptr<Arg> trarg;
+  if (!transforms.is_none()) {
+    trarg.reset(new Arg(transforms, "transforms", 2, false));
+    if (trarg->dim(0) != c.dim(0) || trarg->dim(1) != 10) throw py::value_error("transforms must be float32 of shape (batch, 10)");
+    trs = reinterpret_cast<const lmg_transform*>(trarg->dev());
+  }
+  if (!n_atoms.is_none()) counts = device_counts(n_atoms, c.dim(0));
   {
     py::gil_scoped_release nogil;
     Grid<float, 5, true> og = o.g5();
-    if (vec) gm.forward<3>(ce.g2(), c.g3(), t.g3(), r.g2(), og);
-    else gm.forward<2>(ce.g2(), c.g3(), t.g2(), r.g2(), og);
+    if (vec) gm.forward<3>(ce.g2(), c.g3(), t.g3(), r.g2(), og, trs, counts);
+    else gm.forward<2>(ce.g2(), c.g3(), t.g2(), r.g2(), og, trs, counts);
   }
   o.finish();
 }
 
+// backward for a batch (an addition of this library; the reference's overloads take one example)
+void gm_backward_batch(const GridMaker& gm, const py::object& center, const py::object& coords,
+                       const py::object& types, const py::object& radii, const py::object& diff,
+                       const py::object& atom_gradients, const py::object& type_gradients,
+                       const py::object& transforms, const py::object& n_atoms) {
+  Arg ce(center, "centers", 2, false), c(coords, "coords", 3, false), r(radii, "radii", 2, false),
+      d(diff, "diff", 5, false), ag(atom_gradients, "atom_gradients", 3, true);
+  bool vec = ndim_of(types) == 3;
+  Arg t(types, "types", vec ? 3 : 2, false);
+  std::unique_ptr<Arg> tg, trarg;
+  float* tgp = nullptr;
+  if (!type_gradients.is_none()) {
+    tg.reset(new Arg(type_gradients, "type_gradients", 3, true));
+    if (tg->dim(0) != c.dim(0) || tg->dim(1) != c.dim(1) || !vec || tg->dim(2) != t.dim(2))
+      throw py::value_error("type_gradients must have the shape of the type vectors");
+    tgp = tg->dev();
+  }
+  const lmg_transform* trs = nullptr;
+  const int* counts = nullptr;
+  if (!transforms.is_none()) {
+    trarg.reset(new Arg(transforms, "transforms", 2, false));
+    if (trarg->dim(0) != c.dim(0) || trarg->dim(1) != 10) throw py::value_error("transforms must be float32 of shape (batch, 10)");
+    trs = reinterpret_cast<const lmg_transform*>(trarg->dev());
+  }
+  if (!n_atoms.is_none()) counts = device_counts(n_atoms, c.dim(0));
+  {
+    py::gil_scoped_release nogil;
+    Grid<float, 3, true> g = ag.g3();
+    if (vec) gm.backward<3>(ce.g2(), c.g3(), t.g3(), r.g2(), d.g5(), g, tgp, trs, counts);
+    else gm.backward<2>(ce.g2(), c.g3(), t.g2(), r.g2(), d.g5(), g, tgp, trs, counts);
+  }
+  if (tg) tg->finish();
+  ag.finish();
+}
+
 void gm_backward_arrays(const GridMaker& gm, const py::object& center, const py::object& coords,
                         const py::object& types, const py::object& radii, const py::object& diff,
-                        const py::object& atom_gradients, const py::object& type_gradients) {
+                        const py::object& atom_gradients, const py::object& type_gradients,
+                        const py::object& transforms, const py::object& n_atoms) {
+  if (ndim_of(coords) == 3) {
+    gm_backward_batch(gm, center, coords, types, radii, diff, atom_gradients, type_gradients, transforms, n_atoms);
+    return;
+  }
+  if (!transforms.is_none() || !n_atoms.is_none())
+    throw py::type_error("transforms= and n_atoms= belong to the batched overload");
   Arg c(coords, "coords", 2, false), r(radii, "radii", 1, false), d(diff, "diff", 4, false),
       ag(atom_gradients, "atom_gradients", 2, true);
   bool vec = ndim_of(types) == 2;
@@ -197,9 +253,10 @@ PYBIND11_MODULE(molgrid_native, m) {
       .def("get_radii_type_indexed", &GridMaker::get_radii_type_indexed)
       .def("set_radii_type_indexed", &GridMaker::set_radii_type_indexed)
       .def("forward", &gm_forward_arrays, py::arg("center"), py::arg("coords"), py::arg("types"), py::arg("radii"),
-           py::arg("grid"))
+           py::arg("grid"), py::arg("transforms") = py::none(), py::arg("n_atoms") = py::none())
       .def("backward", &gm_backward_arrays, py::arg("center"), py::arg("coords"), py::arg("types"),
-           py::arg("radii"), py::arg("diff"), py::arg("atom_gradients"), py::arg("type_gradients") = py::none())
+           py::arg("radii"), py::arg("diff"), py::arg("atom_gradients"), py::arg("type_gradients") = py::none(),
+           py::arg("transforms") = py::none(), py::arg("n_atoms") = py::none())
       .def("backward_gradients",
            [](GridMaker& gm, const py::object& center, const py::object& coords, const py::object& types,
               const py::object& radii, const py::object& diff, const py::object& atom_gradients,

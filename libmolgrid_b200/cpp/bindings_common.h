@@ -42,9 +42,72 @@ struct ViewInfo {
   py::object keep;
 };
 
+// torch's tensor type and dtypes, looked up once (null when torch is not importable)
+struct TorchNames {
+  PyTypeObject* tensor = nullptr;
+  py::object f32, f64, i32;
+};
+inline const TorchNames& torch_names() {
+  static TorchNames* names = [] {
+    auto* n = new TorchNames();  // lives as long as the interpreter
+    try {
+      py::module_ torch = py::module_::import("torch");
+      n->f32 = torch.attr("float32");
+      n->f64 = torch.attr("float64");
+      n->i32 = torch.attr("int32");
+      n->tensor = reinterpret_cast<PyTypeObject*>(torch.attr("Tensor").ptr());
+    } catch (py::error_already_set&) {
+      n->tensor = nullptr;
+    }
+    return n;
+  }();
+  return *names;
+}
+
+// The common case of a training loop, a plain contiguous torch tensor, read with as few attribute
+// look-ups as its checks need.  False: not such a tensor, take the general route.
+inline bool tensor_view(const py::object& o, const std::string& name, ViewInfo& v) {
+  const TorchNames& tn = torch_names();
+  if (tn.tensor == nullptr || Py_TYPE(o.ptr()) != tn.tensor) return false;
+  py::object dt = o.attr("dtype");
+  if (dt.is(tn.f32)) v.is_double = false;
+  else if (dt.is(tn.f64)) v.is_double = true;
+  else throw py::value_error(name + ": tensors must be float32 or float64");
+  if (!o.attr("is_contiguous")().cast<bool>()) throw py::value_error("Attempt to use non-contiguous tensor as grid");
+  int dev = o.attr("get_device")().cast<int>();  // -1 for a host tensor
+  v.cuda = dev >= 0;
+  if (v.cuda) {
+    int cur = 0;
+    LMG_CUDA_CHECK(cudaGetDevice(&cur));
+    if (dev != cur)
+      throw py::value_error("Tensor on different device than current: " + std::to_string(dev) + " vs " +
+                            std::to_string(cur));
+  }
+  v.ptr = reinterpret_cast<void*>(o.attr("data_ptr")().cast<size_t>());
+  py::tuple shape = py::reinterpret_borrow<py::tuple>(o.attr("shape"));  // torch.Size is a tuple
+  v.shape.reserve(shape.size());
+  for (auto d : shape) v.shape.push_back(d.cast<size_t>());
+  v.keep = o;
+  return true;
+}
+
+// A resident int32 tensor with one entry per example (valid atoms of a padded batch), or a
+// resident float32 (B,10) tensor of transforms: the device address, after the checks.
+inline const int* device_counts(const py::object& o, size_t batch) {
+  const TorchNames& tn = torch_names();
+  if (tn.tensor == nullptr || !py::isinstance(o, py::reinterpret_borrow<py::object>((PyObject*)tn.tensor)))
+    throw py::type_error("n_atoms: expected an int32 CUDA tensor");
+  py::object dt = o.attr("dtype");
+  if (!dt.is(tn.i32) || o.attr("get_device")().cast<int>() < 0 || !o.attr("is_contiguous")().cast<bool>())
+    throw py::type_error("n_atoms: expected a contiguous int32 CUDA tensor");
+  if (o.attr("numel")().cast<size_t>() != batch) throw py::value_error("n_atoms must have one entry per example");
+  return reinterpret_cast<const int*>(o.attr("data_ptr")().cast<size_t>());
+}
+
 inline ViewInfo view_info(const py::handle& h, const std::string& name) {
   ViewInfo v;
   py::object o = py::reinterpret_borrow<py::object>(h);
+  if (tensor_view(o, name, v)) return v;
   if (py::hasattr(o, "ongpu") && py::hasattr(o, "gpu")) o = gpu_enabled() ? o.attr("gpu")() : o.attr("cpu")();
   if (py::hasattr(o, "t") && py::hasattr(o, "dimension")) o = o.attr("t");  // Grid view of the ctypes layer
   if (py::hasattr(o, "_lmg_ptr")) {

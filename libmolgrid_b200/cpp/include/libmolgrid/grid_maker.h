@@ -94,9 +94,13 @@ class GridMaker {
   }
 
   // batched raw arrays: one launch sequence for the whole batch (the reference loops on the host)
+  // `transforms` (device, one lmg_transform per example, applied to the coordinates inside the
+  // kernels) and `n_atoms` (device, valid atoms per example of a padded batch) are this library's
+  // additions; both may be null.
   template <int N>
   void forward(const Grid<float, 2, true>& centers, const Grid<float, 3, true>& coords, const Grid<float, N, true>& types,
-               const Grid<float, 2, true>& radii, Grid<float, 5, true>& out) const {
+               const Grid<float, 2, true>& radii, Grid<float, 5, true>& out, const lmg_transform* transforms = nullptr,
+               const int* n_atoms = nullptr) const {
     static_assert(N == 2 || N == 3, "Unsupported types dimension");
     size_t B = centers.dimension(0);
     batch_check(coords.dimension(0), B); batch_check(types.dimension(0), B);
@@ -106,9 +110,43 @@ class GridMaker {
     lmg_atoms a = {};
     a.batch = (int)B; a.max_atoms = (int)coords.dimension(1); a.ntypes = (int)out.dimension(1);
     a.coords = coords.data(); a.radii = radii.data(); a.centers = centers.data();
+    a.transforms = transforms; a.n_atoms = n_atoms;
     if (N == 2) a.type_index = types.data(); else a.type_vector = types.data();
     if (N == 3) check_vector_radii(radii.dimension(1), coords.dimension(1), types.dimension(N - 1), true);
     run_forward(a, out.data(), N == 3);
+  }
+
+  // batched backward (an addition: the reference loops over the examples on the host):
+  // atom_gradients[B][N][3], and type_gradients[B][N][T] with vector types (null: not wanted)
+  template <int N>
+  void backward(const Grid<float, 2, true>& centers, const Grid<float, 3, true>& coords, const Grid<float, N, true>& types,
+                const Grid<float, 2, true>& radii, const Grid<float, 5, true>& diff, Grid<float, 3, true>& atom_gradients,
+                float* type_gradients = nullptr, const lmg_transform* transforms = nullptr, const int* n_atoms = nullptr) const {
+    static_assert(N == 2 || N == 3, "Unsupported types dimension");
+    size_t B = centers.dimension(0), n = coords.dimension(1);
+    batch_check(coords.dimension(0), B); batch_check(types.dimension(0), B); batch_check(radii.dimension(0), B);
+    batch_check(diff.dimension(0), B); batch_check(atom_gradients.dimension(0), B);
+    if (N == 2 && s_.radii_type_indexed) throw std::invalid_argument("Type indexed radii not supported with index types.");
+    if (types.dimension(1) != n) throw std::invalid_argument("Type dimension doesn't equal number of coordinates.");
+    if (atom_gradients.dimension(1) != n) throw std::invalid_argument("Gradient dimension doesn't equal number of coordinates");
+    if (coords.dimension(2) != 3 || atom_gradients.dimension(2) != 3) throw std::invalid_argument("Need x,y,z,r for coord_radius");
+    for (int i = 2; i <= 4; i++)
+      if (diff.dimension(i) != s_.dim) throw std::invalid_argument("Incorrect grid dimension for diff");
+    size_t T = diff.dimension(1);
+    if (N == 3) {
+      if (types.dimension(2) != T) throw std::invalid_argument("Channels in diff doesn't equal number of types");
+      check_vector_radii(radii.dimension(1), n, T, false);
+    } else {
+      if (radii.dimension(1) != n) throw std::invalid_argument("Radii dimension doesn't equal number of coordinates");
+      if (type_gradients != nullptr) throw std::invalid_argument("type_gradients given with index types");
+    }
+    lmg_atoms a = {};
+    a.batch = (int)B; a.max_atoms = (int)n; a.ntypes = (int)T;
+    a.coords = coords.data(); a.radii = radii.data(); a.centers = centers.data();
+    a.transforms = transforms; a.n_atoms = n_atoms;
+    if (N == 2) a.type_index = types.data(); else a.type_vector = types.data();
+    size_t bytes = lmg_workspace_bytes(&s_, LMG_OP_BACKWARD, (int)B, (int)n, (int)T, N == 3);
+    detail::check(lmg_backward(&s_, &a, diff.data(), atom_gradients.data(), type_gradients, detail::workspace(bytes), bytes, nullptr));
   }
 
   void forward(float3 grid_center, const CoordinateSet& in, Grid<float, 4, true>& out, const Transform* transform = nullptr) const {

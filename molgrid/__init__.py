@@ -7,9 +7,10 @@ reaches the kernels through C++, as it does in the reference.  What the compiled
 define comes from the Python layer of ``libmolgrid_b200``: atom typers, pre-typed file readers, the
 example provider (which hands out the compiled Example / CoordinateSet types here), the device-side
 batch assembly and the torch.autograd bindings.  Calls that use this library's extensions to the
-reference interface (per-example ``transforms=`` / ``n_atoms=`` on the array overloads, batched
-backward, ``DeviceBatch`` arguments) are served by the Python layer's GridMaker with the same
-settings.
+reference interface are served by the compiled GridMaker when every argument is a CUDA tensor
+(batched arrays with per-example ``transforms=`` and ``n_atoms=``, batched backward: the calls of a
+training loop) and by the Python layer's GridMaker with the same settings otherwise (host arrays,
+lists of Transform objects, ``DeviceBatch`` arguments).
 """
 import numpy as np
 
@@ -69,7 +70,23 @@ class GridMaker(native.GridMaker):
             return True
         return bool(args) and isinstance(args[0], _DeviceBatch)
 
+    @staticmethod
+    def _resident_batch(args, kw):
+        """A batch the compiled module takes as it is: every array a CUDA tensor, per-example
+        transforms as a (B,10) float32 CUDA tensor, atom counts as an int32 CUDA tensor."""
+        import torch
+        if len(args) < 5 or _ndim(args[1]) != 3 or set(kw) - {"transforms", "n_atoms"}:
+            return False
+        if not all(type(x) is torch.Tensor and x.is_cuda for x in args):
+            return False
+        tr, na = kw.get("transforms"), kw.get("n_atoms")
+        if tr is not None and not (type(tr) is torch.Tensor and tr.is_cuda and tr.dtype is torch.float32):
+            return False
+        return na is None or (type(na) is torch.Tensor and na.is_cuda and na.dtype is torch.int32)
+
     def forward(self, *args, **kw):
+        if self._resident_batch(args, kw):
+            return native.GridMaker.forward(self, *args, **kw)
         # a batch of arrays about one common centre given as a tuple is this library's shorthand
         one_centre = len(args) > 1 and _ndim(args[1]) == 3 and _ndim(args[0]) < 0
         if self._extension(args, kw) or one_centre:
@@ -77,6 +94,8 @@ class GridMaker(native.GridMaker):
         return native.GridMaker.forward(self, *args, **kw)
 
     def backward(self, *args, **kw):
+        if self._resident_batch(args, kw):
+            return native.GridMaker.backward(self, *args, **kw)
         batched = len(args) > 1 and _ndim(args[1]) == 3
         if self._extension(args, kw) or batched:
             return self._twin().backward(*args, **kw)

@@ -94,3 +94,43 @@ def test_autograd_on_the_compiled_gridmaker(molgrid):
     for a, b in zip(*results):
         assert torch.allclose(a, b, rtol=1e-5, atol=1e-6)
     assert float(results[0][1].abs().max()) > 0
+
+
+@pytest.mark.parametrize("vector", [False, True])
+def test_resident_batches_take_the_compiled_route(molgrid, vector):
+    """Batched CUDA tensors with per-example transforms and ragged atom counts: the compiled GridMaker
+    serves them (forward and the batched backward), with the results of the Python layer's calls."""
+    import libmolgrid_b200 as lmg
+    from libmolgrid_b200 import synthetic as cases
+    B, T = 3, 6
+    coords, types, radii, ns, tr = cases.blob_batch(77, B, 200, 300, T)
+    if vector:
+        tv = np.zeros(types.shape + (T,), np.float32)
+        np.put_along_axis(tv, types.astype(np.int64)[..., None], 0.75, axis=2)
+        tv[..., 0] += 0.25
+        types = tv
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    dc, dt, dr, dtr, dn = d(coords), d(types), d(radii), d(tr), d(ns)
+    cen = torch.zeros((B, 3), device="cuda")
+    gm, gp = molgrid.GridMaker(0.5, 11.5), lmg.GridMaker(0.5, 11.5)
+    assert gm._resident_batch((cen, dc, dt, dr, None), dict(transforms=dtr, n_atoms=dn)) is False  # None is no tensor
+    a = torch.full((B,) + gm.grid_dimensions(T), 3.0, device="cuda")
+    b = torch.full_like(a, 4.0)
+    assert gm._resident_batch((cen, dc, dt, dr, a), dict(transforms=dtr, n_atoms=dn))
+    gm.forward(cen, dc, dt, dr, a, transforms=dtr, n_atoms=dn)
+    gp.forward(cen, dc, dt, dr, b, transforms=dtr, n_atoms=dn)
+    assert torch.allclose(a, b, rtol=1e-5, atol=1e-6) and float(a.sum()) > 0
+    diff = torch.randn_like(a)
+    N = coords.shape[1]
+    ag, ag2 = torch.full((B, N, 3), 9.0, device="cuda"), torch.full((B, N, 3), 8.0, device="cuda")
+    if vector:
+        tg, tg2 = torch.full((B, N, T), 9.0, device="cuda"), torch.full((B, N, T), 8.0, device="cuda")
+        gm.backward(cen, dc, dt, dr, diff, ag, tg, transforms=dtr, n_atoms=dn)
+        gp.backward(cen, dc, dt, dr, diff, ag2, tg2, transforms=dtr, n_atoms=dn)
+        assert torch.equal(tg, tg2)
+    else:
+        gm.backward(cen, dc, dt, dr, diff, ag, transforms=dtr, n_atoms=dn)
+        gp.backward(cen, dc, dt, dr, diff, ag2, transforms=dtr, n_atoms=dn)
+    assert torch.equal(ag, ag2)            # the backward kernels sum in a fixed order
+    with pytest.raises((TypeError, ValueError)):
+        molgrid.native.GridMaker.forward(gm, cen, dc, dt, dr, a, transforms=dtr[:, :9].contiguous())

@@ -325,7 +325,8 @@ class Example(object):
             return CoordinateSet()
         if len(self.coord_sets) == start + 1:
             return self.coord_sets[start].clone()
-        return self._merged(start, unique, force_vector=not has_ind)
+        # vector types win when every non-empty set has them (src/example.cpp:211-227)
+        return self._merged(start, unique, force_vector=has_vec)
 
     def _merged(self, start, unique, force_vector):
         sets = self.coord_sets[start:]

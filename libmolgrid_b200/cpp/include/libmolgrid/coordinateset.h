@@ -1,7 +1,7 @@
 // CoordinateSet and Example: the containers the GridMaker/Transform convenience overloads take
 // (reference: include/libmolgrid/coordinateset.h, include/libmolgrid/example.h).  Only what feeds the
 // gridding path is here: construction from arrays, type queries, center(), host/device residency,
-// clone(), and Example::merge_coordinates for index types.  Construction from OpenBabel molecules
+// clone(), and Example::merge_coordinates.  Construction from OpenBabel molecules
 // and the type-summing helpers are not part of this library.
 #ifndef LMGB200_COORDINATESET_H_
 #define LMGB200_COORDINATESET_H_
@@ -112,9 +112,27 @@ struct Example {
     return unique_index_types ? total : mx;
   }
 
-  // Concatenation of the sets from `start` on (reference: src/example.cpp:80-110): empty sets are
-  // skipped, and with unique_index_types each set's type indices are shifted past the previous sets'.
+  // every non-empty set from `start` on has vector (index) types; empty sets count as both
+  bool has_vector_types(unsigned start = 0) const {
+    for (size_t i = start; i < sets.size(); i++)
+      if (sets[i].size() > 0 && !sets[i].has_vector_types()) return false;
+    return true;
+  }
+  bool has_index_types(unsigned start = 0) const {
+    for (size_t i = start; i < sets.size(); i++)
+      if (sets[i].size() > 0 && !sets[i].has_indexed_types()) return false;
+    return true;
+  }
+
+  // Concatenation of the sets from `start` on (reference: src/example.cpp:80-110, 147-228): empty
+  // sets are skipped, and with unique_index_types each set's types are shifted past the previous
+  // sets'.  Vector types are merged when every non-empty set has them, index types otherwise.
   CoordinateSet merge_coordinates(unsigned start = 0, bool unique_index_types = true) const {
+    bool has_vec = has_vector_types(start), has_ind = has_index_types(start);
+    if (!has_ind && !has_vec) throw std::invalid_argument("Inconsistent typing schemes in merge_coordinates");
+    if (sets.size() <= start) return CoordinateSet();
+    if (sets.size() == start + 1) return sets[start].clone();
+    if (has_vec) return merge_vector_types(start, unique_index_types);
     std::vector<float3> c;
     std::vector<float> t, r;
     unsigned shift = 0;
@@ -137,6 +155,45 @@ struct Example {
     for (size_t s = start; s < sets.size(); s++)
       maxt = unique_index_types ? maxt + sets[s].max_type : std::max(maxt, sets[s].max_type);
     return CoordinateSet(c, t, r, maxt);
+  }
+
+ private:
+  // type vectors side by side (or over one another), radii concatenated as they are: per atom, or
+  // per type after make_vector_types (src/example.cpp:147-196)
+  CoordinateSet merge_vector_types(unsigned start, bool unique_index_types) const {
+    unsigned maxt = 0;
+    for (size_t i = start; i < sets.size(); i++) {
+      maxt = unique_index_types ? maxt + sets[i].max_type : std::max(maxt, sets[i].max_type);
+      if (sets[i].size() == 0) continue;
+      if (sets[i].max_type != sets[i].type_vector.dimension(1))
+        throw std::logic_error("Coordinate set " + itoa(i) + " does not have consistent max_type/vector type sizes");
+    }
+    std::vector<float3> c;
+    std::vector<std::vector<float>> t;
+    std::vector<float> r;
+    unsigned offset = 0;
+    for (size_t s = start; s < sets.size(); s++) {
+      const CoordinateSet& cs = sets[s];
+      unsigned n = cs.size();
+      if (n > 0) {
+        Grid2f cc = cs.coords.cpu(), tv = cs.type_vector.cpu();
+        unsigned w = (unsigned)tv.dimension(1);
+        if (offset + w > maxt) throw std::logic_error("Incompatible vector sizes in merge_coordinates");
+        for (unsigned i = 0; i < n; i++) {
+          c.push_back(make_float3(cc(i, 0), cc(i, 1), cc(i, 2)));
+          std::vector<float> row(maxt, 0.f);
+          for (unsigned k = 0; k < w; k++) row[offset + k] = tv(i, k);
+          t.push_back(row);
+        }
+      }
+      Grid1f rr = cs.radii.cpu();
+      for (unsigned i = 0; i < rr.size(); i++) r.push_back(rr(i));
+      if (unique_index_types) offset += cs.max_type;
+    }
+    CoordinateSet out(c, t, r);
+    out.max_type = maxt;
+    if (c.empty()) out.type_vector = MGrid2f(0, maxt);
+    return out;
   }
 };
 

@@ -240,3 +240,56 @@ def test_device_batches_follow_the_order_settings(provider_dir, settings):
             keep = types[b, :ns[b]] >= 0
             np.testing.assert_array_equal(coords[b, :ns[b]][keep], m.coords.tonumpy())
             np.testing.assert_array_equal(types[b, :ns[b]][keep], m.type_index.tonumpy())
+
+
+def test_vector_typed_examples_grid_like_index_typed_ones(provider_dir):
+    """make_vector_types (one-hot vectors, radii by type) grids like the index-typed examples
+    (test/test_gridmaker.py:281-340), into CUDA and host tensors alike."""
+    ps = []
+    for vec in (False, True):
+        p = coord_cache.ExampleProvider(data_root=str(provider_dir), make_vector_types=vec)
+        p.populate(str(provider_dir / "list.types"))
+        ps.append(p)
+    g = molgrid.GridMaker(0.5, 23.5)
+    gv = molgrid.GridMaker(0.5, 23.5, radius_type_indexed=True)
+    for _ in range(3):
+        ex, exv = ps[0].next(), ps[1].next()
+        assert exv.has_vector_types() and not ex.has_vector_types()
+        dims = g.grid_dimensions(ex.num_types())
+        a = torch.zeros(dims, device="cuda")
+        b = torch.zeros(dims, device="cuda")
+        host = torch.zeros(dims)
+        g.forward(ex, a)
+        gv.forward(exv, b)
+        gv.forward(exv, host)
+        assert float(a.max()) > 0
+        assert torch.allclose(host, b.cpu(), rtol=1e-5, atol=1e-6)
+        # channels that group types of different radii (4: the heavier halogens, 13: the metals) get
+        # the mean radius of the group as their type radius, so only the other channels must agree
+        same = [c for c in range(dims[0]) if c % 14 not in (4, 13)]
+        assert torch.allclose(a[same], b[same], rtol=1e-5, atol=1e-6)
+        assert not torch.allclose(a[[4, 13]], b[[4, 13]], rtol=1e-5, atol=1e-6)
+
+
+def test_duplicated_first_set_grids_on_device_and_host(tmp_path):
+    """duplicate_first with three files per line: four sets per example, the first one twice; grids
+    into CUDA and host tensors agree (test/test_gridmaker.py:342-362)."""
+    rng = np.random.default_rng(5)
+    for name, n, spread in (("r.gninatypes", 200, 6.0), ("a.gninatypes", 12, 2.0), ("b.gninatypes", 9, 2.0)):
+        coord_cache.write_gninatypes(tmp_path / name, rng.normal(size=(n, 3)) * spread, rng.integers(2, 14, n))
+    (tmp_path / "dup.types").write_text("1 r.gninatypes a.gninatypes b.gninatypes\n")
+    p = coord_cache.ExampleProvider(data_root=str(tmp_path), duplicate_first=True)
+    p.populate(str(tmp_path / "dup.types"))
+    batch = p.next_batch(1)
+    assert len(batch[0].coord_sets) == 4 and p.num_types() == batch[0].num_types()
+    g = molgrid.GridMaker(0.5, 23.5)
+    shape = (1,) + g.grid_dimensions(p.num_types())
+    dev_out, host_out = torch.zeros(shape, device="cuda"), torch.zeros(shape)
+    g.forward(batch, dev_out, random_translation=0.0, random_rotation=False)
+    g.forward(batch, host_out, random_translation=0.0, random_rotation=False)
+    assert torch.allclose(dev_out.cpu(), host_out, rtol=1e-5, atol=1e-6) and 0 < float(dev_out.max()) < 75
+    T0 = p.caches[0].num_types()
+    T1 = p.caches[1].num_types()
+    # the receptor's channels appear twice, before each ligand's
+    assert torch.equal(dev_out[0, :T0], dev_out[0, T0 + T1:2 * T0 + T1]) or \
+        torch.allclose(dev_out[0, :T0], dev_out[0, T0 + T1:2 * T0 + T1], rtol=1e-5, atol=1e-6)

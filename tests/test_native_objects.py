@@ -194,3 +194,34 @@ def test_object_overloads_on_the_gpu(n, port):
     assert gt.shape == dims and gt[0, 3, 3, 3] == float(out[0, 3, 3, 3])
     with pytest.raises(TypeError):
         n.Grid4f(out)
+
+
+def test_merge_prefers_vector_types_in_both_layers():
+    """Sets that carry index AND vector types (after make_vector_types) merge as vector types, type
+    vectors side by side and the radii concatenated (src/example.cpp:198-228), in the compiled classes
+    and in the Python layer alike."""
+    import libmolgrid_b200 as molgrid
+    from libmolgrid_b200 import molgrid_native
+    rng = np.random.default_rng(4)
+    merged = []
+    for mod in (molgrid, molgrid_native):
+        ex = mod.Example()
+        for n, T in ((5, 3), (0, 2), (4, 2)):
+            c = rng.normal(size=(n, 3)).astype(np.float32)
+            t = rng.integers(0, T, n).astype(np.float32)
+            r = rng.uniform(1, 2, n).astype(np.float32)
+            cs = mod.CoordinateSet(c, t, r, T) if n else mod.CoordinateSet()
+            if n:
+                cs.make_vector_types(False, [1.0 + k for k in range(T)])
+            else:
+                cs.max_type = T
+            ex.coord_sets.append(cs)
+        rng = np.random.default_rng(4)      # the same numbers for the second module
+        m = ex.merge_coordinates()
+        assert m.has_vector_types() and m.max_type == 7
+        merged.append((m.coords.tonumpy(), m.type_vector.tonumpy(), m.radii.tonumpy()))
+    for a, b in zip(*merged):
+        assert np.array_equal(a, b)
+    tv, radii = merged[0][1], merged[0][2]
+    assert tv.shape == (9, 7) and not tv[:5, 3:].any() and not tv[5:, :5].any() and np.array_equal(tv.sum(1), np.ones(9))
+    assert np.array_equal(radii, [1, 2, 3, 1, 2])          # by type: set 0's three, set 2's two

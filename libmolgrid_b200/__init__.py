@@ -12,8 +12,9 @@ from .torch_bindings import (Coords2Grid, Coords2GridFunction, BatchedCoords2Gri
 from .grids import *  # noqa: F401,F403  Grid1f..Grid8dCUDA, MGrid1f..MGrid8d, set/get_gpu_enabled, ...
 from .grids import __all__ as _grid_names
 from .coordinates import CoordinateSet, Example, ExampleVec  # noqa: F401
-from .atom_typing import (GninaIndexTyper, FileAtomMapper, FileMappedGninaTyper,  # noqa: F401
-                          default_receptor_typer, default_ligand_typer)
+from .atom_typing import (GninaIndexTyper, FileAtomMapper, FileMappedGninaTyper, NullIndexTyper,  # noqa: F401
+                          default_receptor_typer, default_ligand_typer, defaultGninaReceptorTyper,
+                          defaultGninaLigandTyper)
 from .coord_cache import (CoordCache, DeviceBatch, ExampleDataset, ExampleProvider,  # noqa: F401
                           read_gninatypes)
 from .example_order import ExampleProviderSettings, IterationScheme  # noqa: F401
@@ -22,6 +23,7 @@ from . import _cabi  # noqa: F401
 __all__ = ["GridMaker", "GridInterpolater", "Transform", "Quaternion", "float3", "set_random_seed",
            "Coords2Grid", "Coords2GridFunction", "BatchedCoords2GridFunction", "Grid2CoordsGradientFunction",
            "CoordinateSet", "Example", "ExampleVec", "GninaIndexTyper", "FileAtomMapper",
-           "FileMappedGninaTyper", "default_receptor_typer", "default_ligand_typer", "CoordCache",
+           "FileMappedGninaTyper", "NullIndexTyper", "default_receptor_typer", "default_ligand_typer",
+           "defaultGninaReceptorTyper", "defaultGninaLigandTyper", "CoordCache",
            "ExampleProvider", "ExampleDataset", "ExampleProviderSettings", "IterationScheme", "DeviceBatch",
            "read_gninatypes"] + list(_grid_names)

@@ -201,3 +201,33 @@ def default_receptor_typer():
 
 def default_ligand_typer():
     return FileMappedGninaTyper(DEFAULT_LIGMAP)
+
+
+class NullIndexTyper(object):
+    """No types at all: every atom is dropped and the coordinate sets it types take no channels
+    (include/libmolgrid/atom_typer.h: NullIndexTyper).  For examples whose first file is only a
+    place holder."""
+
+    def num_types(self):
+        return 0
+
+    def get_type_names(self):
+        return []
+
+    def get_type_radii(self):
+        return []
+
+    def is_vector_typer(self):
+        return False
+
+    def get_int_type(self, t):
+        return -1, 0.0
+
+    def map_types(self, raw):
+        raw = np.asarray(raw)
+        return np.full(raw.shape, -1, dtype=np.int64), np.zeros(raw.shape, dtype=np.float32)
+
+
+# the reference's module-level instances (python/bindings.in.cpp: defaultGninaLigandTyper, ...)
+defaultGninaReceptorTyper = default_receptor_typer()
+defaultGninaLigandTyper = default_ligand_typer()

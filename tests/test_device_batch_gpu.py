@@ -293,3 +293,31 @@ def test_duplicated_first_set_grids_on_device_and_host(tmp_path):
     # the receptor's channels appear twice, before each ligand's
     assert torch.equal(dev_out[0, :T0], dev_out[0, T0 + T1:2 * T0 + T1]) or \
         torch.allclose(dev_out[0, :T0], dev_out[0, T0 + T1:2 * T0 + T1], rtol=1e-5, atol=1e-6)
+
+
+def test_device_batch_with_a_null_typer(provider_dir):
+    """The receptor typed by NullIndexTyper: no receptor atom survives, the ligand's channels start
+    at zero, on the host path and in the device batch alike."""
+    ps = []
+    for _ in range(2):
+        p = coord_cache.ExampleProvider(molgrid.NullIndexTyper(), molgrid.defaultGninaLigandTyper,
+                                        data_root=str(provider_dir))
+        p.populate(str(provider_dir / "list.types"))
+        ps.append(p)
+    assert ps[0].num_types() == 14
+    exs = ps[0].next_batch(5)
+    batch = ps[1].next_device_batch(5).check()
+    types, ns = batch.type_index.cpu().numpy(), batch.n_atoms.cpu().numpy()
+    coords = batch.coords.cpu().numpy()
+    for b, ex in enumerate(exs):
+        assert ex.coord_sets[0].size() == 0 and ex.num_types() == 14
+        m = ex.merge_coordinates()
+        keep = types[b, :ns[b]] >= 0
+        np.testing.assert_array_equal(types[b, :ns[b]][keep], m.type_index.tonumpy())
+        np.testing.assert_array_equal(coords[b, :ns[b]][keep], m.coords.tonumpy())
+    g = molgrid.GridMaker(0.5, 23.5)
+    a = torch.zeros((5,) + g.grid_dimensions(14), device="cuda")
+    b = torch.zeros_like(a)
+    g.forward(batch, a)
+    g.forward(exs, b)
+    assert torch.allclose(a, b, rtol=1e-5, atol=1e-6) and float(a.max()) > 0

@@ -223,3 +223,35 @@ def test_mem_caches_round_trip(lists, tmp_path_factory):
     for name, coords in want:
         x = q.next()
         assert _lig(x) == name and np.array_equal(x.coord_sets[1].coords.tonumpy(), coords)
+
+
+def test_null_typer_and_type_sums_of_a_batch(lists):
+    """A receptor typed by NullIndexTyper takes no channels; provider and examples agree on the number
+    of types; ExampleVec.sum_types counts the atoms of every type per example, the same into an MGrid
+    and a numpy array (test/test_example_provider.py:236-302)."""
+    d, f, _ = lists
+    e = molgrid.ExampleProvider(molgrid.NullIndexTyper(), molgrid.defaultGninaLigandTyper, data_root=str(d),
+                                make_vector_types=True)
+    e.populate(f)
+    b = e.next_batch(10)
+    assert e.num_types() == 14 and b[0].num_types() == 14
+    assert b[0].coord_sets[0].has_vector_types() and b[0].coord_sets[1].has_vector_types()
+    c = b[0].merge_coordinates()
+    tv = c.type_vector.tonumpy()
+    assert tv.shape == (c.size(), 14) and np.array_equal(tv.sum(1), np.ones(c.size()))
+    sums = molgrid.MGrid2f(10, e.num_types())
+    b.sum_types(sums)
+    sums2 = np.zeros((10, 14), np.float32)
+    b.sum_types(sums2)
+    assert np.array_equal(sums.tonumpy(), sums2)
+    for i, ex in enumerate(b):
+        assert sums2[i].sum() == ex.coord_sets[1].size()
+        assert np.array_equal(sums2[i], ex.coord_sets[1].type_vector.tonumpy().sum(0))
+    # with both default typers the example has 28 types and the sums fill the ligand's half as above
+    e2 = molgrid.ExampleProvider(data_root=str(d), make_vector_types=True)
+    e2.populate(f)
+    b2 = e2.next_batch(10)
+    assert e2.num_types() == b2[0].num_types() == 28
+    s28 = np.zeros((10, 28), np.float32)
+    b2.sum_types(s28)
+    assert np.array_equal(s28[:, 14:], sums2)

@@ -207,3 +207,32 @@ def test_interpolate_backward_is_the_adjoint(gi):
     assert abs(float((fb.double() * yb.double()).sum()) - float((xb.double() * bb.double()).sum())) <= 1e-5 * scale
     with pytest.raises(ValueError):
         g.backward(y, tr, torch.empty_like(y) if din != dout else y)
+
+
+@pytest.mark.parametrize("layer", ["python", "compiled"])
+def test_transform_known_answers_on_host_arrays_and_in_place(layer):
+    """The reference's worked example (test/test_transform.py:65-140): a quarter turn about z through
+    (0,1,1) then a shift by (2,0,-3), on numpy arrays and MGrids, the input left unchanged; a random
+    transform undone in place."""
+    if layer == "python":
+        import libmolgrid_b200 as mg
+    else:
+        import molgrid as mg
+    from math import sqrt
+    q = mg.Quaternion(sqrt(0.5), 0, 0, sqrt(0.5))
+    nr = mg.Transform(q, mg.float3(0, 1, 1), mg.float3(2, 0, -3))
+    data = np.array([[0, 0, 0], [1, 0, 0], [0, 1, 0], [0, 0, 1], [-1, .5, 3], [1, 1, 1], [0, 1, 1], [.333, .75, -9]],
+                    np.float32)
+    coords, out = data.copy(), np.zeros((8, 3), np.float32)
+    nr.forward(coords, out)
+    assert tuple(out[6]) == (2, 1, -2) and tuple(out[2]) == (2, 1, -3) and tuple(out[5]) == (2, 2, -2)
+    assert np.array_equal(coords, data)
+    m_in, m_out = mg.MGrid2f(8, 3), mg.MGrid2f(8, 3)
+    m_in.copyFrom(data)
+    nr.forward(m_in, m_out)
+    assert np.array_equal(m_out.tonumpy(), out)
+    r = mg.Transform(mg.float3(0, 1, 1), 10.0, True)
+    r.forward(coords, out)
+    assert not np.isclose(out, coords, atol=1e-5).all(axis=1).any()
+    r.backward(out, out)                                   # in place
+    assert np.allclose(out, coords, atol=1e-5)

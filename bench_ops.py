@@ -224,6 +224,10 @@ def main():
         from libmolgrid_b200 import coord_cache
         rng = np.random.default_rng(1006)
         B, nex = 50, 100
+        # wall-clock section: nothing of the earlier operations may still be queued, and their
+        # cached device memory goes back first (a later cudaMalloc would otherwise free it mid-run)
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
         with tempfile.TemporaryDirectory() as tmp:
             lines = []
             for i in range(nex):

@@ -46,7 +46,7 @@ WORKLOAD_C4A = ("one batch of 1024 x [2000,4000] index-typed atoms (70% in a 4A 
 # example: every example's grids are separate and larger than what L2 keeps, so traffic grows in
 # proportion).  forward = the fill's own 12,386,304 B + the scatter kernel's 6.50 MB of read-modify-
 # write on the sectors atoms touch; backward = the touched part of the grid gradient.
-NCU_TRAFFIC_PER_EXAMPLE = {"forward": 12386304 + 6.50e6, "backward": 6.88e6}
+NCU_TRAFFIC_PER_EXAMPLE = {"forward": 12386304 + 6.59e6, "backward": 6.87e6}
 
 
 # ------------------------------------------------------------------------------------------------

@@ -44,7 +44,7 @@ WORKLOAD_C4A = ("one batch of 1024 x [2000,4000] index-typed atoms (70% in a 4A 
                 "example over the GPUs; forward with fused rotation+translation, then backward")
 # dram bytes per example from the ncu captures summarised under profiles/ (batch 12, scaled per
 # example: every example's grids are separate and larger than what L2 keeps, so traffic grows in
-# proportion).  forward = the fill's own 12,386,304 B + the scatter kernel's 6.50 MB of read-modify-
+# proportion).  forward = the fill's own 12,386,304 B + the scatter kernel's 6.59 MB of read-modify-
 # write on the sectors atoms touch; backward = the touched part of the grid gradient.
 NCU_TRAFFIC_PER_EXAMPLE = {"forward": 12386304 + 6.59e6, "backward": 6.87e6}
 

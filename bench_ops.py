@@ -213,6 +213,9 @@ def main():
         trs = [lmg.Transform(lmg.Quaternion(*[float(v) for v in q[b]]), (0, 0, 0),
                              tuple(float(v) for v in rng.uniform(-2, 2, 3))) for b in range(B)]
         ms = timeit(lambda: gi.forward(src, trs, dst))
+        from libmolgrid_b200 import _cabi
+        # a staged box that did not arrive would have sent its block down the slower direct reads
+        assert _cabi.lib().lmg_tma_timeouts() == 0, "tensor copies timed out during the interpolation"
         report("interpolate", "28x48^3 -> 28x48^3, batch %d, random rotation and translation" % B, ms, B,
                2 * src.numel() * 4)
 

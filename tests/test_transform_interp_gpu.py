@@ -15,6 +15,15 @@ def dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
+@pytest.fixture(autouse=True)
+def _no_copy_timeouts():
+    """No block of the tiled interpolation ever gave up waiting for its staged box."""
+    yield
+    from libmolgrid_b200 import _cabi
+    torch.cuda.synchronize()
+    assert _cabi.lib().lmg_tma_timeouts() == 0
+
+
 def make_transform(q, c, t):
     import libmolgrid_b200 as lmg
     return lmg.Transform(lmg.Quaternion(*q), tuple(c), tuple(t))

@@ -3,6 +3,7 @@
 // The input holds seeded arrays written by tests/test_cpp_api_gpu.py, which also checks the arrays
 // this program writes against the CPU oracle.  Structural checks (exceptions, MGrid behaviour) are
 // asserted here and reported through the exit code.
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <vector>
@@ -318,6 +319,102 @@ int main(int argc, char** argv) {
     EXPECT_THROW(m[3], std::out_of_range);
     Grid2f v = m.cpu();
     EXPECT(v[1][2] == 5.f && v(1, 3) == 7.f && v.offset(0) == 4 && v.size() == 12);
+  }
+
+  // ---- 10. batched arrays with per-example transforms and ragged atom counts (additions of this
+  // library): the batch equals the examples gridded one by one; batched backward likewise, bit for bit
+  {
+    const int B = 2, NB = N;                 // example 1 uses only the first NL atoms of the padded row
+    MGrid3f bc(B, NB, 3);
+    MGrid2f bt(B, NB), br(B, NB), cen(B, 3), trs(B, 10);
+    for (int b = 0; b < B; b++) {
+      int n = b == 0 ? N : NL;
+      const std::vector<float>& cs = b == 0 ? coords : lcoords;
+      const std::vector<float>& ts = b == 0 ? types : ltypes;
+      const std::vector<float>& rs = b == 0 ? radii : lradii;
+      for (int i = 0; i < n; i++) {
+        for (int k = 0; k < 3; k++) bc(b, i, k) = cs[i * 3 + k];
+        bt(b, i) = ts[i];
+        br(b, i) = rs[i];
+      }
+      for (int k = 0; k < 10; k++) trs(b, k) = tr[k];
+      trs(b, 7) += 0.25f * b;                // a different translation per example
+      for (int k = 0; k < 3; k++) cen(b, k) = tr[4 + k];
+    }
+    int counts_h[B] = {N, NL};
+    int* counts = nullptr;
+    EXPECT(cudaMalloc(&counts, sizeof counts_h) == cudaSuccess);
+    EXPECT(cudaMemcpy(counts, counts_h, sizeof counts_h, cudaMemcpyHostToDevice) == cudaSuccess);
+    MGrid5f outb(B, T, D, D, D);
+    {
+      Grid5fCUDA og = outb.gpu();
+      gm.forward<2>(cen.gpu(), bc.gpu(), bt.gpu(), br.gpu(), og,
+                    reinterpret_cast<const lmg_transform*>(trs.gpu().data()), counts);
+    }
+    MGrid5f diffb(B, T, D, D, D);
+    for (int b = 0; b < B; b++)
+      for (size_t i = 0; i < diffv.size(); i++) diffb.cpu().data()[b * diffv.size() + i] = diffv[i] * (b + 1);
+    MGrid3f agb(B, NB, 3);
+    {
+      Grid3fCUDA ag = agb.gpu();
+      gm.backward<2>(cen.gpu(), bc.gpu(), bt.gpu(), br.gpu(), diffb.gpu(), ag, nullptr,
+                     reinterpret_cast<const lmg_transform*>(trs.gpu().data()), counts);
+    }
+    for (int b = 0; b < B; b++) {
+      int n = b == 0 ? N : NL;
+      MGrid2f c1(n, 3), ag1(n, 3);
+      MGrid1f t1(n), r1(n);
+      for (int i = 0; i < n; i++) {
+        for (int k = 0; k < 3; k++) c1(i, k) = bc(b, i, k);
+        t1(i) = bt(b, i);
+        r1(i) = br(b, i);
+      }
+      Transform one(Quaternion(tr[0], tr[1], tr[2], tr[3]), make_float3(tr[4], tr[5], tr[6]),
+                    make_float3(tr[7] + 0.25f * b, tr[8], tr[9]));
+      MGrid4f o1(T, D, D, D), d1(T, D, D, D);
+      for (size_t i = 0; i < diffv.size(); i++) d1.cpu().data()[i] = diffv[i] * (b + 1);
+      {
+        Grid4fCUDA og = o1.gpu();
+        Grid2fCUDA ag = ag1.gpu();
+        gm.forward(one.get_rotation_center(), c1.gpu(), t1.gpu(), r1.gpu(), og, &one);
+        gm.backward(one.get_rotation_center(), c1.gpu(), t1.gpu(), r1.gpu(), d1.gpu(), ag, &one);
+      }
+      const float* want = o1.cpu().data();
+      const float* got = outb.cpu().data() + (size_t)b * T * D * D * D;
+      bool same = true, any = false;
+      for (size_t i = 0; i < (size_t)T * D * D * D; i++) {
+        same = same && std::fabs(got[i] - want[i]) <= 1e-6f + 1e-5f * std::fabs(want[i]);
+        any = any || want[i] != 0.f;
+      }
+      EXPECT(same && any);
+      bool equal = true;
+      for (int i = 0; i < n; i++)
+        for (int k = 0; k < 3; k++) equal = equal && agb(b, i, k) == ag1(i, k);
+      EXPECT(equal);                          // the backward kernels sum in a fixed order
+      for (int i = n; i < NB; i++) EXPECT(agb(b, i, 0) == 0.f && agb(b, i, 1) == 0.f && agb(b, i, 2) == 0.f);
+    }
+    cudaFree(counts);
+  }
+
+  // ---- 11. merge_coordinates: vector types win when every non-empty set has them
+  {
+    std::vector<float3> c2 = {make_float3(0, 0, 0), make_float3(1, 0, 0)};
+    std::vector<std::vector<float>> v3 = {{1, 0, 0}, {0, 0.5f, 0.5f}}, v2 = {{0, 1}, {1, 0}};
+    Example ex;
+    ex.sets.push_back(CoordinateSet(c2, v3, std::vector<float>{1.f, 2.f, 3.f}));
+    CoordinateSet empty;
+    empty.max_type = 4;
+    ex.sets.push_back(empty);
+    ex.sets.push_back(CoordinateSet(c2, v2, std::vector<float>{4.f, 5.f}));
+    CoordinateSet m = ex.merge_coordinates();
+    EXPECT(m.has_vector_types() && m.size() == 4 && m.max_type == 9);
+    EXPECT(m.type_vector.dimension(1) == 9 && m.radii.size() == 5);
+    EXPECT(m.type_vector(1, 2) == 0.5f && m.type_vector(2, 8) == 1.f && m.type_vector(3, 7) == 1.f);
+    EXPECT(m.type_vector(2, 0) == 0.f && m.radii(3) == 4.f);
+    Example mixed;
+    mixed.sets.push_back(CoordinateSet(c2, std::vector<float>{0.f, 1.f}, std::vector<float>{1.f, 1.f}, 2));
+    mixed.sets.push_back(CoordinateSet(c2, v2, std::vector<float>{4.f, 5.f}));
+    EXPECT_THROW(mixed.merge_coordinates(), std::invalid_argument);
   }
 
   std::fclose(out);

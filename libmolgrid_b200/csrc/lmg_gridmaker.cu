@@ -648,9 +648,9 @@ __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, 
 // line, so a warp's reduction reaches 32/ZQ rows instead of 32 (the scatter kernels are bound by the
 // number of distinct lines their reductions touch).  `quad(i, dxy2, exy, d2v, ev, dzv, off)` is called
 // by every lane whose quad can hold a voxel of the item: i = column slot, off = row*dim + z of the quad.
-template <int ZQ, class BUF, class QuadFn>
+template <int ZQ, bool SCALED, class BUF, class QuadFn>
 __device__ __forceinline__ void qlane_sweep(const ItemParams& P, const BUF& buf, unsigned nkept, size_t dim,
-                                            float oz, float res, float kexp, float Tcull, int lane,
+                                            float oz, float res, float kexp, float Tcull, float scale, int lane,
                                             QuadFn quad) {
   constexpr int CPI = 32 / ZQ;
   const int zq = lane % ZQ, cl = lane / ZQ;
@@ -663,6 +663,7 @@ __device__ __forceinline__ void qlane_sweep(const ItemParams& P, const BUF& buf,
       dzv[j] = __fsub_rn(voxel_coord(oz, zz, res), P.z);
       bool in = zz >= P.loz && zz < P.hiz;
       d2v[j] = in ? __fmul_rn(dzv[j], dzv[j]) : CUDART_NAN_F;
+      if (SCALED) d2v[j] *= scale;
       ev[j] = ex2_approx(d2v[j] * kexp);
       lo = fminf(lo, d2v[j]);  // fminf skips the NaN entries
     }
@@ -670,6 +671,7 @@ __device__ __forceinline__ void qlane_sweep(const ItemParams& P, const BUF& buf,
     for (unsigned c0 = 0; c0 < nkept; c0 += CPI) {
       unsigned i = c0 + cl;
       float dxy2 = (cl < CPI && i < nkept) ? buf.dxy2[i] : CUDART_NAN_F;
+      if (SCALED) dxy2 *= scale;
       if (!(__fadd_rn(dxy2, lo) <= Tcull)) continue;  // also false for NaN: no column, or no z in range
       quad(i, dxy2, ex2_approx(dxy2 * kexp), d2v, ev, dzv, (size_t)buf.row[i] * dim + zoff);
     }
@@ -679,16 +681,25 @@ __device__ __forceinline__ void qlane_sweep(const ItemParams& P, const BUF& buf,
 // The sweep with as many lanes along z as the footprint spans aligned quads.  Measured: dense type
 // vectors at 96^3 (spans of 6) 2.16 -> 1.97 ms per 4 examples; the index-typed benchmark (spans of
 // 3 to 5) unchanged at 0.259 ms per 50.
+// SCALED: squared distances are handed to `quad` (and compared with Tcull) in units of the squared
+// atom radius, `scale` = 1 / ar^2 and `kexp` = -2 log2(e): one multiplication per column instead of
+// one per voxel for callers that want rsq / ar^2 (density only: the binary test keeps rsq itself).
+template <bool SCALED, class BUF, class QuadFn>
+__device__ __forceinline__ void qlane_sweep_span_t(unsigned span, const ItemParams& P, const BUF& buf, unsigned nkept,
+                                                   size_t dim, float oz, float res, float kexp, float Tcull,
+                                                   float scale, int lane, QuadFn quad) {
+  if (span <= 2) qlane_sweep<2, SCALED>(P, buf, nkept, dim, oz, res, kexp, Tcull, scale, lane, quad);
+  else if (span == 3) qlane_sweep<3, SCALED>(P, buf, nkept, dim, oz, res, kexp, Tcull, scale, lane, quad);
+  else if (span == 4) qlane_sweep<4, SCALED>(P, buf, nkept, dim, oz, res, kexp, Tcull, scale, lane, quad);
+  else if (span == 5) qlane_sweep<5, SCALED>(P, buf, nkept, dim, oz, res, kexp, Tcull, scale, lane, quad);
+  else if (span == 6) qlane_sweep<6, SCALED>(P, buf, nkept, dim, oz, res, kexp, Tcull, scale, lane, quad);
+  else qlane_sweep<8, SCALED>(P, buf, nkept, dim, oz, res, kexp, Tcull, scale, lane, quad);
+}
 template <class BUF, class QuadFn>
 __device__ __forceinline__ void qlane_sweep_span(unsigned span, const ItemParams& P, const BUF& buf, unsigned nkept,
                                                  size_t dim, float oz, float res, float kexp, float Tcull, int lane,
                                                  QuadFn quad) {
-  if (span <= 2) qlane_sweep<2>(P, buf, nkept, dim, oz, res, kexp, Tcull, lane, quad);
-  else if (span == 3) qlane_sweep<3>(P, buf, nkept, dim, oz, res, kexp, Tcull, lane, quad);
-  else if (span == 4) qlane_sweep<4>(P, buf, nkept, dim, oz, res, kexp, Tcull, lane, quad);
-  else if (span == 5) qlane_sweep<5>(P, buf, nkept, dim, oz, res, kexp, Tcull, lane, quad);
-  else if (span == 6) qlane_sweep<6>(P, buf, nkept, dim, oz, res, kexp, Tcull, lane, quad);
-  else qlane_sweep<8>(P, buf, nkept, dim, oz, res, kexp, Tcull, lane, quad);
+  qlane_sweep_span_t<false>(span, P, buf, nkept, dim, oz, res, kexp, Tcull, 1.f, lane, quad);
 }
 
 // number of aligned quads between the first and the last z of a footprint
@@ -727,20 +738,43 @@ __device__ __forceinline__ void forward_quads_item(const BwdArgs& G, int item, i
     unsigned nkept = compact_columns<ColBuf, false>(buf, P, cbase, ncols, ny, inv_ny, P.Tcut, ox, oy,
                                                     gm.res, gm.dim, lane);
     __syncwarp();
-    auto quad = [&](unsigned, float dxy2, float exy, const float (&d2v)[4], const float (&ev)[4],
-                    const float (&)[4], size_t off) {
-      float v[4];
+    // With a tail the density is continuous in the distance, and the squared distances may be taken
+    // in units of ar^2 (s = rsq / ar^2: one multiplication per column and z position instead of one per
+    // voxel; the Gaussian part ends at s = G^2, the tail clamps to zero at the cut-off).  Without a
+    // tail (negative gaussian_radius_multiple) the density jumps at the cut-off, and the comparison
+    // stays the reference's own, rsq against the threshold.
+    const bool tail = ta != 0.f || ntb != 0.f;
+    if (tail) {
+      const float sg = P.Tg * P.inv_ar2, scut = P.Tcut * P.inv_ar2;
+      auto quad = [&](unsigned, float dxy2, float exy, const float (&d2v)[4], const float (&ev)[4],
+                      const float (&)[4], size_t off) {
+        float v[4];
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
-        float rsq = __fadd_rn(dxy2, d2v[j]);
-        // tail (ta*dr - tb)^2 clamped to zero beyond the cut-off; a NaN rsq gives zero too
-        float tq = fminf(fmaf(ta, sqrt_approx(rsq * P.inv_ar2), ntb), 0.f);
-        float val = rsq <= P.Tg ? exy * ev[j] : tq * tq;
-        v[j] = VEC ? val * P.w : val;
-      }
-      red_add_v4(out + off, v[0], v[1], v[2], v[3]);
-    };
-    qlane_sweep_span(quad_span(P), P, buf, nkept, dim, oz, gm.res, kexp, P.Tcut, lane, quad);
+        for (int j = 0; j < 4; j++) {
+          float sq = dxy2 + d2v[j];
+          float tq = fminf(fmaf(ta, sqrt_approx(sq), ntb), 0.f);  // a NaN gives zero too
+          float val = sq <= sg ? exy * ev[j] : tq * tq;
+          v[j] = VEC ? val * P.w : val;
+        }
+        red_add_v4(out + off, v[0], v[1], v[2], v[3]);
+      };
+      qlane_sweep_span_t<true>(quad_span(P), P, buf, nkept, dim, oz, gm.res, NEG2_LOG2E, scut, P.inv_ar2, lane, quad);
+    } else {
+      auto quad = [&](unsigned, float dxy2, float exy, const float (&d2v)[4], const float (&ev)[4],
+                      const float (&)[4], size_t off) {
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          float rsq = __fadd_rn(dxy2, d2v[j]);
+          // tail (ta*dr - tb)^2 clamped to zero beyond the cut-off; a NaN rsq gives zero too
+          float tq = fminf(fmaf(ta, sqrt_approx(rsq * P.inv_ar2), ntb), 0.f);
+          float val = rsq <= P.Tg ? exy * ev[j] : tq * tq;
+          v[j] = VEC ? val * P.w : val;
+        }
+        red_add_v4(out + off, v[0], v[1], v[2], v[3]);
+      };
+      qlane_sweep_span(quad_span(P), P, buf, nkept, dim, oz, gm.res, kexp, P.Tcut, lane, quad);
+    }
     __syncwarp();
   }
 }

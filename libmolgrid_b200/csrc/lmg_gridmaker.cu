@@ -851,6 +851,8 @@ __device__ __forceinline__ BwdSums backward_quads_core(const BwdArgs& G, ItemPar
   const float k4 = want_ag ? 4.f * P.inv_ar2 : 0.f;
   const float kD = (want_ag && tail) ? -gm.D * P.inv_ar2 : 0.f, kE = (want_ag && tail) ? -gm.E * P.inv_ar : 0.f;
   const float ta = gm.ta, ntb = -gm.tb;
+  const float g16 = 16.f * P.inv_ar2 * P.inv_ar2, gm4 = -4.f * P.inv_ar2;  // MODE 3, Gaussian part
+  float sb = 0.f;                                                            // MODE 3: sum of diff*beta
 
   if (P.valid) {
     unsigned nx = P.hix - P.lox, ny = P.hiy - P.loy;
@@ -875,6 +877,7 @@ __device__ __forceinline__ BwdSums backward_quads_core(const BwdArgs& G, ItemPar
           float exy4 = k4 * exy;
           float fsum = 0.f;
           float dotxy = MODE == 3 ? fmaf(dx, inx, dy * iny) : 0.f;
+          float a0 = 0.f, a1 = 0.f, a2 = 0.f;  // MODE 3: sums over the column of diff*alpha*{1, dz, dz^2}
           for (unsigned q0 = 0; q0 < nq; q0 += 4) {
             // up to four quads of the column are requested together, then used
             float4 dv[4];
@@ -927,29 +930,29 @@ __device__ __forceinline__ BwdSums backward_quads_core(const BwdArgs& G, ItemPar
                     if (v > 0.f && dev[j] > 0.f) tg += __fdiv_rn(__fmul_rn(dvv[j], v), dev[j]);
                   }
                   if (MODE == 3) {
-                    if (rsq <= P.Tcut) {
-                      // second derivatives H_ab = alpha*delta_a*delta_b + [a==b]*beta of the density
-                      // (src/grid_maker.cu:812-878); delta = atom - grid point
-                      float alpha, beta;
-                      if (rsq <= P.Tg) {
-                        alpha = 16.f * g * P.inv_ar2 * P.inv_ar2;
-                        beta = -4.f * g * P.inv_ar2;
-                      } else {
-                        float id = rsqrt_approx(rsq);
-                        float S = fmaf(gm.D * P.inv_ar, rsq * id, gm.E);
-                        beta = S * id * P.inv_ar;
-                        alpha = fmaf(gm.D * P.inv_ar2, id * id, -beta * id * id);
-                      }
-                      float dzj = dzv[j], dvj = dvv[j];
-                      float dot = fmaf(dzj, inz, dotxy);
-                      float wa = P.w * alpha * dot;
-                      float wb = P.w * beta;
-                      float tt = alpha * intg;
-                      float bt = beta * intg;
-                      agx = fmaf(dvj, fmaf(wa, dx, fmaf(wb, inx, fmaf(tt, dx * dx, bt))), agx);
-                      agy = fmaf(dvj, fmaf(wa, dy, fmaf(wb, iny, fmaf(tt, dy * dy, bt))), agy);
-                      agz = fmaf(dvj, fmaf(wa, dzj, fmaf(wb, inz, fmaf(tt, dzj * dzj, bt))), agz);
+                    // second derivatives H_ab = alpha*delta_a*delta_b + [a==b]*beta of the density
+                    // (src/grid_maker.cu:812-878); delta = atom - grid point.  Per voxel only the
+                    // moments of diff*alpha in dz and the sum of diff*beta are taken; what is the same
+                    // for a whole column (dx, dy, the incoming gradients) is applied after it.
+                    float alpha, beta;
+                    if (rsq <= P.Tg) {
+                      alpha = g16 * g;
+                      beta = gm4 * g;
+                    } else {
+                      float id = rsqrt_approx(rsq);
+                      float S = fmaf(gm.D * P.inv_ar, rsq * id, gm.E);
+                      beta = S * id * P.inv_ar;
+                      alpha = fmaf(gm.D * P.inv_ar2, id * id, -beta * id * id);
                     }
+                    // nothing beyond the cut-off, nor for a NaN rsq (z outside the footprint), whose
+                    // alpha and beta are NaN as well: the products are selected, not multiplied by zero
+                    const bool inside = rsq <= P.Tcut;
+                    float t0 = inside ? dvv[j] * alpha : 0.f, tb = inside ? dvv[j] * beta : 0.f;
+                    float t1 = t0 * dzv[j];
+                    a0 += t0;
+                    a1 += t1;
+                    a2 = fmaf(t1, dzv[j], a2);
+                    sb += tb;
                   }
                 }
               }
@@ -959,10 +962,23 @@ __device__ __forceinline__ BwdSums backward_quads_core(const BwdArgs& G, ItemPar
             agx = fmaf(fsum, dx, agx);
             agy = fmaf(fsum, dy, agy);
           }
+          if (MODE == 3) {
+            // sum over the column of diff * (w*alpha*dot*delta_c + intg*alpha*delta_c^2), dot = dotxy + dz*inz
+            float wd = P.w * fmaf(dotxy, a0, inz * a1);
+            agx = fmaf(dx, fmaf(intg * dx, a0, wd), agx);
+            agy = fmaf(dy, fmaf(intg * dy, a0, wd), agy);
+            agz += fmaf(P.w, fmaf(dotxy, a1, inz * a2), intg * a2);
+          }
         }
       }
       __syncwarp();
     }
+  }
+  if (MODE == 3) {
+    // the isotropic part: diff*beta*(w*in_c + intg), the same factor for every voxel of the item
+    agx = fmaf(sb, fmaf(P.w, inx, intg), agx);
+    agy = fmaf(sb, fmaf(P.w, iny, intg), agy);
+    agz = fmaf(sb, fmaf(P.w, inz, intg), agz);
   }
 #pragma unroll
   for (int o = 16; o >= 1; o >>= 1) {

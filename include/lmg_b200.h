@@ -120,7 +120,10 @@ int lmg_forward(const lmg_gridmaker* g, const lmg_atoms* atoms, float* out, void
 /* Atom gradients atom_gradients[batch][max_atoms][3] from grid gradients
  * diff[batch][ntypes][D][D][D]; with vector types also type_gradients[batch][max_atoms][ntypes]
  * (must be NULL for index types).
- * Replaces GridMaker::backward (src/grid_maker.cu:576-642, CPU src/grid_maker.cpp:436-519). */
+ * Replaces GridMaker::backward (src/grid_maker.cu:576-642, CPU src/grid_maker.cpp:436-519).
+ * Inputs without atoms or without examples (max_atoms == 0 or batch == 0) are accepted by every
+ * pass, as the reference's loops over zero atoms are: lmg_forward and lmg_backward_gradients still
+ * clear their grids, the per-atom outputs (which are empty) are not touched and may be NULL. */
 int lmg_backward(const lmg_gridmaker* g, const lmg_atoms* atoms, const float* diff,
                  float* atom_gradients, float* type_gradients, void* workspace,
                  size_t workspace_bytes, void* stream);

@@ -159,3 +159,9 @@ class ExampleProvider(_py.ExampleProvider):
         if hasattr(self._order, "check_batch_size"):
             self._order.check_batch_size(B)
         return native.ExampleVec([self.next() for _ in range(B)])
+
+
+class ExampleDataset(_py.ExampleDataset):
+    """Random access to the examples of the lists, as compiled Example objects."""
+
+    _make = ExampleProvider._make

@@ -134,3 +134,35 @@ def test_resident_batches_take_the_compiled_route(molgrid, vector):
     assert torch.equal(ag, ag2)            # the backward kernels sum in a fixed order
     with pytest.raises((TypeError, ValueError)):
         molgrid.native.GridMaker.forward(gm, cen, dc, dt, dr, a, transforms=dtr[:, :9].contiguous())
+
+
+def test_provider_settings_feed_the_compiled_gridmaker(molgrid, tmp_path):
+    """A shuffled, balanced provider with vector types and a data set with random access: their
+    compiled Examples grid through the compiled GridMaker like the Python layer's do through its own."""
+    import libmolgrid_b200 as lmg
+    from libmolgrid_b200 import coord_cache
+    rng = np.random.default_rng(9)
+    lines = []
+    for i in range(8):
+        coord_cache.write_gninatypes(tmp_path / ("r%d.gninatypes" % i), rng.normal(size=(60, 3)) * 5, rng.integers(2, 14, 60))
+        coord_cache.write_gninatypes(tmp_path / ("l%d.gninatypes" % i), rng.normal(size=(9, 3)) * 2, rng.integers(2, 14, 9))
+        lines.append("%d %.2f r%d.gninatypes l%d.gninatypes" % (i % 2, i * 0.5, i, i))
+    (tmp_path / "s.types").write_text("\n".join(lines) + "\n")
+    kw = dict(data_root=str(tmp_path), shuffle=True, balanced=True, seed=5, default_batch_size=4)
+    pn, pp = molgrid.ExampleProvider(**kw), lmg.ExampleProvider(**kw)
+    for p in (pn, pp):
+        p.populate(str(tmp_path / "s.types"))
+    gn, gp = molgrid.GridMaker(0.5, 11.5), lmg.GridMaker(0.5, 11.5)
+    bn, bp = pn.next_batch(), pp.next_batch()
+    assert type(bn).__module__.endswith("molgrid_native") and [x.labels[0] for x in bn] == [1.0, 0.0, 1.0, 0.0]
+    a = torch.zeros((4,) + gn.grid_dimensions(pn.num_types()), device="cuda")
+    b = torch.zeros_like(a)
+    gn.forward(bn, a, 0.0, False)
+    gp.forward(bp, b, 0.0, False)
+    assert torch.allclose(a, b, rtol=1e-5, atol=1e-6) and float(a.max()) > 0
+    ds = molgrid.ExampleDataset(data_root=str(tmp_path))
+    ds.populate(str(tmp_path / "s.types"))
+    ex = ds[3]
+    one = torch.zeros(gn.grid_dimensions(ex.num_types()), device="cuda")
+    gn.forward(ex, one)
+    assert len(ds) == 8 and float(one.max()) > 0 and type(ex).__module__.endswith("molgrid_native")
